@@ -1,0 +1,62 @@
+// C ABI of the tcgen05 GEMM family.  Python fills LfGemmArgs through ctypes; the layout
+// below (all 8-byte fields first, then 4-byte fields) must stay in sync with
+// lorafusion_b200/ops/_native.py.
+#pragma once
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+// Epilogue selectors.
+enum LfGemmEpi {
+  LF_EPI_BF16 = 0,           // out[m, n] = bf16(acc * scale + bias[n])
+  LF_EPI_BF16_DROPMIX = 1,   // out[m, n] = bf16(acc0 + keep(m, n) * inv_keep * acc1)   (nacc == 2)
+  LF_EPI_F32_ACCUM = 2,      // out_f32[adapter][m, n] (or [n, m]) += scale * acc
+  LF_EPI_BF16_ADAPTER_SCALE = 3,  // out[m, n] = bf16(acc * adapter_scale[adapter(m tile)])
+};
+
+// D[M, N] = sum_k A[m, k] * B[n, k]  (+ second "slab" product A2[m, k2] * B2[n, k2]).
+// Operands are 2-D row-major bf16 tensors described as stored in memory:
+//   K-major operand : [rows = M or N, cols = K]   (reduction index contiguous)
+//   MN-major operand: [rows = K, cols = M or N]   (reduction index strided)
+typedef struct LfGemmArgs {
+  const void* a;
+  int64_t a_rows, a_cols, a_ld;
+  const void* b;
+  int64_t b_rows, b_cols, b_ld;
+  const void* a2;  // slab A operand, always K-major [M, K2]
+  int64_t a2_rows, a2_cols, a2_ld;
+  const void* b2;  // slab B operand
+  int64_t b2_rows, b2_cols, b2_ld;
+  const int32_t* tile_adapter;  // adapter id per 128-row M tile (dense mode), <0 = none; may be null
+  const int32_t* seg_tiles;     // segment mode: int4 {m0, k0, num_k_blocks, adapter} per tile
+  void* out;
+  int64_t ldo;
+  int64_t out_adapter_stride;   // elements between adapters in `out` (F32_ACCUM)
+  const float* adapter_scale;   // per-adapter scalar (ADAPTER_SCALE epilogue)
+  const void* bias;             // bf16 [N] or null
+  const uint32_t* adapter_thresh16;  // per-adapter dropout threshold (keep iff lane >= thresh) or null
+  const float* adapter_inv_keep;     // per-adapter 1 / (1 - p) or null
+  int32_t* err;                 // device error word
+  void* stream;
+  int32_t a_mn, b_mn, b2_mn;
+  int32_t M, N, K, K2;
+  int32_t bn, nacc, epi, mask_a;
+  int32_t b_adapter_rows, b2_adapter_rows;
+  int32_t num_seg_tiles;
+  int32_t out_transposed;
+  float scale;
+  float inv_keep;
+  uint32_t thresh16;
+  uint32_t seed_lo, seed_hi, stream_id;
+  int32_t row_offset, col_offset;
+  int32_t group_m, max_ctas;
+} LfGemmArgs;
+
+// Returns 0 on success, negative on argument/launch errors.
+int lf_gemm(const LfGemmArgs* args);
+
+#ifdef __cplusplus
+}
+#endif

@@ -1,0 +1,593 @@
+// Persistent, warp-specialised bf16 GEMM family for sm_100a built directly on tcgen05.mma
+// with fp32 accumulators in TMEM and TMA-fed 128-byte-swizzled shared-memory stages.
+//
+// One kernel template covers every GEMM-shaped op of the fused LoRA linear layer:
+//   * forward  Y = X W^T + S' B_a^T        (main loop over W, one extra "slab" of k-blocks
+//                                           over the rank dimension, adapter chosen per
+//                                           128-row tile)           -- reference K4/K5/K9
+//   * dX       dX = dY W + keep (.) (dS A_a) / (1 - p)              -- reference K6/K7/K10
+//   * the skinny LoRA products S' = a * drop(X) A_a^T, dS = a * dY B_a, dB, dA, with the
+//     dropout mask regenerated from Philox inside shared memory (never stored)
+//                                           -- reference K1-K3, K8, K11 and cuBLAS calls
+// (file:line citations of the reference live in lorafusion_b200/ops/lora.py).
+//
+// Roles inside a CTA (1 CTA per SM, grid = min(#tiles, #SMs)):
+//   warp 0      : TMA producer (one elected lane)
+//   warp 1      : TMEM allocator + single-thread tcgen05.mma issuer
+//   warps 2..5  : epilogue (each warp owns one 32-lane TMEM quarter)
+//   warps 6..13 : only when MASK_A: apply the dropout mask to the A stage in place
+// Accumulators are double-buffered in TMEM so the epilogue of tile i overlaps the main loop
+// of tile i+1.
+#include <stdio.h>
+
+#include "../common/philox.cuh"
+#include "../common/ptx.cuh"
+#include "../common/tensormap.h"
+#include "gemm_api.h"
+
+namespace lf {
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr int kNumMaskWarps = 8;
+
+struct GemmKParams {
+  int M, N;
+  int nkb_main, nkb2;
+  int num_m_tiles, num_n_tiles, num_tiles, group_m;
+  const int* tile_adapter;
+  const int4* seg_tiles;
+  int b_adapter_rows, b2_adapter_rows;
+  void* out;
+  long long ldo;
+  long long out_adapter_stride;
+  int out_transposed;
+  const float* adapter_scale;
+  float scale;
+  const __nv_bfloat16* bias;
+  const uint32_t* adapter_thresh16;
+  const float* adapter_inv_keep;
+  uint32_t thresh16;
+  float inv_keep;
+  uint32_t seed_lo, seed_hi, stream_id;
+  int row_offset, col_offset;
+  int* err;
+};
+
+struct TileCoord {
+  int m0, n0, k0, nkb, adapter;
+};
+
+__device__ __forceinline__ TileCoord decode_tile(const GemmKParams& p, int idx) {
+  TileCoord t;
+  if (p.seg_tiles != nullptr) {
+    const int4 s = p.seg_tiles[idx];
+    t.m0 = s.x;
+    t.n0 = 0;
+    t.k0 = s.y;
+    t.nkb = s.z;
+    t.adapter = s.w;
+    return t;
+  }
+  const int per_group = p.group_m * p.num_n_tiles;
+  const int g = idx / per_group;
+  const int first_m = g * p.group_m;
+  const int gsz = min(p.group_m, p.num_m_tiles - first_m);
+  const int r = idx - g * per_group;
+  const int m_tile = first_m + r % gsz;
+  const int n_tile = r / gsz;
+  t.m0 = m_tile * BM;
+  t.n0 = n_tile;  // multiplied by BN by the caller (BN is a template constant there)
+  t.k0 = 0;
+  t.nkb = p.nkb_main;
+  t.adapter = (p.tile_adapter != nullptr) ? p.tile_adapter[m_tile] : 0;
+  return t;
+}
+
+template <int BN>
+struct SmemPlan {
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr int BAR_BYTES = 512;
+  static constexpr int TOTAL = STAGES * STAGE_BYTES + BAR_BYTES + 1024;  // + alignment slack
+};
+
+template <int BN, int NACC, bool A_MN, bool B_MN, bool B2_MN, int EPI, bool MASK_A>
+__global__ void __launch_bounds__(MASK_A ? (192 + 32 * kNumMaskWarps) : 192, 1)
+    umma_gemm_kernel(const GemmKParams p, const __grid_constant__ CUtensorMap tmA,
+                     const __grid_constant__ CUtensorMap tmB,
+                     const __grid_constant__ CUtensorMap tmA2,
+                     const __grid_constant__ CUtensorMap tmB2) {
+  using Plan = SmemPlan<BN>;
+  constexpr int STAGES = Plan::STAGES;
+  constexpr int TMEM_COLS = BN * NACC * 2;
+  static_assert(TMEM_COLS <= 512, "TMEM budget");
+  constexpr uint32_t TMEM_ALLOC = TMEM_COLS <= 32 ? 32 : TMEM_COLS <= 64 ? 64 : TMEM_COLS <= 128 ? 128 : TMEM_COLS <= 256 ? 256 : 512;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * Plan::STAGE_BYTES);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + STAGES;
+  uint64_t* ready = bars + 2 * STAGES;
+  uint64_t* tfull = bars + 3 * STAGES;
+  uint64_t* tempty = tfull + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  AbortCtx ctx{p.err, abort_flag};
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+      mbar_init(&ready[s], 32 * kNumMaskWarps);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&tfull[b], 1);
+      mbar_init(&tempty[b], 128);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+    if (p.nkb2 > 0) {
+      tma_prefetch_desc(&tmA2);
+      tma_prefetch_desc(&tmB2);
+    }
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_ALLOC);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      int it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+        TileCoord t = decode_tile(p, tile);
+        const int n0 = (p.seg_tiles != nullptr) ? 0 : t.n0 * BN;
+        const int nkb2 = (t.adapter >= 0) ? p.nkb2 : 0;
+        const int by = (t.adapter >= 0) ? t.adapter * p.b_adapter_rows : 0;
+        const int by2 = (t.adapter >= 0) ? t.adapter * p.b2_adapter_rows : 0;
+        const int nkb = (t.adapter < 0 && p.b_adapter_rows > 0) ? 0 : t.nkb;
+        const int total = nkb + nkb2;
+        for (int kb = 0; kb < total; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&empty[s], ph ^ 1, ctx, ERR_WAIT_EMPTY)) {
+            ok = false;
+            break;
+          }
+          uint8_t* sA = smem + s * Plan::STAGE_BYTES;
+          uint8_t* sB = sA + Plan::A_BYTES;
+          mbar_expect_tx(&full[s], Plan::STAGE_BYTES);
+          if (kb < nkb) {
+            const int kk = t.k0 + kb * BK;
+            if (!A_MN) {
+              tma_load_2d(sA, &tmA, &full[s], kk, t.m0);
+            } else {
+              tma_load_2d(sA, &tmA, &full[s], t.m0, kk);
+              tma_load_2d(sA + 8192, &tmA, &full[s], t.m0 + 64, kk);
+            }
+            if (!B_MN) {
+              tma_load_2d(sB, &tmB, &full[s], kk, by + n0);
+            } else {
+#pragma unroll
+              for (int h = 0; h < BN / 64; ++h)
+                tma_load_2d(sB + h * 8192, &tmB, &full[s], n0 + 64 * h, by + kk);
+            }
+          } else {
+            const int kk2 = (kb - nkb) * BK;
+            tma_load_2d(sA, &tmA2, &full[s], kk2, t.m0);
+            if (!B2_MN) {
+              tma_load_2d(sB, &tmB2, &full[s], kk2, by2 + n0);
+            } else {
+#pragma unroll
+              for (int h = 0; h < BN / 64; ++h)
+                tma_load_2d(sB + h * 8192, &tmB2, &full[s], n0 + 64 * h, by2 + kk2);
+            }
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ------------------------------
+    if (lane == 0) {
+      constexpr uint32_t IDESC_MAIN = make_idesc_bf16(BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      constexpr uint32_t IDESC_SLAB = make_idesc_bf16(BM, BN, 0, B2_MN ? 1 : 0);
+      int it = 0;
+      int tile_iter = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++tile_iter) {
+        TileCoord t = decode_tile(p, tile);
+        const int nkb2 = (t.adapter >= 0) ? p.nkb2 : 0;
+        const int nkb = (t.adapter < 0 && p.b_adapter_rows > 0) ? 0 : t.nkb;
+        const int total = nkb + nkb2;
+        const int buf = tile_iter & 1;
+        const uint32_t bph = (tile_iter >> 1) & 1;
+        if (!mbar_wait(&tempty[buf], bph ^ 1, ctx, ERR_WAIT_TMEM_EMPTY)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t acc0 = tmem_base + uint32_t(buf * BN * NACC);
+        const uint32_t acc1 = acc0 + BN;
+        for (int kb = 0; kb < total; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(MASK_A ? &ready[s] : &full[s], ph, ctx,
+                         MASK_A ? ERR_WAIT_READY : ERR_WAIT_FULL)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t sA = smem_u32(smem + s * Plan::STAGE_BYTES);
+          const uint32_t sB = sA + Plan::A_BYTES;
+          const bool slab = kb >= nkb;
+          const bool a_mn = slab ? false : A_MN;
+          const bool b_mn = slab ? B2_MN : B_MN;
+          const uint32_t d = (NACC == 2 && slab) ? acc1 : acc0;
+#pragma unroll
+          for (int kk = 0; kk < BK / 16; ++kk) {
+            const uint64_t da = a_mn ? make_smem_desc_sw128(sA + kk * 2048, 8192, 1024)
+                                     : make_smem_desc_sw128(sA + kk * 32, 16, 1024);
+            const uint64_t db = b_mn ? make_smem_desc_sw128(sB + kk * 2048, 8192, 1024)
+                                     : make_smem_desc_sw128(sB + kk * 32, 16, 1024);
+            const uint32_t accum =
+                (NACC == 2 && slab) ? uint32_t(kb > nkb || kk > 0) : uint32_t(kb > 0 || kk > 0);
+            umma_bf16_ss(d, da, db, slab ? IDESC_SLAB : IDESC_MAIN, accum);
+          }
+          tc_commit(&empty[s]);
+        }
+        if (!ok) break;
+        if (total > 0) {
+          tc_commit(&tfull[buf]);
+        } else {
+          mbar_arrive(&tfull[buf]);
+        }
+      }
+    }
+  } else if (warp < 6) {
+    // ------------------------------ epilogue ------------------------------
+    const int q = warp & 3;  // TMEM lane quarter this warp may access
+    int tile_iter = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++tile_iter) {
+      TileCoord t = decode_tile(p, tile);
+      const int n0 = (p.seg_tiles != nullptr) ? 0 : t.n0 * BN;
+      const int nkb2 = (t.adapter >= 0) ? p.nkb2 : 0;
+      const int nkb = (t.adapter < 0 && p.b_adapter_rows > 0) ? 0 : t.nkb;
+      const bool has_work = (nkb + nkb2) > 0;
+      const bool has_slab = nkb2 > 0;
+      const int buf = tile_iter & 1;
+      const uint32_t bph = (tile_iter >> 1) & 1;
+      if (!mbar_wait(&tfull[buf], bph, ctx, ERR_WAIT_TMEM_FULL)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after_sync();
+      const int row = t.m0 + q * 32 + lane;
+      const uint32_t lane_addr = uint32_t(q * 32) << 16;
+      const uint32_t acc0 = tmem_base + uint32_t(buf * BN * NACC) + lane_addr;
+      const uint32_t acc1 = acc0 + BN;
+
+      float tile_scale = p.scale;
+      if (EPI == LF_EPI_BF16_ADAPTER_SCALE) {
+        tile_scale = (t.adapter >= 0 && p.adapter_scale != nullptr) ? p.adapter_scale[t.adapter]
+                                                                    : (t.adapter >= 0 ? p.scale : 0.f);
+      }
+      uint32_t thresh = p.thresh16;
+      float inv_keep = p.inv_keep;
+      if (EPI == LF_EPI_BF16_DROPMIX && t.adapter >= 0 && p.adapter_thresh16 != nullptr) {
+        thresh = p.adapter_thresh16[t.adapter];
+        inv_keep = p.adapter_inv_keep[t.adapter];
+      }
+
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        uint32_t r2[32];
+        if (has_work) {
+          tmem_ld_32x32b_x32(acc0 + c * 32, r);
+          if (NACC == 2 && has_slab) tmem_ld_32x32b_x32(acc1 + c * 32, r2);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r[j] = 0u;
+        }
+        const int col0 = n0 + c * 32;
+        if (EPI == LF_EPI_F32_ACCUM) {
+          if (has_work && row < p.M) {
+            float* out = reinterpret_cast<float*>(p.out) +
+                         (t.adapter >= 0 ? t.adapter * p.out_adapter_stride : 0);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const int col = col0 + j;
+              if (col < p.N) {
+                float* dst = p.out_transposed ? (out + (long long)col * p.ldo + row)
+                                              : (out + (long long)row * p.ldo + col);
+                *dst += tile_scale * __uint_as_float(r[j]);
+              }
+            }
+          }
+        } else {
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * tile_scale;
+          if (EPI == LF_EPI_BF16_DROPMIX) {
+            if (NACC == 2 && has_slab) {
+              if (thresh == 0) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] += __uint_as_float(r2[j]);
+              } else {
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {
+                  const uint32_t keep =
+                      dropout_keep8(uint32_t(row + p.row_offset),
+                                    uint32_t((col0 + p.col_offset) >> 3) + g, p.stream_id,
+                                    p.seed_lo, p.seed_hi, thresh);
+#pragma unroll
+                  for (int j = 0; j < 8; ++j)
+                    if ((keep >> j) & 1u) v[g * 8 + j] += inv_keep * __uint_as_float(r2[g * 8 + j]);
+                }
+              }
+            }
+          }
+          if (EPI == LF_EPI_BF16 && p.bias != nullptr) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const int col = col0 + j;
+              if (col < p.N) v[j] += __bfloat162float(p.bias[col]);
+            }
+          }
+          if (row < p.M) {
+            __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.out) + (long long)row * p.ldo;
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              const int col = col0 + g * 8;
+              if (col + 8 <= p.N) {
+                st_global_v4(out + col, pack_bf16x2(v[g * 8 + 0], v[g * 8 + 1]),
+                             pack_bf16x2(v[g * 8 + 2], v[g * 8 + 3]),
+                             pack_bf16x2(v[g * 8 + 4], v[g * 8 + 5]),
+                             pack_bf16x2(v[g * 8 + 6], v[g * 8 + 7]));
+              } else {
+                for (int j = 0; j < 8; ++j)
+                  if (col + j < p.N) out[col + j] = __float2bfloat16(v[g * 8 + j]);
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before_sync();
+      mbar_arrive(&tempty[buf]);
+    }
+  } else if (MASK_A) {
+    // ------------------- dropout mask applied to the A stage in place -------------------
+    const int mt = threadIdx.x - 192;  // 0 .. 32*kNumMaskWarps-1
+    constexpr int NMT = 32 * kNumMaskWarps;
+    int it = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+      TileCoord t = decode_tile(p, tile);
+      const int nkb2 = (t.adapter >= 0) ? p.nkb2 : 0;
+      const int nkb = (t.adapter < 0 && p.b_adapter_rows > 0) ? 0 : t.nkb;
+      const int total = nkb + nkb2;
+      uint32_t thresh = p.thresh16;
+      float inv_keep = p.inv_keep;
+      if (t.adapter >= 0 && p.adapter_thresh16 != nullptr) {
+        thresh = p.adapter_thresh16[t.adapter];
+        inv_keep = p.adapter_inv_keep[t.adapter];
+      }
+      for (int kb = 0; kb < total; ++kb, ++it) {
+        const int s = it % STAGES;
+        const uint32_t ph = (it / STAGES) & 1;
+        if (!mbar_wait(&full[s], ph, ctx, ERR_WAIT_FULL)) {
+          ok = false;
+          break;
+        }
+        if (kb < nkb && thresh != 0) {
+          uint8_t* sA = smem + s * Plan::STAGE_BYTES;
+          const int kk = t.k0 + kb * BK;
+#pragma unroll
+          for (int i = 0; i < (Plan::A_BYTES / 16) / NMT; ++i) {
+            const int qd = mt + i * NMT;  // 16-byte chunk index inside the A stage
+            int token, feature;
+            if (!A_MN) {
+              const int r = qd >> 3;
+              const int c = (qd & 7) ^ (r & 7);
+              token = t.m0 + r;
+              feature = kk + 8 * c;
+            } else {
+              const int h = qd >> 9;
+              const int kr = (qd & 511) >> 3;
+              const int c = (qd & 7) ^ (kr & 7);
+              token = kk + kr;
+              feature = t.m0 + 64 * h + 8 * c;
+            }
+            const uint32_t keep =
+                dropout_keep8(uint32_t(token + p.row_offset), uint32_t((feature + p.col_offset) >> 3),
+                              p.stream_id, p.seed_lo, p.seed_hi, thresh);
+            uint4* ptr = reinterpret_cast<uint4*>(sA + qd * 16);
+            uint4 x = *ptr;
+            uint32_t w[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              float2 f = unpack_bf16x2(w[j]);
+              f.x = ((keep >> (2 * j)) & 1u) ? f.x * inv_keep : 0.f;
+              f.y = ((keep >> (2 * j + 1)) & 1u) ? f.y * inv_keep : 0.f;
+              w[j] = pack_bf16x2(f.x, f.y);
+            }
+            *ptr = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+          fence_proxy_async_smem();
+        }
+        mbar_arrive(&ready[s]);
+      }
+    }
+  }
+
+  // ------------------------------ teardown ------------------------------
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag != 0) {
+    // Give copies that may still be in flight a bounded time to land before the shared
+    // memory and TMEM of this CTA are released.
+    const unsigned long long t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, TMEM_ALLOC);
+  }
+}
+
+// ------------------------------------------------------------------------------------
+// host side
+// ------------------------------------------------------------------------------------
+template <int BN, int NACC, bool A_MN, bool B_MN, bool B2_MN, int EPI, bool MASK_A>
+static int launch_variant(const GemmKParams& kp, const CUtensorMap& tA, const CUtensorMap& tB,
+                          const CUtensorMap& tA2, const CUtensorMap& tB2, int grid,
+                          cudaStream_t stream) {
+  auto kern = umma_gemm_kernel<BN, NACC, A_MN, B_MN, B2_MN, EPI, MASK_A>;
+  constexpr int smem = SmemPlan<BN>::TOTAL;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) {
+      fprintf(stderr, "lf_gemm: cudaFuncSetAttribute failed: %s\n", cudaGetErrorString(e));
+      return -10;
+    }
+    configured = true;
+  }
+  const int threads = MASK_A ? (192 + 32 * kNumMaskWarps) : 192;
+  kern<<<grid, threads, smem, stream>>>(kp, tA, tB, tA2, tB2);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    fprintf(stderr, "lf_gemm: launch failed: %s\n", cudaGetErrorString(e));
+    return -11;
+  }
+  return 0;
+}
+
+static int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+  }
+  return n;
+}
+
+}  // namespace lf
+
+extern "C" int lf_gemm(const LfGemmArgs* a) {
+  using namespace lf;
+  if (a == nullptr || a->a == nullptr || a->b == nullptr || a->out == nullptr) return -1;
+  if (a->bn != 64 && a->bn != 128 && a->bn != 256) return -2;
+  if (a->K2 % BK != 0) return -3;
+  const int BN = a->bn;
+
+  CUtensorMap tA, tB, tA2, tB2;
+  int rc;
+  // A: K-major box = [128 rows x 64 cols]; MN-major box = [64 rows(k) x 64 cols(mn)]
+  rc = make_tmap_2d_b16(&tA, a->a, a->a_rows, a->a_cols, a->a_ld, a->a_mn ? 64 : BM, 64, true);
+  if (rc != 0) return -20 + rc;
+  rc = make_tmap_2d_b16(&tB, a->b, a->b_rows, a->b_cols, a->b_ld, a->b_mn ? 64 : BN, 64, true);
+  if (rc != 0) return -30 + rc;
+  if (a->K2 > 0) {
+    if (a->a2 == nullptr || a->b2 == nullptr) return -4;
+    rc = make_tmap_2d_b16(&tA2, a->a2, a->a2_rows, a->a2_cols, a->a2_ld, BM, 64, true);
+    if (rc != 0) return -40 + rc;
+    rc = make_tmap_2d_b16(&tB2, a->b2, a->b2_rows, a->b2_cols, a->b2_ld, a->b2_mn ? 64 : BN, 64,
+                          true);
+    if (rc != 0) return -50 + rc;
+  } else {
+    tA2 = tA;
+    tB2 = tB;
+  }
+
+  GemmKParams kp;
+  kp.M = a->M;
+  kp.N = a->N;
+  kp.nkb_main = (a->K + BK - 1) / BK;
+  kp.nkb2 = a->K2 / BK;
+  kp.num_m_tiles = (a->M + BM - 1) / BM;
+  kp.num_n_tiles = (a->N + BN - 1) / BN;
+  kp.seg_tiles = reinterpret_cast<const int4*>(a->seg_tiles);
+  kp.num_tiles = (a->seg_tiles != nullptr) ? a->num_seg_tiles : kp.num_m_tiles * kp.num_n_tiles;
+  kp.group_m = a->group_m > 0 ? a->group_m : 8;
+  kp.tile_adapter = a->tile_adapter;
+  kp.b_adapter_rows = a->b_adapter_rows;
+  kp.b2_adapter_rows = a->b2_adapter_rows;
+  kp.out = a->out;
+  kp.ldo = a->ldo;
+  kp.out_adapter_stride = a->out_adapter_stride;
+  kp.out_transposed = a->out_transposed;
+  kp.adapter_scale = a->adapter_scale;
+  kp.scale = a->scale;
+  kp.bias = reinterpret_cast<const __nv_bfloat16*>(a->bias);
+  kp.adapter_thresh16 = a->adapter_thresh16;
+  kp.adapter_inv_keep = a->adapter_inv_keep;
+  kp.thresh16 = a->thresh16;
+  kp.inv_keep = a->inv_keep;
+  kp.seed_lo = a->seed_lo;
+  kp.seed_hi = a->seed_hi;
+  kp.stream_id = a->stream_id;
+  kp.row_offset = a->row_offset;
+  kp.col_offset = a->col_offset;
+  kp.err = a->err;
+  if (kp.num_tiles <= 0) return 0;
+
+  int grid = sm_count();
+  if (a->max_ctas > 0 && a->max_ctas < grid) grid = a->max_ctas;
+  if (kp.num_tiles < grid) grid = kp.num_tiles;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(a->stream);
+
+  const int key = (BN << 16) | (a->nacc << 12) | ((a->a_mn ? 1 : 0) << 11) |
+                  ((a->b_mn ? 1 : 0) << 10) | ((a->b2_mn ? 1 : 0) << 9) | (a->epi << 4) |
+                  (a->mask_a ? 1 : 0);
+#define LF_KEY(bn, nacc, amn, bmn, b2mn, epi, mask) \
+  (((bn) << 16) | ((nacc) << 12) | ((amn) << 11) | ((bmn) << 10) | ((b2mn) << 9) | ((epi) << 4) | (mask))
+#define LF_CASE(bn, nacc, amn, bmn, b2mn, epi, mask)                                         \
+  case LF_KEY(bn, nacc, amn, bmn, b2mn, epi, mask):                                          \
+    return launch_variant<bn, nacc, (amn) != 0, (bmn) != 0, (b2mn) != 0, epi, (mask) != 0>(  \
+        kp, tA, tB, tA2, tB2, grid, st);
+  switch (key) {
+    // forward base+LoRA and plain NT GEMM
+    LF_CASE(256, 1, 0, 0, 0, LF_EPI_BF16, 0)
+    LF_CASE(128, 1, 0, 0, 0, LF_EPI_BF16, 0)
+    // dX without dropout and plain NN GEMM
+    LF_CASE(256, 1, 0, 1, 1, LF_EPI_BF16, 0)
+    LF_CASE(128, 1, 0, 1, 1, LF_EPI_BF16, 0)
+    // dX with the dropout mask regenerated in the epilogue
+    LF_CASE(128, 2, 0, 1, 1, LF_EPI_BF16_DROPMIX, 0)
+    // S' = alpha * dropout(X) A^T
+    LF_CASE(64, 1, 0, 0, 0, LF_EPI_BF16_ADAPTER_SCALE, 0)
+    LF_CASE(64, 1, 0, 0, 0, LF_EPI_BF16_ADAPTER_SCALE, 1)
+    // dS = alpha * dY B
+    LF_CASE(64, 1, 0, 1, 0, LF_EPI_BF16_ADAPTER_SCALE, 0)
+    // dB += dY^T S'   /   dA += dS^T dropout(X)
+    LF_CASE(64, 1, 1, 1, 0, LF_EPI_F32_ACCUM, 0)
+    LF_CASE(64, 1, 1, 1, 0, LF_EPI_F32_ACCUM, 1)
+    default:
+      fprintf(stderr, "lf_gemm: no kernel variant for key 0x%x\n", key);
+      return -5;
+  }
+#undef LF_CASE
+#undef LF_KEY
+}
