@@ -1,0 +1,494 @@
+// Backward of the causal varlen GQA attention (head_dim 128) on sm_100a, as three kernels:
+//   1. attn_delta_kernel : delta[h, m] = sum_d O[m, h, d] * dO[m, h, d]
+//   2. attn_dq_kernel    : one CTA per (query tile, query head) loops over key tiles,
+//                          recomputes P from the saved log-sum-exp and accumulates
+//                          dQ += dS K in TMEM.
+//   3. attn_dkdv_kernel  : one CTA per (key tile, kv head) loops over the query heads of
+//                          its group and the query tiles at or below the diagonal and
+//                          accumulates dV += P^T dO and dK += dS^T Q in TMEM.
+// Splitting dQ from dK/dV costs two extra recomputation GEMMs per tile pair but keeps
+// every output element owned by exactly one CTA: no atomics, bitwise-reproducible
+// gradients.  Gradients are written into a buffer with the layout of the packed QKV
+// projection so that the rotary backward and the QKV-linear backward consume it in place.
+// (The reference calls FlashAttention-2's backward through autograd.)
+#include <stdio.h>
+
+#include "../common/tensormap.h"
+#include "attn_common.cuh"
+
+namespace lf {
+
+struct AttnBwdParams {
+  const int4* tiles;
+  int num_tiles;
+  int Hq, Hkv;
+  int q_col0, k_col0, v_col0;
+  __nv_bfloat16* dqkv;
+  long long ld_qkv;
+  const float* lse;
+  const float* delta;
+  long long M_total;
+  float scale, scale_log2e;
+  int* err;
+};
+
+constexpr int BWD_SMEM = ATT_TILE_BYTES * 7 + 256 + 1024;
+
+// ----------------------------------------------------------------------------------
+__global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o,
+                                  const __nv_bfloat16* __restrict__ d_o, float* __restrict__ delta,
+                                  long long M, int Hq, long long ld) {
+  const long long w = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (w >= M * Hq) return;
+  const long long m = w / Hq;
+  const int h = int(w % Hq);
+  const uint2 a = *reinterpret_cast<const uint2*>(o + m * ld + h * ATT_D + lane * 4);
+  const uint2 b = *reinterpret_cast<const uint2*>(d_o + m * ld + h * ATT_D + lane * 4);
+  const float2 a0 = unpack_bf16x2(a.x), a1 = unpack_bf16x2(a.y);
+  const float2 b0 = unpack_bf16x2(b.x), b1 = unpack_bf16x2(b.y);
+  float s = a0.x * b0.x + a0.y * b0.y + a1.x * b1.x + a1.y * b1.y;
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+  if (lane == 0) delta[(long long)h * M + m] = s;
+}
+
+// ----------------------------------------------------------------------------------
+// dQ
+// ----------------------------------------------------------------------------------
+__global__ void __launch_bounds__(192, 1)
+attn_dq_kernel(const AttnBwdParams p, const __grid_constant__ CUtensorMap tmQKV,
+               const __grid_constant__ CUtensorMap tmDO) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sDO = smem + ATT_TILE_BYTES;
+  uint8_t* sKV = smem + 2 * ATT_TILE_BYTES;  // stage s: K, V
+  uint8_t* sDS = smem + 6 * ATT_TILE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 7 * ATT_TILE_BYTES);
+  uint64_t* q_full = bars;
+  uint64_t* kv_full = bars + 1;
+  uint64_t* kv_empty = bars + 3;
+  uint64_t* sdp_full = bars + 5;
+  uint64_t* sdp_empty = bars + 6;
+  uint64_t* ds_full = bars + 7;
+  uint64_t* dq_done = bars + 8;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  AbortCtx ctx{p.err, abort_flag};
+  const int4 tile = p.tiles[blockIdx.x];
+  const int row0 = tile.x, rows = tile.y, seq_row0 = tile.z;
+  const int h = blockIdx.y;
+  const int g = h / (p.Hq / p.Hkv);
+  const int n_kv = (row0 - seq_row0) / ATT_TILE + 1;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&kv_full[i], 1);
+      mbar_init(&kv_empty[i], 1);
+    }
+    mbar_init(sdp_full, 1);
+    mbar_init(sdp_empty, 128);
+    mbar_init(ds_full, 128);
+    mbar_init(dq_done, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tS = tmem_base, tDP = tmem_base + 128, tDQ = tmem_base + 256;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(q_full, 2 * ATT_TILE_BYTES);
+      att_load_tile(sQ, &tmQKV, q_full, p.q_col0 + h * ATT_D, row0);
+      att_load_tile(sDO, &tmDO, q_full, h * ATT_D, row0);
+      for (int j = 0; j < n_kv; ++j) {
+        const int s = j & 1;
+        if (!mbar_wait(&kv_empty[s], ((j >> 1) & 1) ^ 1, ctx, ERR_WAIT_EMPTY)) break;
+        mbar_expect_tx(&kv_full[s], 2 * ATT_TILE_BYTES);
+        uint8_t* sK = sKV + s * 2 * ATT_TILE_BYTES;
+        att_load_tile(sK, &tmQKV, &kv_full[s], p.k_col0 + g * ATT_D, seq_row0 + j * ATT_TILE);
+        att_load_tile(sK + ATT_TILE_BYTES, &tmQKV, &kv_full[s], p.v_col0 + g * ATT_D,
+                      seq_row0 + j * ATT_TILE);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      bool ok = mbar_wait(q_full, 0, ctx, ERR_WAIT_FULL);
+      for (int j = 0; ok && j < n_kv; ++j) {
+        const int s = j & 1;
+        const uint32_t sK = smem_u32(sKV + s * 2 * ATT_TILE_BYTES);
+        if (!mbar_wait(&kv_full[s], (j >> 1) & 1, ctx, ERR_WAIT_FULL) ||
+            !mbar_wait(sdp_empty, (j & 1) ^ 1, ctx, ERR_WAIT_TMEM_EMPTY)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        att_mma_kk(tS, smem_u32(sQ), sK, false);
+        att_mma_kk(tDP, smem_u32(sDO), sK + ATT_TILE_BYTES, false);
+        tc_commit(sdp_full);
+        if (!mbar_wait(ds_full, j & 1, ctx, ERR_WAIT_READY)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        att_mma_kmn(tDQ, smem_u32(sDS), sK, j > 0);
+        tc_commit(&kv_empty[s]);
+        tc_commit(dq_done);
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    const int r = q * 32 + lane;
+    const uint32_t lane_addr = uint32_t(q * 32) << 16;
+    const long long grow = (long long)row0 + r;
+    const bool row_valid = r < rows;
+    const float lse2 = row_valid ? p.lse[(long long)h * p.M_total + grow] * 1.4426950408889634f : 0.f;
+    const float dlt = row_valid ? p.delta[(long long)h * p.M_total + grow] : 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_kv; ++j) {
+      if (!mbar_wait(sdp_full, j & 1, ctx, ERR_WAIT_TMEM_FULL)) {
+        ok = false;
+        break;
+      }
+      if (j > 0 && !mbar_wait(dq_done, (j - 1) & 1, ctx, ERR_WAIT_MISC)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after_sync();
+      const bool diag = (j == n_kv - 1);
+#pragma unroll 1
+      for (int cc = 0; cc < 4; ++cc) {
+        uint32_t sv[32], dv[32];
+        tmem_ld_32x32b_x32(tS + lane_addr + cc * 32, sv);
+        tmem_ld_32x32b_x32(tDP + lane_addr + cc * 32, dv);
+        tmem_ld_wait();
+        float ds[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int col = cc * 32 + i;
+          float pv = exp2f(__uint_as_float(sv[i]) * p.scale_log2e - lse2);
+          if (!row_valid || (diag && col > r)) pv = 0.f;
+          ds[i] = pv * (__uint_as_float(dv[i]) - dlt) * p.scale;
+        }
+        att_store_row_chunk(sDS, r, cc * 32, ds);
+      }
+      tc_fence_before_sync();
+      mbar_arrive(sdp_empty);
+      fence_proxy_async_smem();
+      mbar_arrive(ds_full);
+    }
+    if (ok && mbar_wait(dq_done, (n_kv - 1) & 1, ctx, ERR_WAIT_MISC)) {
+      tc_fence_after_sync();
+      __nv_bfloat16* orow = p.dqkv + grow * p.ld_qkv + p.q_col0 + h * ATT_D;
+#pragma unroll 1
+      for (int cc = 0; cc < 4; ++cc) {
+        uint32_t o[32];
+        tmem_ld_32x32b_x32(tDQ + lane_addr + cc * 32, o);
+        tmem_ld_wait();
+        if (row_valid) {
+#pragma unroll
+          for (int gq = 0; gq < 4; ++gq)
+            st_global_v4(orow + cc * 32 + gq * 8,
+                         pack_bf16x2(__uint_as_float(o[gq * 8 + 0]), __uint_as_float(o[gq * 8 + 1])),
+                         pack_bf16x2(__uint_as_float(o[gq * 8 + 2]), __uint_as_float(o[gq * 8 + 3])),
+                         pack_bf16x2(__uint_as_float(o[gq * 8 + 4]), __uint_as_float(o[gq * 8 + 5])),
+                         pack_bf16x2(__uint_as_float(o[gq * 8 + 6]), __uint_as_float(o[gq * 8 + 7])));
+        }
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag != 0) {
+    const unsigned long long t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// ----------------------------------------------------------------------------------
+// dK, dV
+// ----------------------------------------------------------------------------------
+__global__ void __launch_bounds__(192, 1)
+attn_dkdv_kernel(const AttnBwdParams p, const __grid_constant__ CUtensorMap tmQKV,
+                 const __grid_constant__ CUtensorMap tmDO) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~uintptr_t(1023));
+  uint8_t* sK = smem;
+  uint8_t* sV = smem + ATT_TILE_BYTES;
+  uint8_t* sQD = smem + 2 * ATT_TILE_BYTES;  // stage s: Q, dO
+  uint8_t* sPD = smem + 6 * ATT_TILE_BYTES;  // P, then dS
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 7 * ATT_TILE_BYTES);
+  uint64_t* kv_full = bars;
+  uint64_t* qd_full = bars + 1;
+  uint64_t* qd_empty = bars + 3;
+  uint64_t* sdp_full = bars + 5;
+  uint64_t* sdp_empty = bars + 6;
+  uint64_t* p_full = bars + 7;
+  uint64_t* dv_done = bars + 8;
+  uint64_t* ds_full = bars + 9;
+  uint64_t* dk_done = bars + 10;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  AbortCtx ctx{p.err, abort_flag};
+  const int4 tile = p.tiles[blockIdx.x];
+  const int row0 = tile.x, rows = tile.y, seq_row0 = tile.z, seq_rows = tile.w;
+  const int g = blockIdx.y;
+  const int group = p.Hq / p.Hkv;
+  const int i_kv = (row0 - seq_row0) / ATT_TILE;
+  const int n_q_tiles = (seq_rows + ATT_TILE - 1) / ATT_TILE;
+  const int per_head = n_q_tiles - i_kv;
+  const int n_it = per_head * group;
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&qd_full[i], 1);
+      mbar_init(&qd_empty[i], 1);
+    }
+    mbar_init(sdp_full, 1);
+    mbar_init(sdp_empty, 128);
+    mbar_init(p_full, 128);
+    mbar_init(dv_done, 1);
+    mbar_init(ds_full, 128);
+    mbar_init(dk_done, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tS = tmem_base, tDP = tmem_base + 128, tDV = tmem_base + 256, tDK = tmem_base + 384;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(kv_full, 2 * ATT_TILE_BYTES);
+      att_load_tile(sK, &tmQKV, kv_full, p.k_col0 + g * ATT_D, row0);
+      att_load_tile(sV, &tmQKV, kv_full, p.v_col0 + g * ATT_D, row0);
+      for (int it = 0; it < n_it; ++it) {
+        const int s = it & 1;
+        const int h = g * group + it / per_head;
+        const int qrow0 = seq_row0 + (i_kv + it % per_head) * ATT_TILE;
+        if (!mbar_wait(&qd_empty[s], ((it >> 1) & 1) ^ 1, ctx, ERR_WAIT_EMPTY)) break;
+        mbar_expect_tx(&qd_full[s], 2 * ATT_TILE_BYTES);
+        uint8_t* sQ = sQD + s * 2 * ATT_TILE_BYTES;
+        att_load_tile(sQ, &tmQKV, &qd_full[s], p.q_col0 + h * ATT_D, qrow0);
+        att_load_tile(sQ + ATT_TILE_BYTES, &tmDO, &qd_full[s], h * ATT_D, qrow0);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      bool ok = mbar_wait(kv_full, 0, ctx, ERR_WAIT_FULL);
+      for (int it = 0; ok && it < n_it; ++it) {
+        const int s = it & 1;
+        const uint32_t sQ = smem_u32(sQD + s * 2 * ATT_TILE_BYTES);
+        const uint32_t sDO = sQ + ATT_TILE_BYTES;
+        if (!mbar_wait(&qd_full[s], (it >> 1) & 1, ctx, ERR_WAIT_FULL) ||
+            !mbar_wait(sdp_empty, (it & 1) ^ 1, ctx, ERR_WAIT_TMEM_EMPTY)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        att_mma_kk(tS, sQ, smem_u32(sK), false);
+        att_mma_kk(tDP, sDO, smem_u32(sV), false);
+        tc_commit(sdp_full);
+        if (!mbar_wait(p_full, it & 1, ctx, ERR_WAIT_READY)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        att_mma_mnmn(tDV, smem_u32(sPD), sDO, it > 0);
+        tc_commit(dv_done);
+        if (!mbar_wait(ds_full, it & 1, ctx, ERR_WAIT_READY)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        att_mma_mnmn(tDK, smem_u32(sPD), sQ, it > 0);
+        tc_commit(&qd_empty[s]);
+        tc_commit(dk_done);
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    const int r = q * 32 + lane;  // query row inside the current query tile
+    const uint32_t lane_addr = uint32_t(q * 32) << 16;
+    bool ok = true;
+    for (int it = 0; it < n_it; ++it) {
+      const int h = g * group + it / per_head;
+      const int jq = i_kv + it % per_head;
+      const int qrow0 = seq_row0 + jq * ATT_TILE;
+      const int q_valid = min(ATT_TILE, seq_rows - jq * ATT_TILE);
+      const bool row_valid = r < q_valid;
+      const bool diag = (jq == i_kv);
+      const long long grow = (long long)qrow0 + r;
+      const float lse2 = row_valid ? p.lse[(long long)h * p.M_total + grow] * 1.4426950408889634f : 0.f;
+      const float dlt = row_valid ? p.delta[(long long)h * p.M_total + grow] : 0.f;
+      if (!mbar_wait(sdp_full, it & 1, ctx, ERR_WAIT_TMEM_FULL)) {
+        ok = false;
+        break;
+      }
+      if (it > 0 && !mbar_wait(dk_done, (it - 1) & 1, ctx, ERR_WAIT_MISC)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after_sync();
+      uint32_t pk[64];  // P of this row as packed bf16 pairs
+#pragma unroll
+      for (int cc = 0; cc < 4; ++cc) {
+        uint32_t sv[32];
+        tmem_ld_32x32b_x32(tS + lane_addr + cc * 32, sv);
+        tmem_ld_wait();
+        float pv[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int col = cc * 32 + i;
+          float x = exp2f(__uint_as_float(sv[i]) * p.scale_log2e - lse2);
+          if (!row_valid || (diag && col > r)) x = 0.f;
+          pv[i] = x;
+        }
+#pragma unroll
+        for (int i = 0; i < 16; ++i) pk[cc * 16 + i] = pack_bf16x2(pv[2 * i], pv[2 * i + 1]);
+        att_store_row_chunk(sPD, r, cc * 32, pv);
+      }
+      fence_proxy_async_smem();
+      mbar_arrive(p_full);
+      if (!mbar_wait(dv_done, it & 1, ctx, ERR_WAIT_MISC)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after_sync();
+#pragma unroll
+      for (int cc = 0; cc < 4; ++cc) {
+        uint32_t dv[32];
+        tmem_ld_32x32b_x32(tDP + lane_addr + cc * 32, dv);
+        tmem_ld_wait();
+        float ds[32];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const float2 pp = unpack_bf16x2(pk[cc * 16 + i]);
+          ds[2 * i] = pp.x * (__uint_as_float(dv[2 * i]) - dlt) * p.scale;
+          ds[2 * i + 1] = pp.y * (__uint_as_float(dv[2 * i + 1]) - dlt) * p.scale;
+        }
+        att_store_row_chunk(sPD, r, cc * 32, ds);
+      }
+      tc_fence_before_sync();
+      mbar_arrive(sdp_empty);
+      fence_proxy_async_smem();
+      mbar_arrive(ds_full);
+    }
+    if (ok && n_it > 0 && mbar_wait(dk_done, (n_it - 1) & 1, ctx, ERR_WAIT_MISC)) {
+      tc_fence_after_sync();
+      const long long grow = (long long)row0 + r;  // key row owned by this thread
+      __nv_bfloat16* krow = p.dqkv + grow * p.ld_qkv + p.k_col0 + g * ATT_D;
+      __nv_bfloat16* vrow = p.dqkv + grow * p.ld_qkv + p.v_col0 + g * ATT_D;
+#pragma unroll 1
+      for (int cc = 0; cc < 8; ++cc) {
+        uint32_t o[32];
+        const bool is_k = cc >= 4;
+        tmem_ld_32x32b_x32((is_k ? tDK : tDV) + lane_addr + (cc & 3) * 32, o);
+        tmem_ld_wait();
+        if (r < rows) {
+          __nv_bfloat16* dst = (is_k ? krow : vrow) + (cc & 3) * 32;
+#pragma unroll
+          for (int gq = 0; gq < 4; ++gq)
+            st_global_v4(dst + gq * 8,
+                         pack_bf16x2(__uint_as_float(o[gq * 8 + 0]), __uint_as_float(o[gq * 8 + 1])),
+                         pack_bf16x2(__uint_as_float(o[gq * 8 + 2]), __uint_as_float(o[gq * 8 + 3])),
+                         pack_bf16x2(__uint_as_float(o[gq * 8 + 4]), __uint_as_float(o[gq * 8 + 5])),
+                         pack_bf16x2(__uint_as_float(o[gq * 8 + 6]), __uint_as_float(o[gq * 8 + 7])));
+        }
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag != 0) {
+    const unsigned long long t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+}  // namespace lf
+
+using namespace lf;
+
+// out / d_out: [M, Hq*128]; qkv and dqkv: [M, ld_qkv]; lse, delta: fp32 [Hq, M]
+// (delta is scratch filled here).
+extern "C" int lf_attn_bwd(const void* qkv, const void* out, const void* d_out, void* dqkv,
+                           long long M, long long ld_qkv, int q_col0, int k_col0, int v_col0, int Hq,
+                           int Hkv, const void* tiles, int num_tiles, long long ldo, const float* lse,
+                           float* delta, float scale, int* err, void* stream) {
+  if (num_tiles <= 0) return 0;
+  if (Hq % Hkv != 0) return -1;
+  cudaStream_t st = (cudaStream_t)stream;
+  CUtensorMap tmQKV, tmDO;
+  int rc = make_tmap_2d_b16(&tmQKV, qkv, (uint64_t)M, (uint64_t)ld_qkv, (uint64_t)ld_qkv, 128, 64, true);
+  if (rc != 0) return -20 + rc;
+  rc = make_tmap_2d_b16(&tmDO, d_out, (uint64_t)M, (uint64_t)Hq * ATT_D, (uint64_t)ldo, 128, 64, true);
+  if (rc != 0) return -30 + rc;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(attn_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BWD_SMEM) != cudaSuccess ||
+        cudaFuncSetAttribute(attn_dkdv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BWD_SMEM) != cudaSuccess)
+      return -10;
+    configured = true;
+  }
+  {
+    const long long warps = M * Hq;
+    const int block = 256;
+    const long long grid = (warps * 32 + block - 1) / block;
+    attn_delta_kernel<<<(unsigned)grid, block, 0, st>>>((const __nv_bfloat16*)out,
+                                                         (const __nv_bfloat16*)d_out, delta, M, Hq, ldo);
+  }
+  AttnBwdParams p;
+  p.tiles = (const int4*)tiles;
+  p.num_tiles = num_tiles;
+  p.Hq = Hq;
+  p.Hkv = Hkv;
+  p.q_col0 = q_col0;
+  p.k_col0 = k_col0;
+  p.v_col0 = v_col0;
+  p.dqkv = (__nv_bfloat16*)dqkv;
+  p.ld_qkv = ld_qkv;
+  p.lse = lse;
+  p.delta = delta;
+  p.M_total = M;
+  p.scale = scale;
+  p.scale_log2e = scale * 1.4426950408889634f;
+  p.err = err;
+  attn_dq_kernel<<<dim3(num_tiles, Hq), 192, BWD_SMEM, st>>>(p, tmQKV, tmDO);
+  attn_dkdv_kernel<<<dim3(num_tiles, Hkv), 192, BWD_SMEM, st>>>(p, tmQKV, tmDO);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}

@@ -1,0 +1,291 @@
+// Causal, variable-length, grouped-query attention forward for head_dim 128 on sm_100a.
+// Replaces the FlashAttention-2 varlen call of the reference
+// (lorafusion/patch/patch_transformers.py:150-159).
+//
+// One CTA handles one 128-row query tile of one sequence for one query head:
+//   warp 0      TMA producer: Q once, then (K, V) tiles through a 2-stage ring
+//   warp 1      tcgen05.mma issuer: S = Q K^T into one of two TMEM buffers, O += P V
+//   warps 2..5  softmax: read S from TMEM (one row per thread), online max/sum with lazy
+//               rescaling of O (only when the running max grows by more than 2^8), write
+//               bf16 P into swizzled shared memory for the second MMA, final normalise.
+// Q/K/V are read straight out of the packed, RoPE-rotated QKV projection with one tensor
+// map; O is written token-major [M, Hq * 128]; the log-sum-exp is kept for the backward.
+#include <stdio.h>
+
+#include "../common/tensormap.h"
+#include "attn_common.cuh"
+
+namespace lf {
+
+struct AttnFwdParams {
+  const int4* tiles;
+  int num_tiles;
+  int Hq, Hkv;
+  int q_col0, k_col0, v_col0;
+  __nv_bfloat16* out;
+  long long ldo;
+  float* lse;
+  long long M_total;
+  float scale, scale_log2e;
+  int* err;
+};
+
+constexpr int FWD_SMEM = ATT_TILE_BYTES * (1 + 4 + 1) + 256 + 1024;
+
+__global__ void __launch_bounds__(192, 1)
+attn_fwd_kernel(const AttnFwdParams p, const __grid_constant__ CUtensorMap tm) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sKV = smem + ATT_TILE_BYTES;            // stage s: K at s*64K, V at s*64K + 32K
+  uint8_t* sP = smem + ATT_TILE_BYTES * 5;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + ATT_TILE_BYTES * 6);
+  uint64_t* q_full = bars;
+  uint64_t* kv_full = bars + 1;   // [2]
+  uint64_t* kv_empty = bars + 3;  // [2]
+  uint64_t* s_full = bars + 5;    // [2]
+  uint64_t* s_empty = bars + 7;   // [2]
+  uint64_t* p_full = bars + 9;
+  uint64_t* pv_done = bars + 10;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  AbortCtx ctx{p.err, abort_flag};
+  const int4 tile = p.tiles[blockIdx.x];
+  const int row0 = tile.x, rows = tile.y, seq_row0 = tile.z;
+  const int h = blockIdx.y;
+  const int g = h / (p.Hq / p.Hkv);
+  const int n_kv = (row0 - seq_row0) / ATT_TILE + 1;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&kv_full[i], 1);
+      mbar_init(&kv_empty[i], 1);
+      mbar_init(&s_full[i], 1);
+      mbar_init(&s_empty[i], 128);
+    }
+    mbar_init(p_full, 128);
+    mbar_init(pv_done, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tm);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tS[2] = {tmem_base, tmem_base + 128};
+  const uint32_t tO = tmem_base + 256;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(q_full, ATT_TILE_BYTES);
+      att_load_tile(sQ, &tm, q_full, p.q_col0 + h * ATT_D, row0);
+      for (int j = 0; j < n_kv; ++j) {
+        const int s = j & 1;
+        if (!mbar_wait(&kv_empty[s], ((j >> 1) & 1) ^ 1, ctx, ERR_WAIT_EMPTY)) break;
+        mbar_expect_tx(&kv_full[s], 2 * ATT_TILE_BYTES);
+        uint8_t* sK = sKV + s * 2 * ATT_TILE_BYTES;
+        att_load_tile(sK, &tm, &kv_full[s], p.k_col0 + g * ATT_D, seq_row0 + j * ATT_TILE);
+        att_load_tile(sK + ATT_TILE_BYTES, &tm, &kv_full[s], p.v_col0 + g * ATT_D,
+                      seq_row0 + j * ATT_TILE);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      bool ok = mbar_wait(q_full, 0, ctx, ERR_WAIT_FULL);
+      ok = ok && mbar_wait(&kv_full[0], 0, ctx, ERR_WAIT_FULL);
+      if (ok) {
+        tc_fence_after_sync();
+        att_mma_kk(tS[0], smem_u32(sQ), smem_u32(sKV), false);
+        tc_commit(&s_full[0]);
+      }
+      for (int j = 0; ok && j < n_kv; ++j) {
+        if (j + 1 < n_kv) {
+          const int s1 = (j + 1) & 1;
+          const uint32_t ph = ((j + 1) >> 1) & 1;
+          if (!mbar_wait(&kv_full[s1], ph, ctx, ERR_WAIT_FULL) ||
+              !mbar_wait(&s_empty[s1], ph ^ 1, ctx, ERR_WAIT_TMEM_EMPTY)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          att_mma_kk(tS[s1], smem_u32(sQ), smem_u32(sKV + s1 * 2 * ATT_TILE_BYTES), false);
+          tc_commit(&s_full[s1]);
+        }
+        if (!mbar_wait(p_full, j & 1, ctx, ERR_WAIT_READY)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        att_mma_kmn(tO, smem_u32(sP), smem_u32(sKV + (j & 1) * 2 * ATT_TILE_BYTES + ATT_TILE_BYTES),
+                    j > 0);
+        tc_commit(&kv_empty[j & 1]);
+        tc_commit(pv_done);
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    const int r = q * 32 + lane;  // row inside the tile
+    const uint32_t lane_addr = uint32_t(q * 32) << 16;
+    float m_ref = -INFINITY, l = 0.f;
+    const float c = p.scale_log2e;
+    bool ok = true;
+    for (int j = 0; j < n_kv; ++j) {
+      const int b = j & 1;
+      if (!mbar_wait(&s_full[b], (j >> 1) & 1, ctx, ERR_WAIT_TMEM_FULL)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after_sync();
+      float s[128];
+#pragma unroll
+      for (int cc = 0; cc < 4; ++cc) {
+        uint32_t(&dst)[32] = *reinterpret_cast<uint32_t(*)[32]>(&s[cc * 32]);
+        tmem_ld_32x32b_x32(tS[b] + lane_addr + cc * 32, dst);
+      }
+      tmem_ld_wait();
+      tc_fence_before_sync();
+      mbar_arrive(&s_empty[b]);
+      if (j == n_kv - 1) {
+#pragma unroll
+        for (int col = 0; col < 128; ++col)
+          if (col > r) s[col] = -INFINITY;
+      }
+      float mx = s[0];
+#pragma unroll
+      for (int col = 1; col < 128; ++col) mx = fmaxf(mx, s[col]);
+      float alpha = 1.f;
+      bool need = false;
+      if (j == 0) {
+        m_ref = mx;
+      } else {
+        need = (mx - m_ref) * c > 8.f;
+        if (need) {
+          alpha = exp2f((m_ref - mx) * c);
+          m_ref = mx;
+          l *= alpha;
+        }
+      }
+      const bool warp_need = __any_sync(0xffffffffu, need);
+      const float mc = m_ref * c;
+      float sum = 0.f;
+#pragma unroll
+      for (int col = 0; col < 128; ++col) {
+        s[col] = exp2f(s[col] * c - mc);
+        sum += s[col];
+      }
+      l += sum;
+      if (j > 0) {
+        if (!mbar_wait(pv_done, (j - 1) & 1, ctx, ERR_WAIT_MISC)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+      }
+#pragma unroll
+      for (int cc = 0; cc < 4; ++cc) {
+        float(&src)[32] = *reinterpret_cast<float(*)[32]>(&s[cc * 32]);
+        att_store_row_chunk(sP, r, cc * 32, src);
+      }
+      if (warp_need) {
+#pragma unroll 1
+        for (int cc = 0; cc < 4; ++cc) {
+          uint32_t o[32];
+          tmem_ld_32x32b_x32(tO + lane_addr + cc * 32, o);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tmem_st_32x32b_x32(tO + lane_addr + cc * 32, o);
+        }
+        tmem_st_wait();
+      }
+      fence_proxy_async_smem();
+      tc_fence_before_sync();
+      mbar_arrive(p_full);
+    }
+    if (ok && mbar_wait(pv_done, (n_kv - 1) & 1, ctx, ERR_WAIT_MISC)) {
+      tc_fence_after_sync();
+      const float inv_l = 1.f / l;
+      const long long grow = (long long)row0 + r;
+      __nv_bfloat16* orow = p.out + grow * p.ldo + h * ATT_D;
+#pragma unroll 1
+      for (int cc = 0; cc < 4; ++cc) {
+        uint32_t o[32];
+        tmem_ld_32x32b_x32(tO + lane_addr + cc * 32, o);
+        tmem_ld_wait();
+        if (r < rows) {
+#pragma unroll
+          for (int gq = 0; gq < 4; ++gq) {
+            st_global_v4(orow + cc * 32 + gq * 8,
+                         pack_bf16x2(__uint_as_float(o[gq * 8 + 0]) * inv_l, __uint_as_float(o[gq * 8 + 1]) * inv_l),
+                         pack_bf16x2(__uint_as_float(o[gq * 8 + 2]) * inv_l, __uint_as_float(o[gq * 8 + 3]) * inv_l),
+                         pack_bf16x2(__uint_as_float(o[gq * 8 + 4]) * inv_l, __uint_as_float(o[gq * 8 + 5]) * inv_l),
+                         pack_bf16x2(__uint_as_float(o[gq * 8 + 6]) * inv_l, __uint_as_float(o[gq * 8 + 7]) * inv_l));
+          }
+        }
+      }
+      if (r < rows) p.lse[(long long)h * p.M_total + grow] = m_ref * p.scale + __logf(l);
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag != 0) {
+    const unsigned long long t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+}  // namespace lf
+
+using namespace lf;
+
+// qkv: packed [M, ld_qkv] bf16 (q heads, then k heads, then v heads at the given column
+// offsets); tiles: device int32 [num_tiles, 4]; out [M, Hq*128]; lse fp32 [Hq, M].
+extern "C" int lf_attn_fwd(const void* qkv, long long M, long long ld_qkv, int q_col0, int k_col0,
+                           int v_col0, int Hq, int Hkv, const void* tiles, int num_tiles, void* out,
+                           long long ldo, float* lse, float scale, int* err, void* stream) {
+  if (num_tiles <= 0) return 0;
+  if (Hq % Hkv != 0 || (q_col0 | k_col0 | v_col0) % 64 != 0) return -1;
+  CUtensorMap tm;
+  int rc = make_tmap_2d_b16(&tm, qkv, (uint64_t)M, (uint64_t)ld_qkv, (uint64_t)ld_qkv, 128, 64, true);
+  if (rc != 0) return -20 + rc;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             FWD_SMEM) != cudaSuccess)
+      return -10;
+    configured = true;
+  }
+  AttnFwdParams p;
+  p.tiles = (const int4*)tiles;
+  p.num_tiles = num_tiles;
+  p.Hq = Hq;
+  p.Hkv = Hkv;
+  p.q_col0 = q_col0;
+  p.k_col0 = k_col0;
+  p.v_col0 = v_col0;
+  p.out = (__nv_bfloat16*)out;
+  p.ldo = ldo;
+  p.lse = lse;
+  p.M_total = M;
+  p.scale = scale;
+  p.scale_log2e = scale * 1.4426950408889634f;
+  p.err = err;
+  dim3 grid(num_tiles, Hq);
+  attn_fwd_kernel<<<grid, 192, FWD_SMEM, (cudaStream_t)stream>>>(p, tm);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}

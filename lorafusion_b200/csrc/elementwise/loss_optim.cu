@@ -1,0 +1,211 @@
+// Cross-entropy over a chunk of logits (loss + in-place gradient) and the multi-tensor
+// Adam step for LoRA adapters.
+//
+// Cross-entropy: the lm_head GEMM is run chunk by chunk over tokens so that the
+// [tokens, vocab] logits never exist in full; this kernel turns one bf16 logits chunk into
+// per-token losses and overwrites it with d(loss)/d(logits), which the next GEMM multiplies
+// by the lm_head weight.  (The reference goes through HF's lm_head + torch cross-entropy,
+// lorafusion/pipeline_parallel/pipe_module.py:218-221.)
+//
+// Adam: one launch updates every LoRA tensor of one adapter.  Tensors are described by a
+// chunk table (offset, length) into parallel arenas: fp32 gradient, fp32 master weight,
+// fp32 m, fp32 v and the bf16 working copy the GEMM kernels read.  The gradient arena is
+// zeroed as it is consumed.  (The reference uses torch.optim.AdamW(fused=True) per adapter,
+// benchmarks_paper/bench_multi_gpu.py:225-230.)
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace lf {
+
+constexpr int CE_THREADS = 512;
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ float warp_sum2(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// One CTA per token.  Pass 1: online max / sum-exp.  Pass 2: write the gradient in place.
+// labels < 0 are ignored (loss 0, gradient 0).  grad_scale multiplies the gradient
+// (1 / number of valid tokens for a mean loss).
+__global__ void __launch_bounds__(CE_THREADS)
+cross_entropy_kernel(__nv_bfloat16* __restrict__ logits, const int* __restrict__ labels,
+                     float* __restrict__ loss_out, int V, long long ld, float grad_scale) {
+  __shared__ float red_m[CE_THREADS / 32];
+  __shared__ float red_s[CE_THREADS / 32];
+  const long long row = blockIdx.x;
+  __nv_bfloat16* lr = logits + row * ld;
+  const int label = labels[row];
+  const int nvec = V / 8;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (label < 0) {
+    const uint4 z = make_uint4(0, 0, 0, 0);
+    for (int c = threadIdx.x; c < nvec; c += CE_THREADS) reinterpret_cast<uint4*>(lr)[c] = z;
+    for (int c = nvec * 8 + threadIdx.x; c < V; c += CE_THREADS) lr[c] = __float2bfloat16(0.f);
+    if (threadIdx.x == 0) loss_out[row] = 0.f;
+    return;
+  }
+
+  float m = -INFINITY, s = 0.f;
+  for (int c = threadIdx.x; c < nvec; c += CE_THREADS) {
+    uint4 raw = reinterpret_cast<const uint4*>(lr)[c];
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+    float f[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 t = __bfloat1622float2(h[j]);
+      f[2 * j] = t.x;
+      f[2 * j + 1] = t.y;
+    }
+    float lm = f[0];
+#pragma unroll
+    for (int j = 1; j < 8; ++j) lm = fmaxf(lm, f[j]);
+    if (lm > m) {
+      s *= __expf(m - lm);
+      m = lm;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) s += __expf(f[j] - m);
+  }
+  for (int c = nvec * 8 + threadIdx.x; c < V; c += CE_THREADS) {
+    const float f = __bfloat162float(lr[c]);
+    if (f > m) {
+      s *= __expf(m - f);
+      m = f;
+    }
+    s += __expf(f - m);
+  }
+  // block reduce (max, then rescaled sums)
+  float wm = warp_max(m);
+  s *= __expf(m - wm);
+  s = warp_sum2(s);
+  if (lane == 0) {
+    red_m[warp] = wm;
+    red_s[warp] = s;
+  }
+  __syncthreads();
+  float bm = red_m[0];
+  for (int i = 1; i < CE_THREADS / 32; ++i) bm = fmaxf(bm, red_m[i]);
+  float bs = 0.f;
+  for (int i = 0; i < CE_THREADS / 32; ++i) bs += red_s[i] * __expf(red_m[i] - bm);
+  const float lse = bm + __logf(bs);
+  const float inv_sum = 1.f / bs;
+  const float label_logit = __bfloat162float(lr[label]);
+  __syncthreads();  // everyone has read lr[label] before it is overwritten
+  if (threadIdx.x == 0) loss_out[row] = lse - label_logit;
+
+  for (int c = threadIdx.x; c < nvec; c += CE_THREADS) {
+    uint4 raw = reinterpret_cast<const uint4*>(lr)[c];
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 t = __bfloat1622float2(h[j]);
+      const int col = c * 8 + 2 * j;
+      float g0 = __expf(t.x - bm) * inv_sum - (col == label ? 1.f : 0.f);
+      float g1 = __expf(t.y - bm) * inv_sum - (col + 1 == label ? 1.f : 0.f);
+      h[j] = __floats2bfloat162_rn(g0 * grad_scale, g1 * grad_scale);
+    }
+    reinterpret_cast<uint4*>(lr)[c] = raw;
+  }
+  for (int c = nvec * 8 + threadIdx.x; c < V; c += CE_THREADS) {
+    const float f = __bfloat162float(lr[c]);
+    const float g = __expf(f - bm) * inv_sum - (c == label ? 1.f : 0.f);
+    lr[c] = __float2bfloat16(g * grad_scale);
+  }
+}
+
+// ---------------------------------------------------------------------------------
+// Adam / AdamW over a chunk table.
+// ---------------------------------------------------------------------------------
+// A chunk is a 2-D region of `rows` x `ld` elements starting at `offset` in every arena.
+// Its gradient is always cleared; only columns [col0, col0 + cols) of each row are
+// trainable (block-diagonal B matrices of merged projections keep their off-diagonal
+// blocks at zero this way).  A flat tensor is rows = 1, ld = cols = length, col0 = 0.
+struct AdamChunk {
+  long long offset;
+  long long rows;
+  long long ld;
+  long long col0;
+  long long cols;
+};
+
+struct AdamHyper {
+  float lr, beta1, beta2, eps, weight_decay;
+  float bias_c1, bias_c2;  // 1 - beta1^t, 1 - beta2^t
+  float grad_scale;        // multiplies the accumulated gradient before the update
+};
+
+__global__ void __launch_bounds__(256)
+adam_chunks_kernel(const AdamChunk* __restrict__ chunks, int num_chunks, float* __restrict__ grad,
+                   float* __restrict__ master, float* __restrict__ m, float* __restrict__ v,
+                   __nv_bfloat16* __restrict__ work, AdamHyper h, int blocks_per_chunk) {
+  const int chunk = blockIdx.x / blocks_per_chunk;
+  const int sub = blockIdx.x % blocks_per_chunk;
+  if (chunk >= num_chunks) return;
+  const AdamChunk c = chunks[chunk];
+  const float inv_c1 = 1.f / h.bias_c1;
+  const float inv_sqrt_c2 = rsqrtf(h.bias_c2);
+  const long long total = c.rows * c.ld;
+  for (long long i = sub * 256LL + threadIdx.x; i < total; i += blocks_per_chunk * 256LL) {
+    const long long e = c.offset + i;
+    const float g = grad[e] * h.grad_scale;
+    grad[e] = 0.f;
+    const long long col = i % c.ld;
+    if (col < c.col0 || col >= c.col0 + c.cols) continue;
+    float w = master[e];
+    const float mi = h.beta1 * m[e] + (1.f - h.beta1) * g;
+    const float vi = h.beta2 * v[e] + (1.f - h.beta2) * g * g;
+    m[e] = mi;
+    v[e] = vi;
+    w -= h.lr * h.weight_decay * w;
+    w -= h.lr * (mi * inv_c1) / (sqrtf(vi) * inv_sqrt_c2 + h.eps);
+    master[e] = w;
+    work[e] = __float2bfloat16(w);
+  }
+}
+
+}  // namespace lf
+
+using namespace lf;
+
+extern "C" {
+
+int lf_cross_entropy(void* logits, const int* labels, float* loss, long long M, int V,
+                     long long ld, float grad_scale, void* stream) {
+  if (M == 0) return 0;
+  if (ld % 8 != 0) return -1;
+  cross_entropy_kernel<<<(unsigned)M, CE_THREADS, 0, (cudaStream_t)stream>>>(
+      (__nv_bfloat16*)logits, labels, loss, V, ld, grad_scale);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+// chunks: device array of AdamChunk {int64 offset, rows, ld, col0, cols}
+int lf_adam_chunks(const void* chunks, int num_chunks, float* grad, float* master, float* m,
+                   float* v, void* work, float lr, float beta1, float beta2, float eps,
+                   float weight_decay, int step, float grad_scale, void* stream) {
+  if (num_chunks <= 0) return 0;
+  AdamHyper h;
+  h.lr = lr;
+  h.beta1 = beta1;
+  h.beta2 = beta2;
+  h.eps = eps;
+  h.weight_decay = weight_decay;
+  h.bias_c1 = 1.f - powf(beta1, (float)step);
+  h.bias_c2 = 1.f - powf(beta2, (float)step);
+  h.grad_scale = grad_scale;
+  int bpc = (148 * 8 + num_chunks - 1) / num_chunks;
+  if (bpc < 1) bpc = 1;
+  if (bpc > 64) bpc = 64;
+  adam_chunks_kernel<<<num_chunks * bpc, 256, 0, (cudaStream_t)stream>>>(
+      (const AdamChunk*)chunks, num_chunks, grad, master, m, v, (__nv_bfloat16*)work, h, bpc);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+}  // extern "C"

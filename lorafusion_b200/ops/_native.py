@@ -100,9 +100,40 @@ EPI_F32_ACCUM = 2
 EPI_BF16_ADAPTER_SCALE = 3
 
 
+_VP, _LL, _I, _F = C.c_void_p, C.c_longlong, C.c_int, C.c_float
+
+_SIGNATURES = {
+    "lf_rmsnorm_fwd": [_VP, _VP, _VP, _VP, _VP, _VP, _LL, _I, _F, _VP],
+    "lf_rmsnorm_bwd": [_VP, _VP, _VP, _VP, _VP, _VP, _LL, _I, _VP],
+    "lf_rope_inplace": [_VP, _VP, _VP, _VP, _I, _I, _I, _I, _I, _VP],
+    "lf_swiglu_fwd": [_VP, _VP, _LL, _I, _VP],
+    "lf_swiglu_bwd": [_VP, _VP, _VP, _LL, _I, _VP],
+    "lf_embedding": [_VP, _VP, _VP, _LL, _I, _I, _VP],
+    "lf_add": [_VP, _VP, _VP, _LL, _VP],
+    "lf_cross_entropy": [_VP, _VP, _VP, _LL, _I, _LL, _F, _VP],
+    "lf_adam_chunks": [_VP, _I, _VP, _VP, _VP, _VP, _VP, _F, _F, _F, _F, _F, _I, _F, _VP],
+    "lf_nf4_quantize": [_VP, _VP, _VP, _LL, _VP],
+    "lf_nf4_dequantize": [_VP, _VP, _VP, _VP, _VP, _F, _VP, _LL, _VP],
+    "lf_attn_fwd": [_VP, _LL, _LL, _I, _I, _I, _I, _I, _VP, _I, _VP, _LL, _VP, _F, _VP, _VP],
+    "lf_attn_bwd": [_VP, _VP, _VP, _VP, _LL, _LL, _I, _I, _I, _I, _I, _VP, _I, _LL, _VP, _VP,
+                    _F, _VP, _VP],
+}
+
+
 def _declare_cuda(lib: C.CDLL) -> None:
     lib.lf_gemm.argtypes = [C.POINTER(LfGemmArgs)]
     lib.lf_gemm.restype = C.c_int
+    for name, sig in _SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.argtypes = sig
+        fn.restype = C.c_int
+
+
+def call(name: str, *args) -> None:
+    """Call an ``int``-returning C entry point and raise on a non-zero status."""
+    rc = getattr(cuda_lib(), name)(*args)
+    if rc != 0:
+        raise RuntimeError(f"{name} failed with code {rc}")
 
 
 # ----------------------------------------------------------------------------------------

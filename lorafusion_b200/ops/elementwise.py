@@ -1,0 +1,100 @@
+"""Launchers for the memory-bound decoder kernels (``csrc/elementwise``): RMSNorm with fused
+residual add, in-place rotary embedding, SwiGLU, embedding gather, chunked cross-entropy and
+the multi-tensor Adam step.  All activations are bf16 ``[tokens, features]``."""
+
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import _native as nv
+
+
+def _p(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def rmsnorm_fwd(x: torch.Tensor, w: torch.Tensor, eps: float, res: Optional[torch.Tensor] = None,
+                want_rstd: bool = True):
+    """``h = x (+ res); y = h * rsqrt(mean(h^2) + eps) * w``.  Returns ``(y, h, rstd)``;
+    ``h`` is ``x`` itself when there is no residual."""
+    M, H = x.shape
+    y = torch.empty_like(x)
+    h = torch.empty_like(x) if res is not None else x
+    rstd = torch.empty(M, dtype=torch.float32, device=x.device) if want_rstd else None
+    nv.call("lf_rmsnorm_fwd", x.data_ptr(), _p(res), w.data_ptr(), y.data_ptr(),
+            h.data_ptr() if res is not None else None, _p(rstd), M, H, eps,
+            nv.current_stream_ptr())
+    return y, h, rstd
+
+
+def rmsnorm_bwd(dy: torch.Tensor, h: torch.Tensor, w: torch.Tensor, rstd: torch.Tensor,
+                dres: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Gradient w.r.t. the normalised input (the frozen weight gets none), plus ``dres``."""
+    M, H = h.shape
+    dx = torch.empty_like(h)
+    nv.call("lf_rmsnorm_bwd", dy.data_ptr(), h.data_ptr(), w.data_ptr(), rstd.data_ptr(), _p(dres),
+            dx.data_ptr(), M, H, nv.current_stream_ptr())
+    return dx
+
+
+def rope_inplace(qkv: torch.Tensor, pos: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor,
+                 n_rot_heads: int, head_dim: int, backward: bool = False) -> None:
+    """Rotate the first ``n_rot_heads`` heads (q then k) of the packed projection in place."""
+    M = qkv.shape[0]
+    nv.call("lf_rope_inplace", qkv.data_ptr(), pos.data_ptr(), cos.data_ptr(), sin.data_ptr(), M,
+            n_rot_heads, head_dim, qkv.stride(0), int(backward), nv.current_stream_ptr())
+
+
+def swiglu_fwd(gu: torch.Tensor) -> torch.Tensor:
+    M, I2 = gu.shape
+    out = torch.empty((M, I2 // 2), dtype=gu.dtype, device=gu.device)
+    nv.call("lf_swiglu_fwd", gu.data_ptr(), out.data_ptr(), M, I2 // 2, nv.current_stream_ptr())
+    return out
+
+
+def swiglu_bwd(dout: torch.Tensor, gu: torch.Tensor) -> torch.Tensor:
+    M, I2 = gu.shape
+    dgu = torch.empty_like(gu)
+    nv.call("lf_swiglu_bwd", dout.data_ptr(), gu.data_ptr(), dgu.data_ptr(), M, I2 // 2,
+            nv.current_stream_ptr())
+    return dgu
+
+
+def embedding(ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
+    M = ids.numel()
+    V, H = table.shape
+    out = torch.empty((M, H), dtype=table.dtype, device=table.device)
+    nv.call("lf_embedding", ids.data_ptr(), table.data_ptr(), out.data_ptr(), M, H, V,
+            nv.current_stream_ptr())
+    return out
+
+
+def add(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    out = torch.empty_like(a)
+    nv.call("lf_add", a.data_ptr(), b.data_ptr(), out.data_ptr(), a.numel(),
+            nv.current_stream_ptr())
+    return out
+
+
+def cross_entropy_inplace(logits: torch.Tensor, labels: torch.Tensor, grad_scale: float,
+                          loss_out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Per-token loss of a logits chunk; ``logits`` is overwritten with
+    ``grad_scale * d loss / d logits``.  ``labels < 0`` are ignored."""
+    M, V = logits.shape
+    if loss_out is None:
+        loss_out = torch.empty(M, dtype=torch.float32, device=logits.device)
+    nv.call("lf_cross_entropy", logits.data_ptr(), labels.data_ptr(), loss_out.data_ptr(), M, V,
+            logits.stride(0), grad_scale, nv.current_stream_ptr())
+    return loss_out
+
+
+def adam_chunks(chunks: torch.Tensor, grad: torch.Tensor, master: torch.Tensor, m: torch.Tensor,
+                v: torch.Tensor, work: torch.Tensor, *, lr: float, beta1: float, beta2: float,
+                eps: float, weight_decay: float, step: int, grad_scale: float = 1.0) -> None:
+    """AdamW over the regions listed in ``chunks`` (int64 ``[n, 5]``: offset, rows, ld, col0,
+    cols) of the parallel arenas; consumes and clears the gradient."""
+    nv.call("lf_adam_chunks", chunks.data_ptr(), chunks.shape[0], grad.data_ptr(),
+            master.data_ptr(), m.data_ptr(), v.data_ptr(), work.data_ptr(), lr, beta1, beta2, eps,
+            weight_decay, step, grad_scale, nv.current_stream_ptr())
