@@ -84,7 +84,7 @@ cross_entropy_kernel(__nv_bfloat16* __restrict__ logits, const int* __restrict__
   }
   // block reduce (max, then rescaled sums)
   float wm = warp_max(m);
-  s *= __expf(m - wm);
+  s = (m == -INFINITY) ? 0.f : s * __expf(m - wm);  // threads that saw no element
   s = warp_sum2(s);
   if (lane == 0) {
     red_m[warp] = wm;
@@ -94,7 +94,8 @@ cross_entropy_kernel(__nv_bfloat16* __restrict__ logits, const int* __restrict__
   float bm = red_m[0];
   for (int i = 1; i < CE_THREADS / 32; ++i) bm = fmaxf(bm, red_m[i]);
   float bs = 0.f;
-  for (int i = 0; i < CE_THREADS / 32; ++i) bs += red_s[i] * __expf(red_m[i] - bm);
+  for (int i = 0; i < CE_THREADS / 32; ++i)
+    bs += (red_m[i] == -INFINITY) ? 0.f : red_s[i] * __expf(red_m[i] - bm);
   const float lse = bm + __logf(bs);
   const float inv_sum = 1.f / bs;
   const float label_logit = __bfloat162float(lr[label]);

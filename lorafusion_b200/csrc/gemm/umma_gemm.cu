@@ -89,7 +89,7 @@ struct SmemPlan {
   static constexpr int A_BYTES = BM * BK * 2;
   static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr int STAGES = (BN == 256) ? 4 : (BN == 192 ? 5 : (BN == 128 ? 6 : 8));
   static constexpr int BAR_BYTES = 512;
   static constexpr int TOTAL = STAGES * STAGE_BYTES + BAR_BYTES + 1024;  // + alignment slack
 };
@@ -498,7 +498,7 @@ static int sm_count() {
 extern "C" int lf_gemm(const LfGemmArgs* a) {
   using namespace lf;
   if (a == nullptr || a->a == nullptr || a->b == nullptr || a->out == nullptr) return -1;
-  if (a->bn != 64 && a->bn != 128 && a->bn != 256) return -2;
+  if (a->bn != 64 && a->bn != 128 && a->bn != 192 && a->bn != 256) return -2;
   if (a->K2 % BK != 0) return -3;
   const int BN = a->bn;
 
@@ -576,14 +576,20 @@ extern "C" int lf_gemm(const LfGemmArgs* a) {
     LF_CASE(128, 1, 0, 1, 1, LF_EPI_BF16, 0)
     // dX with the dropout mask regenerated in the epilogue
     LF_CASE(128, 2, 0, 1, 1, LF_EPI_BF16_DROPMIX, 0)
-    // S' = alpha * dropout(X) A^T
-    LF_CASE(64, 1, 0, 0, 0, LF_EPI_BF16_ADAPTER_SCALE, 0)
-    LF_CASE(64, 1, 0, 0, 0, LF_EPI_BF16_ADAPTER_SCALE, 1)
-    // dS = alpha * dY B
-    LF_CASE(64, 1, 0, 1, 0, LF_EPI_BF16_ADAPTER_SCALE, 0)
-    // dB += dY^T S'   /   dA += dS^T dropout(X)
-    LF_CASE(64, 1, 1, 1, 0, LF_EPI_F32_ACCUM, 0)
-    LF_CASE(64, 1, 1, 1, 0, LF_EPI_F32_ACCUM, 1)
+#define LF_SKINNY(bn)                                                \
+    /* S' = alpha * dropout(X) A^T */                                  \
+    LF_CASE(bn, 1, 0, 0, 0, LF_EPI_BF16_ADAPTER_SCALE, 0)              \
+    LF_CASE(bn, 1, 0, 0, 0, LF_EPI_BF16_ADAPTER_SCALE, 1)              \
+    /* dS = alpha * dY B */                                            \
+    LF_CASE(bn, 1, 0, 1, 0, LF_EPI_BF16_ADAPTER_SCALE, 0)              \
+    /* dB += dY^T S'   and   dA += dS^T dropout(X) */                  \
+    LF_CASE(bn, 1, 1, 1, 0, LF_EPI_F32_ACCUM, 0)                       \
+    LF_CASE(bn, 1, 1, 1, 0, LF_EPI_F32_ACCUM, 1)
+    LF_SKINNY(64)
+    LF_SKINNY(128)
+    LF_SKINNY(192)
+    LF_SKINNY(256)
+#undef LF_SKINNY
     default:
       fprintf(stderr, "lf_gemm: no kernel variant for key 0x%x\n", key);
       return -5;

@@ -22,7 +22,7 @@ Conventions
 * Tokens are packed ``[M, features]``; every 128-row tile belongs to one adapter
   (``tile_adapter[m_tile]``, ``-1`` = no adapter) -- the solver pads each adapter's
   segment to a multiple of 128 tokens.
-* Adapters are stacked and rank-padded to ``R`` (a multiple of 64) with zeros:
+* Adapters are stacked and rank-padded to ``R`` (64, 128, 192 or 256) with zeros:
   ``A_all [n, R, K]``, ``B_all [n, N, R]``; the kernels index them by adapter id, so there
   are no per-call pointer tables and no limit of four adapters.
 * ``alpha`` (= lora_alpha / r) is applied to the fp32 accumulator when ``S'`` and ``dS``
@@ -42,6 +42,7 @@ from .gemm import launch_gemm
 from .philox import dropout_threshold
 
 RANK_PAD = 64
+RANK_PADS = (64, 128, 192, 256)  # stacked-rank widths the skinny kernels are built for
 TILE_M = 128
 
 
@@ -85,6 +86,7 @@ class SegmentTable:
 
     segments: Sequence[tuple[int, int, int]]
     device: torch.device
+    total_rows: Optional[int] = None
     _cache: dict = field(default_factory=dict)
 
     def tiles_for(self, features: int) -> torch.Tensor:
@@ -99,10 +101,11 @@ class SegmentTable:
                 if adapter in seen:
                     raise ValueError("an adapter may own only one token segment per microbatch")
                 seen.add(adapter)
-                if start % TILE_M or end % TILE_M:
+                last = self.total_rows is not None and end >= self.total_rows
+                if start % TILE_M or (end % TILE_M and not last):
                     raise ValueError("segment bounds must be multiples of 128 tokens")
                 for f0 in range(0, features, TILE_M):
-                    rows.append((f0, start, (end - start) // 64, adapter))
+                    rows.append((f0, start, (end - start + 63) // 64, adapter))
             t = torch.tensor(rows, dtype=torch.int32).reshape(-1, 4).to(self.device)
             self._cache[features] = t
         return t
@@ -118,10 +121,10 @@ def lora_down(x: torch.Tensor, a_all: torch.Tensor, *, tile_adapter: Optional[to
     """``S'[M, R] = alpha_a * dropout(x)[M, K] @ A_a[R, K]^T`` with the adapter of each tile."""
     M, K = x.shape
     n, R, K2 = a_all.shape
-    assert K2 == K and R == RANK_PAD, "rank padding other than 64 is not built yet"
+    assert K2 == K and R in RANK_PADS
     if out is None:
         out = torch.empty((M, R), dtype=torch.bfloat16, device=x.device)
-    launch_gemm(a=x, b=_flat2d(a_all), out=out, M=M, N=R, K=K, bn=64,
+    launch_gemm(a=x, b=_flat2d(a_all), out=out, M=M, N=R, K=K, bn=R,
                 epi=nv.EPI_BF16_ADAPTER_SCALE, mask_a=dropout.active,
                 tile_adapter=tile_adapter, b_adapter_rows=R, adapter_scale=adapter_scale,
                 scale=scale, **dropout.kwargs())
@@ -152,10 +155,10 @@ def lora_ds(dy: torch.Tensor, b_all: torch.Tensor, *, tile_adapter: Optional[tor
     """``dS[M, R] = alpha_a * dy[M, N] @ B_a[N, R]``."""
     M, N = dy.shape
     n, N2, R = b_all.shape
-    assert N2 == N and R == RANK_PAD
+    assert N2 == N and R in RANK_PADS
     if out is None:
         out = torch.empty((M, R), dtype=torch.bfloat16, device=dy.device)
-    launch_gemm(a=dy, b=_flat2d(b_all), out=out, M=M, N=R, K=N, b_mn=True, bn=64,
+    launch_gemm(a=dy, b=_flat2d(b_all), out=out, M=M, N=R, K=N, b_mn=True, bn=R,
                 epi=nv.EPI_BF16_ADAPTER_SCALE, tile_adapter=tile_adapter, b_adapter_rows=N,
                 adapter_scale=adapter_scale, scale=scale)
     return out
@@ -169,7 +172,7 @@ def lora_db(dy: torch.Tensor, s: torch.Tensor, segs: SegmentTable, db_all: torch
     tiles = segs.tiles_for(N)
     if tiles.shape[0] == 0:
         return
-    launch_gemm(a=dy, b=s, out=db_all, M=N, N=R, K=M, a_mn=True, b_mn=True, bn=64,
+    launch_gemm(a=dy, b=s, out=db_all, M=N, N=R, K=M, a_mn=True, b_mn=True, bn=R,
                 epi=nv.EPI_F32_ACCUM, seg_tiles=tiles, ldo=R, out_adapter_stride=N * R)
 
 
@@ -182,7 +185,7 @@ def lora_da(x: torch.Tensor, ds: torch.Tensor, segs: SegmentTable, da_all: torch
     tiles = segs.tiles_for(K)
     if tiles.shape[0] == 0:
         return
-    launch_gemm(a=x, b=ds, out=da_all, M=K, N=R, K=M, a_mn=True, b_mn=True, bn=64,
+    launch_gemm(a=x, b=ds, out=da_all, M=K, N=R, K=M, a_mn=True, b_mn=True, bn=R,
                 epi=nv.EPI_F32_ACCUM, mask_a=dropout.active, seg_tiles=tiles, ldo=K,
                 out_transposed=True, out_adapter_stride=R * K, **dropout.kwargs())
 
