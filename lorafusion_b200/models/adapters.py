@@ -1,0 +1,227 @@
+"""Storage of every LoRA adapter of a model (or pipeline stage) in flat arenas.
+
+The reference keeps adapters as PEFT modules named ``lora_{i}`` and, for multi-LoRA data
+parallelism, wraps each adapter's parameters in a fake ``nn.Module`` with its own Megatron
+DDP grad buffer and AdamW (``benchmarks_paper/bench_multi_gpu.py:162-203,276-287``).  Here
+all adapters live in five parallel 1-D arenas with identical element offsets:
+
+    work (bf16, read by the GEMM kernels) | master | m | v | grad   (fp32)
+
+Per merged projection the arena holds stacks ``A [n, R, K]`` and ``B [n, N, R]``
+(``ops/lora.py``).  Merged projections (q|k|v and gate|up) keep one LoRA per sub-projection:
+adapter ``i`` with rank ``r_i`` uses rows ``[j * slot, j * slot + r_i)`` of ``A`` for
+sub-projection ``j`` and the matching columns of the rows of ``B`` that belong to ``j``
+(block-diagonal ``B``); everything else stays zero and is excluded from the optimizer through
+the chunk table (``AdamChunk`` regions: offset, rows, ld, col0, cols).
+
+One chunk table per adapter lets a single kernel launch apply Adam to -- or a single fused
+kernel reduce across data-parallel ranks -- all tensors of that adapter.
+"""
+
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+from typing import Optional, Sequence
+
+import torch
+
+from ..ops.lora import LoRAStack, rank_pad
+from .config import AdapterSpec, ModelConfig
+
+# merged projection -> (sub-projection names, output sizes) resolved per model
+PROJECTIONS = ("qkv", "o", "gate_up", "down")
+
+
+def projection_layout(cfg: ModelConfig) -> dict[str, dict]:
+    h, i = cfg.hidden_size, cfg.intermediate_size
+    return {
+        "qkv": dict(K=h, subs=[("q_proj", cfg.q_size), ("k_proj", cfg.kv_size), ("v_proj", cfg.kv_size)]),
+        "o": dict(K=cfg.q_size, subs=[("o_proj", h)]),
+        "gate_up": dict(K=h, subs=[("gate_proj", i), ("up_proj", i)]),
+        "down": dict(K=i, subs=[("down_proj", h)]),
+    }
+
+
+@dataclass
+class StackView:
+    """Location of one (layer, projection) stack inside the arenas."""
+
+    layer: int
+    proj: str
+    K: int
+    N: int
+    R: int
+    slot: int
+    subs: list  # [(name, out_size)]
+    a_offset: int
+    b_offset: int
+    stack: Optional[LoRAStack] = None
+
+
+class LoRAArena:
+    def __init__(self, cfg: ModelConfig, adapters: Sequence[AdapterSpec], layers: Sequence[int],
+                 device, *, init_b_std: float = 0.0, seed: int = 0, with_optimizer_state: bool = True):
+        self.cfg = cfg
+        self.adapters = list(adapters)
+        self.layers = list(layers)
+        self.device = torch.device(device)
+        n = len(self.adapters)
+        self.num_adapters = n
+        self.slot = max([a.r for a in self.adapters], default=16)
+        layout = projection_layout(cfg)
+        self.views: dict[tuple[int, str], StackView] = {}
+        off = 0
+        for l in self.layers:
+            for proj in PROJECTIONS:
+                K, subs = layout[proj]["K"], layout[proj]["subs"]
+                N = sum(s for _, s in subs)
+                R = rank_pad(len(subs) * self.slot)
+                a_off = off
+                off += n * R * K
+                b_off = off
+                off += n * N * R
+                self.views[(l, proj)] = StackView(l, proj, K, N, R, self.slot, list(subs), a_off, b_off)
+        off = (off + 127) // 128 * 128
+        self.numel = off
+        self.work = torch.zeros(off, dtype=torch.bfloat16, device=self.device)
+        self.grad = torch.zeros(off, dtype=torch.float32, device=self.device)
+        if with_optimizer_state:
+            self.master = torch.zeros(off, dtype=torch.float32, device=self.device)
+            self.m = torch.zeros(off, dtype=torch.float32, device=self.device)
+            self.v = torch.zeros(off, dtype=torch.float32, device=self.device)
+        else:
+            self.master = self.m = self.v = None
+        for v in self.views.values():
+            n_a, n_b = n * v.R * v.K, n * v.N * v.R
+            v.stack = LoRAStack(
+                self.work[v.a_offset:v.a_offset + n_a].view(n, v.R, v.K),
+                self.work[v.b_offset:v.b_offset + n_b].view(n, v.N, v.R),
+                self.grad[v.a_offset:v.a_offset + n_a].view(n, v.R, v.K),
+                self.grad[v.b_offset:v.b_offset + n_b].view(n, v.N, v.R))
+        self.steps = [0] * n
+        self._chunks: dict[int, torch.Tensor] = {}
+        self._init_weights(init_b_std, seed)
+
+    # ------------------------------------------------------------------ layout helpers
+    def targets(self, adapter: int, sub_name: str) -> bool:
+        return sub_name in self.adapters[adapter].target_modules
+
+    def sub_slices(self, view: StackView, adapter: int):
+        """Yield ``(sub_name, row0_of_B, out_size, rank_col0, rank)`` for the sub-projections
+        adapter ``adapter`` is attached to."""
+        r = self.adapters[adapter].r
+        n0 = 0
+        for j, (name, size) in enumerate(view.subs):
+            if self.targets(adapter, name):
+                yield name, n0, size, j * view.slot, r
+            n0 += size
+
+    def stack(self, layer: int, proj: str) -> LoRAStack:
+        return self.views[(layer, proj)].stack
+
+    # ------------------------------------------------------------------ init
+    def _init_weights(self, init_b_std: float, seed: int) -> None:
+        """PEFT's default LoRA init: A ~ kaiming-uniform(a = sqrt 5) i.e. U(-1/sqrt K, 1/sqrt K),
+        B = 0 (or N(0, init_b_std) when a non-zero B is wanted for testing/benchmarks)."""
+        g = torch.Generator(device=self.device).manual_seed(seed)
+        target = self.master if self.master is not None else torch.zeros(
+            self.numel, dtype=torch.float32, device=self.device)
+        for v in self.views.values():
+            n = self.num_adapters
+            a = target[v.a_offset:v.a_offset + n * v.R * v.K].view(n, v.R, v.K)
+            b = target[v.b_offset:v.b_offset + n * v.N * v.R].view(n, v.N, v.R)
+            bound = 1.0 / math.sqrt(v.K)
+            for i in range(n):
+                for _, n0, size, c0, r in self.sub_slices(v, i):
+                    a[i, c0:c0 + r].uniform_(-bound, bound, generator=g)
+                    if init_b_std > 0:
+                        b[i, n0:n0 + size, c0:c0 + r].normal_(0.0, init_b_std, generator=g)
+        self.work.copy_(target)
+        if self.master is not None:
+            # keep master consistent with the bf16 copy the kernels read
+            self.master.copy_(self.work.float())
+
+    # ------------------------------------------------------------------ chunk tables
+    def chunk_table(self, adapter: int) -> torch.Tensor:
+        """int64 ``[n_chunks, 5]`` regions (offset, rows, ld, col0, cols) covering every
+        tensor of ``adapter``; the gradient of the whole region is consumed, only the
+        trainable window is updated."""
+        t = self._chunks.get(adapter)
+        if t is None:
+            rows = []
+            for v in self.views.values():
+                a_base = v.a_offset + adapter * v.R * v.K
+                b_base = v.b_offset + adapter * v.N * v.R
+                # A: whole [R, K] block is cleared; trainable rows are contiguous per sub
+                covered = 0
+                for _, _, _, c0, r in self.sub_slices(v, adapter):
+                    if c0 > covered:  # untargeted slot rows: clear only
+                        rows.append((a_base + covered * v.K, 1, (c0 - covered) * v.K, 0, 0))
+                    rows.append((a_base + c0 * v.K, 1, r * v.K, 0, r * v.K))
+                    covered = c0 + r
+                if covered < v.R:
+                    rows.append((a_base + covered * v.K, 1, (v.R - covered) * v.K, 0, 0))
+                # B: per sub-projection a row block with a column window
+                n0 = 0
+                for j, (name, size) in enumerate(v.subs):
+                    if self.targets(adapter, name):
+                        rows.append((b_base + n0 * v.R, size, v.R, j * v.slot, self.adapters[adapter].r))
+                    else:
+                        rows.append((b_base + n0 * v.R, size, v.R, 0, 0))
+                    n0 += size
+            t = torch.tensor(rows, dtype=torch.int64, device=self.device)
+            self._chunks[adapter] = t
+        return t
+
+    def trainable_numel(self, adapter: int) -> int:
+        tot = 0
+        for v in self.views.values():
+            for _, _, size, _, r in self.sub_slices(v, adapter):
+                tot += r * v.K + size * r
+        return tot
+
+    # ------------------------------------------------------------------ optimizer
+    def adam_step(self, adapter: int, *, lr: float, beta1: float = 0.9, beta2: float = 0.999,
+                  eps: float = 1e-8, weight_decay: float = 0.0, grad_scale: float = 1.0) -> None:
+        from ..ops.elementwise import adam_chunks
+
+        if self.master is None:
+            raise RuntimeError("arena was created without optimizer state")
+        self.steps[adapter] += 1
+        adam_chunks(self.chunk_table(adapter), self.grad, self.master, self.m, self.v, self.work,
+                    lr=lr, beta1=beta1, beta2=beta2, eps=eps, weight_decay=weight_decay,
+                    step=self.steps[adapter], grad_scale=grad_scale)
+
+    def zero_grad(self) -> None:
+        self.grad.zero_()
+
+    # ------------------------------------------------------------------ per-adapter tensors
+    def export_adapter(self, adapter: int) -> dict[str, torch.Tensor]:
+        """``{"layers.{l}.{sub}.lora_A": [r, K], "...lora_B": [N_sub, r]}`` (fp32 master if
+        present, else the bf16 working copy)."""
+        src = self.master if self.master is not None else self.work
+        out = {}
+        n = self.num_adapters
+        for (l, _), v in self.views.items():
+            a = src[v.a_offset:v.a_offset + n * v.R * v.K].view(n, v.R, v.K)[adapter]
+            b = src[v.b_offset:v.b_offset + n * v.N * v.R].view(n, v.N, v.R)[adapter]
+            for name, n0, size, c0, r in self.sub_slices(v, adapter):
+                out[f"layers.{l}.{name}.lora_A"] = a[c0:c0 + r].clone()
+                out[f"layers.{l}.{name}.lora_B"] = b[n0:n0 + size, c0:c0 + r].clone()
+        return out
+
+    def import_adapter(self, adapter: int, tensors: dict[str, torch.Tensor]) -> None:
+        n = self.num_adapters
+        for (l, _), v in self.views.items():
+            for name, n0, size, c0, r in self.sub_slices(v, adapter):
+                ka, kb = f"layers.{l}.{name}.lora_A", f"layers.{l}.{name}.lora_B"
+                if ka not in tensors or kb not in tensors:
+                    raise KeyError(f"missing {ka} / {kb}")
+                for arena in (self.master, self.work):
+                    if arena is None:
+                        continue
+                    a = arena[v.a_offset:v.a_offset + n * v.R * v.K].view(n, v.R, v.K)
+                    b = arena[v.b_offset:v.b_offset + n * v.N * v.R].view(n, v.N, v.R)
+                    a[adapter, c0:c0 + r].copy_(tensors[ka])
+                    b[adapter, n0:n0 + size, c0:c0 + r].copy_(tensors[kb])

@@ -1,0 +1,280 @@
+"""Own decoder-only transformer (Llama / Qwen2 shaped) with a hand-written training engine.
+
+The reference monkey-patches HF models + PEFT and lets autograd drive the backward
+(``lorafusion/train/training_utils.py:533-629``, ``lorafusion/patch/*``).  Here the model
+is a set of frozen weights (bf16 or NF4) plus a :class:`LoRAArena`, and forward / backward
+are written out explicitly over the sm_100a kernels:
+
+    rmsnorm(+residual) -> fused LoRA linear (q|k|v merged) -> RoPE in place -> causal varlen
+    attention -> fused LoRA linear (o) -> rmsnorm(+residual) -> fused LoRA linear (gate|up
+    merged) -> SwiGLU -> fused LoRA linear (down)
+
+Because the base is frozen there are no weight gradients outside the adapters, and because
+the dropout mask is counter-based a layer can be recomputed in the backward from nothing but
+its input (activation recomputation, the counterpart of the reference's selective gradient
+checkpointing, ``training_utils.py:632-732``).  A model instance owns a contiguous range of
+layers (a pipeline stage); the first stage owns the embedding, the last the final norm and
+the lm_head, whose loss is computed chunk by chunk together with its backward so that the
+[tokens, vocab] logits never exist in full.
+"""
+
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+from typing import Optional, Sequence
+
+import torch
+
+from ..ops import elementwise as ew
+from ..ops import attention as att
+from ..ops.batch_info import MultiLoRABatchInfo
+from ..ops.gemm import gemm_nn, gemm_nt
+from ..ops.lora import lora_linear_backward, lora_linear_forward
+from ..ops.nf4 import NF4Weight, quantize_nf4
+from .adapters import LoRAArena
+from .config import AdapterSpec, ModelConfig
+
+PROJ_STREAM = {"qkv": 0, "o": 1, "gate_up": 2, "down": 3}
+
+
+@dataclass
+class PackedBatch:
+    """One packed microbatch on the device.
+
+    ``input_ids`` / ``labels`` / ``position_ids`` are int32 ``[T]`` (labels already shifted,
+    ``-100`` = ignored); ``cu_seqlens`` holds host ints; ``info`` maps 128-token tiles to
+    adapters.  ``T`` is a multiple of 128 because every adapter segment is padded to one."""
+
+    input_ids: torch.Tensor
+    labels: torch.Tensor
+    position_ids: torch.Tensor
+    cu_seqlens: list
+    attn_tiles: att.AttnTiles
+    info: MultiLoRABatchInfo
+    num_real_tokens: int = 0
+    num_loss_tokens: int = 0
+
+    @property
+    def num_tokens(self) -> int:
+        return int(self.input_ids.shape[0])
+
+
+def rope_tables(cfg: ModelConfig, device) -> tuple[torch.Tensor, torch.Tensor]:
+    """cos / sin ``[max_position, head_dim / 2]`` in fp32, with Llama-3.1 scaling if set."""
+    d = cfg.head_dim
+    inv_freq = 1.0 / (cfg.rope_theta ** (torch.arange(0, d, 2, dtype=torch.float64) / d))
+    sc = cfg.rope_scaling
+    if sc is not None:
+        low_wl = sc.original_max_position / sc.low_freq_factor
+        high_wl = sc.original_max_position / sc.high_freq_factor
+        wl = 2 * math.pi / inv_freq
+        smooth = (sc.original_max_position / wl - sc.low_freq_factor) / (sc.high_freq_factor - sc.low_freq_factor)
+        scaled = torch.where(wl > low_wl, inv_freq / sc.factor, inv_freq)
+        mid = (wl <= low_wl) & (wl >= high_wl)
+        scaled = torch.where(mid, (1 - smooth) * inv_freq / sc.factor + smooth * inv_freq, scaled)
+        inv_freq = scaled
+    ang = torch.arange(cfg.max_position, dtype=torch.float64)[:, None] * inv_freq[None, :]
+    return ang.cos().float().to(device).contiguous(), ang.sin().float().to(device).contiguous()
+
+
+@dataclass
+class LayerWeights:
+    ln1: torch.Tensor
+    ln2: torch.Tensor
+    qkv: object  # bf16 tensor or NF4Weight
+    o: object
+    gate_up: object
+    down: object
+    qkv_bias: Optional[torch.Tensor] = None
+
+
+@dataclass
+class LayerSaved:
+    """What a layer keeps for its backward.  With recomputation only ``h_in`` is kept
+    between forward and backward; the rest is rebuilt right before it is needed."""
+
+    h_in: torch.Tensor
+    full: Optional[dict] = None
+
+
+class DecoderStage:
+    """Layers ``[layer_start, layer_end)`` of a decoder, on one GPU."""
+
+    def __init__(self, cfg: ModelConfig, adapters: Sequence[AdapterSpec], device, *,
+                 layer_start: int = 0, layer_end: Optional[int] = None, quantize: bool = False,
+                 double_quant: bool = True, init_std: float = 0.02, init_b_std: float = 0.0,
+                 seed: int = 0, recompute: bool = True, with_optimizer_state: bool = True,
+                 head_chunk_tokens: int = 2048):
+        self.cfg = cfg
+        self.device = torch.device(device)
+        self.layer_start = layer_start
+        self.layer_end = cfg.num_layers if layer_end is None else layer_end
+        self.is_first = self.layer_start == 0
+        self.is_last = self.layer_end == cfg.num_layers
+        self.quantize = quantize
+        self.recompute = recompute
+        self.head_chunk_tokens = head_chunk_tokens
+        self.training = True
+        self.adapters = list(adapters)
+        g = torch.Generator(device=self.device).manual_seed(seed + 1000 * layer_start)
+        h, i = cfg.hidden_size, cfg.intermediate_size
+
+        def rnd(*shape, std=init_std):
+            return (torch.randn(*shape, generator=g, device=self.device, dtype=torch.float32) * std).to(torch.bfloat16)
+
+        def frozen(n, k):
+            w = rnd(n, k)
+            if quantize:
+                q = quantize_nf4(w, double_quant=double_quant)
+                del w
+                return q
+            return w
+
+        self.layers: list[LayerWeights] = []
+        for _ in range(self.layer_start, self.layer_end):
+            self.layers.append(LayerWeights(
+                ln1=torch.ones(h, dtype=torch.bfloat16, device=self.device),
+                ln2=torch.ones(h, dtype=torch.bfloat16, device=self.device),
+                qkv=frozen(cfg.qkv_size, h), o=frozen(h, cfg.q_size),
+                gate_up=frozen(2 * i, h), down=frozen(h, i),
+                qkv_bias=rnd(cfg.qkv_size) if cfg.qkv_bias else None))
+        self.embed = rnd(cfg.vocab_size, h) if self.is_first else None
+        self.final_norm = torch.ones(h, dtype=torch.bfloat16, device=self.device) if self.is_last else None
+        self.lm_head = rnd(cfg.vocab_size, h) if self.is_last else None
+        self.cos, self.sin = rope_tables(cfg, self.device)
+        self.arena = LoRAArena(cfg, self.adapters, range(self.layer_start, self.layer_end), self.device,
+                               init_b_std=init_b_std, seed=seed,
+                               with_optimizer_state=with_optimizer_state) if self.adapters else None
+
+    # ------------------------------------------------------------------ helpers
+    def _stack(self, layer: int, proj: str):
+        return self.arena.stack(layer, proj) if self.arena is not None else None
+
+    @staticmethod
+    def _sid(layer: int, proj: str) -> int:
+        return layer * 8 + PROJ_STREAM[proj]
+
+    def train(self, mode: bool = True):
+        self.training = mode
+        return self
+
+    def base_weight_bytes(self) -> int:
+        tot = 0
+        for lw in self.layers:
+            for w in (lw.qkv, lw.o, lw.gate_up, lw.down):
+                tot += w.nbytes() if isinstance(w, NF4Weight) else w.numel() * w.element_size()
+        return tot
+
+    # ------------------------------------------------------------------ one layer
+    def _layer_forward(self, li: int, res: Optional[torch.Tensor], delta: torch.Tensor,
+                       batch: PackedBatch, keep: bool):
+        """``(res, delta)`` -> ``(h_mid, d)`` with ``h_in = res + delta`` and the layer output
+        ``h_mid + d``.  ``keep`` = store everything the backward needs."""
+        cfg, lw, l = self.cfg, self.layers[li], self.layer_start + li
+        info, tr = batch.info, self.training
+        x1, h_in, rstd1 = ew.rmsnorm_fwd(delta, lw.ln1, cfg.rms_eps, res=res)
+        qkv, s_qkv = lora_linear_forward(x1, lw.qkv, self._stack(l, "qkv"), info,
+                                         stream_id=self._sid(l, "qkv"), bias=lw.qkv_bias, training=tr)
+        ew.rope_inplace(qkv, batch.position_ids, self.cos, self.sin, cfg.num_heads + cfg.num_kv_heads,
+                        cfg.head_dim)
+        attn, lse = att.attention_forward(qkv, batch.attn_tiles, cfg.num_heads, cfg.num_kv_heads)
+        o, s_o = lora_linear_forward(attn, lw.o, self._stack(l, "o"), info, stream_id=self._sid(l, "o"),
+                                     training=tr)
+        x2, h_mid, rstd2 = ew.rmsnorm_fwd(o, lw.ln2, cfg.rms_eps, res=h_in)
+        gu, s_gu = lora_linear_forward(x2, lw.gate_up, self._stack(l, "gate_up"), info,
+                                       stream_id=self._sid(l, "gate_up"), training=tr)
+        act = ew.swiglu_fwd(gu)
+        d, s_d = lora_linear_forward(act, lw.down, self._stack(l, "down"), info,
+                                     stream_id=self._sid(l, "down"), training=tr)
+        full = None
+        if keep:
+            full = dict(x1=x1, rstd1=rstd1, qkv=qkv, attn=attn, lse=lse, s_qkv=s_qkv, s_o=s_o,
+                        h_mid=h_mid, x2=x2, rstd2=rstd2, gu=gu, act=act, s_gu=s_gu, s_d=s_d)
+        return h_mid, d, LayerSaved(h_in, full)
+
+    def _layer_backward(self, li: int, saved: LayerSaved, dh: torch.Tensor, batch: PackedBatch,
+                        need_input_grad: bool = True) -> Optional[torch.Tensor]:
+        cfg, lw, l = self.cfg, self.layers[li], self.layer_start + li
+        info, tr = batch.info, self.training
+        sv = saved.full
+        if sv is None:
+            _, _, re = self._layer_forward(li, None, saved.h_in, batch, keep=True)
+            sv = re.full
+        d_act = lora_linear_backward(dh, sv["act"], sv["s_d"], lw.down, self._stack(l, "down"), info,
+                                     stream_id=self._sid(l, "down"), training=tr)
+        d_gu = ew.swiglu_bwd(d_act, sv["gu"])
+        del d_act
+        d_x2 = lora_linear_backward(d_gu, sv["x2"], sv["s_gu"], lw.gate_up, self._stack(l, "gate_up"), info,
+                                    stream_id=self._sid(l, "gate_up"), training=tr)
+        del d_gu
+        dh_mid = ew.rmsnorm_bwd(d_x2, sv["h_mid"], lw.ln2, sv["rstd2"], dres=dh)
+        d_attn = lora_linear_backward(dh_mid, sv["attn"], sv["s_o"], lw.o, self._stack(l, "o"), info,
+                                      stream_id=self._sid(l, "o"), training=tr)
+        d_qkv = att.attention_backward(sv["qkv"], sv["attn"], d_attn, sv["lse"], batch.attn_tiles,
+                                       cfg.num_heads, cfg.num_kv_heads)
+        ew.rope_inplace(d_qkv, batch.position_ids, self.cos, self.sin, cfg.num_heads + cfg.num_kv_heads,
+                        cfg.head_dim, backward=True)
+        d_x1 = lora_linear_backward(d_qkv, sv["x1"], sv["s_qkv"], lw.qkv, self._stack(l, "qkv"), info,
+                                    stream_id=self._sid(l, "qkv"), need_dx=need_input_grad, training=tr)
+        if not need_input_grad:
+            return None
+        return ew.rmsnorm_bwd(d_x1, saved.h_in, lw.ln1, sv["rstd1"], dres=dh_mid)
+
+    # ------------------------------------------------------------------ stage forward / backward
+    def forward(self, batch: PackedBatch, h_in: Optional[torch.Tensor] = None):
+        """Run this stage.  Returns ``(h_out, saved)``; on the last stage ``h_out`` is the
+        pair ``(res, delta)`` that :meth:`loss_and_grad` consumes."""
+        if self.is_first:
+            delta = ew.embedding(batch.input_ids, self.embed)
+            res = None
+        else:
+            delta, res = h_in, None
+        saved = []
+        for li in range(len(self.layers)):
+            res, delta, sv = self._layer_forward(li, res, delta, batch, keep=not self.recompute)
+            saved.append(sv)
+        if self.is_last:
+            return (res, delta), saved
+        return ew.add(res, delta) if res is not None else delta, saved
+
+    def loss_and_grad(self, out, batch: PackedBatch, loss_scale: float = 1.0):
+        """Final norm + lm_head + cross-entropy, forward and backward together, in token
+        chunks.  Returns ``(sum of token losses, d loss / d h)`` with the gradient already
+        multiplied by ``loss_scale / num_loss_tokens``."""
+        res, delta = out
+        cfg = self.cfg
+        x, h_fin, rstd = ew.rmsnorm_fwd(delta, self.final_norm, cfg.rms_eps, res=res)
+        T = x.shape[0]
+        n_loss = max(batch.num_loss_tokens, 1)
+        dx = torch.empty_like(x)
+        losses = torch.empty(T, dtype=torch.float32, device=x.device)
+        chunk = self.head_chunk_tokens
+        for t0 in range(0, T, chunk):
+            t1 = min(T, t0 + chunk)
+            logits = gemm_nt(x[t0:t1], self.lm_head)
+            ew.cross_entropy_inplace(logits, batch.labels[t0:t1], loss_scale / n_loss, loss_out=losses[t0:t1])
+            gemm_nn(logits, self.lm_head, out=dx[t0:t1])
+            del logits
+        dh = ew.rmsnorm_bwd(dx, h_fin, self.final_norm, rstd)
+        return losses.sum(), dh
+
+    def backward(self, saved: list, dh: torch.Tensor, batch: PackedBatch) -> Optional[torch.Tensor]:
+        """Back-propagate ``dh`` (gradient w.r.t. this stage's output) through the layers;
+        LoRA gradients accumulate in the arena.  Returns the gradient w.r.t. the stage input
+        (``None`` on the first stage, whose input is the frozen embedding)."""
+        for li in reversed(range(len(self.layers))):
+            need = not (self.is_first and li == 0)
+            dh = self._layer_backward(li, saved[li], dh, batch, need_input_grad=need)
+            saved[li] = None
+        return dh
+
+    def forward_backward(self, batch: PackedBatch, loss_scale: float = 1.0) -> torch.Tensor:
+        """Whole-model step for an unpartitioned model: returns the summed token loss."""
+        if not (self.is_first and self.is_last):
+            raise RuntimeError("forward_backward needs the whole model on this stage")
+        out, saved = self.forward(batch)
+        loss, dh = self.loss_and_grad(out, batch, loss_scale)
+        del out
+        self.backward(saved, dh, batch)
+        return loss

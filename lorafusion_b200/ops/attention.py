@@ -65,18 +65,43 @@ def attention_reference(q, k, v, cu_seqlens, scale=None):
     return out
 
 
+def attention_forward(qkv: torch.Tensor, tiles: AttnTiles, n_q_heads: int, n_kv_heads: int,
+                      scale: float | None = None):
+    """Functional forward: returns ``(out [T, Hq*128] bf16, lse [Hq, T] fp32)``."""
+    M = qkv.shape[0]
+    scale = scale if scale is not None else 1.0 / math.sqrt(HEAD_DIM)
+    out = torch.empty((M, n_q_heads * HEAD_DIM), dtype=torch.bfloat16, device=qkv.device)
+    lse = torch.empty((n_q_heads, M), dtype=torch.float32, device=qkv.device)
+    k0 = n_q_heads * HEAD_DIM
+    v0 = k0 + n_kv_heads * HEAD_DIM
+    nv.call("lf_attn_fwd", qkv.data_ptr(), M, qkv.stride(0), 0, k0, v0, n_q_heads, n_kv_heads,
+            tiles.tiles.data_ptr(), tiles.num_tiles, out.data_ptr(), out.stride(0),
+            lse.data_ptr(), scale, nv.err_word(qkv.device).data_ptr(), nv.current_stream_ptr())
+    return out, lse
+
+
+def attention_backward(qkv: torch.Tensor, out: torch.Tensor, d_out: torch.Tensor, lse: torch.Tensor,
+                       tiles: AttnTiles, n_q_heads: int, n_kv_heads: int,
+                       scale: float | None = None) -> torch.Tensor:
+    """Functional backward: gradient w.r.t. the packed (rotated) QKV, same layout as ``qkv``."""
+    M = qkv.shape[0]
+    scale = scale if scale is not None else 1.0 / math.sqrt(HEAD_DIM)
+    d_out = d_out.contiguous()
+    dqkv = torch.empty_like(qkv)
+    delta = torch.empty_like(lse)
+    k0 = n_q_heads * HEAD_DIM
+    v0 = k0 + n_kv_heads * HEAD_DIM
+    nv.call("lf_attn_bwd", qkv.data_ptr(), out.data_ptr(), d_out.data_ptr(), dqkv.data_ptr(), M,
+            qkv.stride(0), 0, k0, v0, n_q_heads, n_kv_heads, tiles.tiles.data_ptr(), tiles.num_tiles,
+            out.stride(0), lse.data_ptr(), delta.data_ptr(), scale,
+            nv.err_word(qkv.device).data_ptr(), nv.current_stream_ptr())
+    return dqkv
+
+
 class _PackedAttention(torch.autograd.Function):
     @staticmethod
     def forward(ctx, qkv, tiles: AttnTiles, n_q_heads: int, n_kv_heads: int, scale: float):
-        M, ld = qkv.shape
-        out = torch.empty((M, n_q_heads * HEAD_DIM), dtype=torch.bfloat16, device=qkv.device)
-        lse = torch.empty((n_q_heads, M), dtype=torch.float32, device=qkv.device)
-        k0 = n_q_heads * HEAD_DIM
-        v0 = k0 + n_kv_heads * HEAD_DIM
-        nv.call("lf_attn_fwd", qkv.data_ptr(), M, qkv.stride(0), 0, k0, v0, n_q_heads, n_kv_heads,
-                tiles.tiles.data_ptr(), tiles.num_tiles, out.data_ptr(), out.stride(0),
-                lse.data_ptr(), scale, nv.err_word(qkv.device).data_ptr(),
-                nv.current_stream_ptr())
+        out, lse = attention_forward(qkv, tiles, n_q_heads, n_kv_heads, scale)
         ctx.save_for_backward(qkv, out, lse)
         ctx.tiles, ctx.hq, ctx.hkv, ctx.scale = tiles, n_q_heads, n_kv_heads, scale
         return out
@@ -84,16 +109,7 @@ class _PackedAttention(torch.autograd.Function):
     @staticmethod
     def backward(ctx, d_out):
         qkv, out, lse = ctx.saved_tensors
-        d_out = d_out.contiguous()
-        M = qkv.shape[0]
-        dqkv = torch.empty_like(qkv)
-        delta = torch.empty_like(lse)
-        k0 = ctx.hq * HEAD_DIM
-        v0 = k0 + ctx.hkv * HEAD_DIM
-        nv.call("lf_attn_bwd", qkv.data_ptr(), out.data_ptr(), d_out.data_ptr(), dqkv.data_ptr(),
-                M, qkv.stride(0), 0, k0, v0, ctx.hq, ctx.hkv, ctx.tiles.tiles.data_ptr(),
-                ctx.tiles.num_tiles, out.stride(0), lse.data_ptr(), delta.data_ptr(), ctx.scale,
-                nv.err_word(qkv.device).data_ptr(), nv.current_stream_ptr())
+        dqkv = attention_backward(qkv, out, d_out, lse, ctx.tiles, ctx.hq, ctx.hkv, ctx.scale)
         return dqkv, None, None, None, None
 
 

@@ -102,9 +102,9 @@ def test_fused_linear_lora_gpu_matches_oracle(p):
                               dropout_p=p)
     y_ref.backward(dy.float().cpu())
     assert_close_two_rounds(y.view(*dy.shape), y_ref.detach(), msg="Y")
-    assert_close_two_rounds(leaves[0].grad, ref_leaves[0].grad, msg="dX")
-    assert_close_two_rounds(leaves[1].grad, ref_leaves[1].grad, atol=2e-2, rtol=3e-2, msg="dA")
-    assert_close_two_rounds(leaves[2].grad, ref_leaves[2].grad, atol=2e-2, rtol=3e-2, msg="dB")
+    assert_close_two_rounds(leaves[0].grad, ref_leaves[0].grad, atol=1e-2, scale_atol_by_rms=True, msg="dX")
+    assert_close_two_rounds(leaves[1].grad, ref_leaves[1].grad, atol=1e-2, rtol=3e-2, scale_atol_by_rms=True, msg="dA")
+    assert_close_two_rounds(leaves[2].grad, ref_leaves[2].grad, atol=1e-2, rtol=3e-2, scale_atol_by_rms=True, msg="dB")
 
 
 @pytest.mark.gpu
@@ -124,7 +124,7 @@ def test_fused_linear_multi_lora_gpu_matches_oracle(mixed_p):
     yr = fused_linear_multi_lora(xr, w.float().cpu(), lora_a_list=ar, lora_b_list=br, **kw)
     yr.backward(dy.float().cpu())
     assert_close_two_rounds(y.view(*dy.shape), yr.detach(), msg="Y")
-    assert_close_two_rounds(xg.grad, xr.grad, msg="dX")
+    assert_close_two_rounds(xg.grad, xr.grad, atol=1e-2, scale_atol_by_rms=True, msg="dX")
     for i in range(3):
-        assert_close_two_rounds(ag[i].grad, ar[i].grad, atol=2e-2, rtol=3e-2, msg=f"dA[{i}]")
-        assert_close_two_rounds(bg[i].grad, br[i].grad, atol=2e-2, rtol=3e-2, msg=f"dB[{i}]")
+        assert_close_two_rounds(ag[i].grad, ar[i].grad, atol=1e-2, rtol=3e-2, scale_atol_by_rms=True, msg=f"dA[{i}]")
+        assert_close_two_rounds(bg[i].grad, br[i].grad, atol=1e-2, rtol=3e-2, scale_atol_by_rms=True, msg=f"dB[{i}]")
