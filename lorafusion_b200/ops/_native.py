@@ -129,8 +129,25 @@ def _declare_cuda(lib: C.CDLL) -> None:
         fn.restype = C.c_int
 
 
+# kernels launched per C entry point (for launch accounting in benchmarks)
+_LAUNCHES_PER_CALL = {"lf_attn_bwd": 3}
+_LAUNCHES = 0
+
+
+def launch_count() -> int:
+    """Number of kernels of this library launched so far by this process."""
+    return _LAUNCHES
+
+
+def note_launch(n: int = 1) -> None:
+    global _LAUNCHES
+    _LAUNCHES += n
+
+
 def call(name: str, *args) -> None:
     """Call an ``int``-returning C entry point and raise on a non-zero status."""
+    global _LAUNCHES
+    _LAUNCHES += _LAUNCHES_PER_CALL.get(name, 1)
     rc = getattr(cuda_lib(), name)(*args)
     if rc != 0:
         raise RuntimeError(f"{name} failed with code {rc}")

@@ -111,6 +111,7 @@ def launch_gemm(
     args.stream_id = stream_id & 0xFFFFFFFF
     args.row_offset, args.col_offset = row_offset, col_offset
     args.group_m, args.max_ctas = group_m, max_ctas
+    nv.note_launch()
     rc = lib.lf_gemm(C.byref(args))
     if rc != 0:
         raise RuntimeError(f"lf_gemm failed with code {rc}")
