@@ -1,0 +1,141 @@
+"""Solver property tests: exact cover, capacity, bubble lemma, greedy vs exact, merge pass,
+serialisation (all CPU)."""
+
+import itertools
+import random
+
+import numpy as np
+import pytest
+
+from lorafusion_b200.solver import schedule as S
+from lorafusion_b200.train.data import LengthDistribution
+
+
+def _data(num_adapters=4, batches=3, gbs=8, seed=0, hi=4096):
+    meds = [256, 512, 1024, 2048]
+    out = []
+    for a in range(num_adapters):
+        d = LengthDistribution(meds[a % 4], 0.6, 32, hi)
+        lens = d.sample(batches * gbs, seed + a).tolist()
+        out.append([lens[i * gbs:(i + 1) * gbs] for i in range(batches)])
+    return out
+
+
+def _padded_load(bin_keys, samples, pad=128):
+    lens = {k: t for k, _, t in samples}
+    ad = {k: a for k, a, _ in samples}
+    per = {}
+    for k in bin_keys:
+        per[ad[k]] = per.get(ad[k], 0) + lens[k]
+    return sum(((v + pad - 1) // pad) * pad for v in per.values())
+
+
+def _brute_force_min_bins(samples, capacity):
+    n = len(samples)
+    for nb in range(1, n + 1):
+        for assign in itertools.product(range(nb), repeat=n):
+            bins = [[] for _ in range(nb)]
+            for (k, _, _), b in zip(samples, assign):
+                bins[b].append(k)
+            if all(_padded_load(b, samples) <= capacity for b in bins if b) and all(bins):
+                return nb
+    return n
+
+
+def test_ffd_and_exact_respect_capacity_and_cover():
+    rng = random.Random(0)
+    for trial in range(20):
+        n = rng.randint(1, 24)
+        samples = [((rng.randint(0, 2), 0, i), None, rng.randint(32, 3000)) for i in range(n)]
+        samples = [(k, k[0], t) for k, _, t in samples]
+        for fn in (S.greedy_pack_decide_bins, lambda s, c: S.solve_micro_milp_lexicographic(s, c, time_limit=0.5)[0]):
+            bins = fn(samples, 4096)
+            keys = sorted(k for b in bins for k in b)
+            assert keys == sorted(k for k, _, _ in samples)
+            assert all(_padded_load(b, samples) <= 4096 for b in bins)
+
+
+def test_exact_matches_brute_force_on_tiny_instances():
+    rng = random.Random(1)
+    for trial in range(12):
+        n = rng.randint(2, 7)
+        samples = [((rng.randint(0, 1), 0, i), 0, rng.randint(100, 1500)) for i in range(n)]
+        samples = [(k, k[0], t) for k, _, t in samples]
+        bins, status = S.solve_micro_milp_lexicographic(samples, 2048, time_limit=2.0)
+        assert status & 1
+        assert len(bins) == _brute_force_min_bins(samples, 2048)
+        greedy = S.greedy_pack_decide_bins(samples, 2048)
+        assert len(bins) <= len(greedy)
+
+
+def test_exact_minimises_leftover_bin():
+    # 3 x 1024 + 1 x 128 at capacity 2048: two bins; the best leftover is 1024 + 128 vs 2048
+    samples = [((0, 0, i), 0, t) for i, t in enumerate([1024, 1024, 1024, 128])]
+    bins, status = S.solve_micro_milp_lexicographic(samples, 2048, time_limit=2.0)
+    loads = sorted(_padded_load(b, samples) for b in bins)
+    assert loads == [1152, 2048] and status & 2
+
+
+def test_oversized_sample_raises():
+    with pytest.raises(ValueError):
+        S.greedy_pack_decide_bins([((0, 0, 0), 0, 5000)], 4096)
+
+
+def test_microbatch_info_padding_and_merge():
+    a = S.MicroBatchInfo({(0, 0, 0): 100, (1, 0, 0): 129}, 1024)
+    assert a.padded_adapter_num_tokens_pairs == {0: 128, 1: 256} and a.padded_total_tokens == 384
+    b = S.MicroBatchInfo({(0, 0, 1): 28, (2, 0, 0): 500}, 1024)
+    assert a.can_full_merge(b) and a.full_merge(b)
+    assert a.padded_total_tokens == 128 + 256 + 512 and not b.data_samples
+    c = S.MicroBatchInfo({(0, 1, 0): 10}, 1024)
+    assert not a.can_full_merge(c)  # adapter 0 with another global batch
+    d = S.MicroBatchInfo({(3, 0, 0): 64, (3, 0, 1): 300}, 1024)
+    assert a.partial_merge(d) == 1 and list(d.data_samples.values()) == [300]
+
+
+@pytest.mark.parametrize("stages", [1, 2, 4])
+def test_full_schedule_is_valid(stages):
+    data = _data()
+    groups = S.group_adapters(data, 4096, num_stages=stages)
+    assert sorted(a for g in groups for a in g) == [0, 1, 2, 3]
+    sched = S.packing_data_to_microbatches_micro_milp(data, groups, 4096, stages, time_limit=0.2, num_workers=4)
+    merged = S.apply_merge_pass_for_adapter_group_step_infos(sched, stages)
+    ok, msgs, fixed = S.verify_correctness_of_schedule(data, merged, stages, add_bubble=True)
+    assert ok, msgs
+    ok2, msgs2 = S.verify_correctness_of_schedule(data, fixed, stages)
+    assert ok2, msgs2
+    before = S.schedule_statistics(sched)
+    after = S.schedule_statistics(merged)
+    assert after["num_microbatches"] <= before["num_microbatches"]
+    assert after["real_tokens"] == before["real_tokens"] == sum(t for a in data for b in a for t in b)
+
+
+def test_bubble_lemma_detection_and_noop_insertion():
+    cap = 4096
+    mk = lambda a, g: S.MicroBatchInfo({(a, g, 0): 1000}, cap)  # noqa: E731
+    sched = [S.AdapterGroupStepInfo([mk(0, 0)]), S.AdapterGroupStepInfo([mk(0, 1)])]
+    ok, msgs = S.verify_correctness_of_schedule([[[1000], [1000]]], sched, 4)
+    assert not ok and "bubble" in " ".join(msgs)
+    ok, msgs, fixed = S.verify_correctness_of_schedule([[[1000], [1000]]], sched, 4, add_bubble=True)
+    assert ok, msgs
+    flat = S.flatten_schedule(fixed)
+    assert [m.is_empty_marker for m in flat] == [False, True, True, True, False]
+
+
+def test_verify_detects_missing_and_duplicate_samples():
+    data = [[[500, 600]]]
+    good = [S.AdapterGroupStepInfo([S.MicroBatchInfo({(0, 0, 0): 500, (0, 0, 1): 600}, 4096)])]
+    assert S.verify_correctness_of_schedule(data, good, 1)[0]
+    missing = [S.AdapterGroupStepInfo([S.MicroBatchInfo({(0, 0, 0): 500}, 4096)])]
+    assert not S.verify_correctness_of_schedule(data, missing, 1)[0]
+    over = [S.AdapterGroupStepInfo([S.MicroBatchInfo({(0, 0, 0): 500, (0, 0, 1): 600}, 1024)])]
+    assert not S.verify_correctness_of_schedule(data, over, 1)[0]
+
+
+def test_schedule_roundtrip(tmp_path):
+    data = _data(batches=2)
+    sched = S.packing_data_to_microbatches_micro_milp(data, None, 4096, 2, time_limit=0.1)
+    S.save_schedule(sched, tmp_path / S.schedule_name("mix", 4096, 4, 2, 8))
+    for suffix in (".json", ".pkl"):
+        back = S.load_schedule((tmp_path / S.schedule_name("mix", 4096, 4, 2, 8)).with_suffix(suffix))
+        assert [m.data_samples for m in S.flatten_schedule(back)] == [m.data_samples for m in S.flatten_schedule(sched)]
