@@ -492,3 +492,89 @@ extern "C" int lf_attn_bwd(const void* qkv, const void* out, const void* d_out, 
   attn_dkdv_kernel<<<dim3(num_tiles, Hkv), 192, BWD_SMEM, st>>>(p, tmQKV, tmDO);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
+
+// ------------------------------------------------------------------------------------
+// Variant that allocates nothing: the delta scratch lives in the library image.
+// See attn_noalloc.h for who needs this and for the rules of use.
+// ------------------------------------------------------------------------------------
+#include "attn_noalloc.h"
+
+static __device__ __align__(256) float g_noalloc_delta[LF_ATTN_NOALLOC_MAX_DELTA];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float* g_noalloc_delta_addr[kMaxDevices] = {nullptr};
+
+// In host code `g_noalloc_delta` is only a handle for the symbol, not a device address;
+// the real address has to be asked for once per device, with that device current.
+int noalloc_delta_address(float** out) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return -1;
+  if (g_noalloc_delta_addr[dev] == nullptr) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_noalloc_delta) != cudaSuccess || p == nullptr) return -1;
+    g_noalloc_delta_addr[dev] = static_cast<float*>(p);
+  }
+  *out = g_noalloc_delta_addr[dev];
+  return 0;
+}
+}  // namespace
+
+extern "C" int lf_attn_bwd_noalloc(const void* qkv, const void* out, const void* d_out, void* dqkv,
+                                   long long M, long long ld_qkv, int q_col0, int k_col0, int v_col0,
+                                   int Hq, int Hkv, const void* tiles, int num_tiles, long long ldo,
+                                   const float* lse, float scale, int* err, void* stream) {
+  if (num_tiles <= 0) return 0;
+  if (Hq <= 0 || Hkv <= 0 || Hq % Hkv != 0 || M <= 0) return -1;
+  if ((long long)Hq * M > (long long)LF_ATTN_NOALLOC_MAX_DELTA) {
+    fprintf(stderr,
+            "lf_attn_bwd_noalloc: Hq * M = %lld exceeds the built-in scratch of %d floats; use "
+            "lf_attn_bwd with a caller-provided delta buffer instead\n",
+            (long long)Hq * M, LF_ATTN_NOALLOC_MAX_DELTA);
+    return LF_ATTN_NOALLOC_TOO_LARGE;
+  }
+  float* delta = nullptr;
+  if (noalloc_delta_address(&delta) != 0) {
+    fprintf(stderr, "lf_attn_bwd_noalloc: could not resolve the scratch symbol on this device\n");
+    return LF_ATTN_NOALLOC_SETUP_FAILED;
+  }
+  cudaStream_t st = (cudaStream_t)stream;
+  CUtensorMap tmQKV, tmDO;
+  int rc = make_tmap_2d_b16(&tmQKV, qkv, (uint64_t)M, (uint64_t)ld_qkv, (uint64_t)ld_qkv, 128, 64, true);
+  if (rc != 0) return -20 + rc;
+  rc = make_tmap_2d_b16(&tmDO, d_out, (uint64_t)M, (uint64_t)Hq * ATT_D, (uint64_t)ldo, 128, 64, true);
+  if (rc != 0) return -30 + rc;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(attn_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BWD_SMEM) != cudaSuccess ||
+        cudaFuncSetAttribute(attn_dkdv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BWD_SMEM) != cudaSuccess)
+      return -10;
+    configured = true;
+  }
+  {
+    const long long warps = M * Hq;
+    const int block = 256;
+    const long long grid = (warps * 32 + block - 1) / block;
+    attn_delta_kernel<<<(unsigned)grid, block, 0, st>>>((const __nv_bfloat16*)out,
+                                                         (const __nv_bfloat16*)d_out, delta, M, Hq, ldo);
+  }
+  AttnBwdParams p;
+  p.tiles = (const int4*)tiles;
+  p.num_tiles = num_tiles;
+  p.Hq = Hq;
+  p.Hkv = Hkv;
+  p.q_col0 = q_col0;
+  p.k_col0 = k_col0;
+  p.v_col0 = v_col0;
+  p.dqkv = (__nv_bfloat16*)dqkv;
+  p.ld_qkv = ld_qkv;
+  p.lse = lse;
+  p.delta = delta;
+  p.M_total = M;
+  p.scale = scale;
+  p.scale_log2e = scale * 1.4426950408889634f;
+  p.err = err;
+  attn_dq_kernel<<<dim3(num_tiles, Hq), 192, BWD_SMEM, st>>>(p, tmQKV, tmDO);
+  attn_dkdv_kernel<<<dim3(num_tiles, Hkv), 192, BWD_SMEM, st>>>(p, tmQKV, tmDO);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
