@@ -1,0 +1,213 @@
+"""Pipeline-parallel runtime: non-interleaved 1F1B over NCCL (or gloo) point-to-point.
+
+Replaces the reference's copies of Megatron's schedules
+(``lorafusion/pipeline_parallel/multi_lora_schedule.py:130-726``) and Megatron's p2p layer:
+
+* **No shape handshake and no empty-batch marker tensors.**  The microbatch schedule is
+  produced offline, so every stage knows each microbatch's padded token count in advance;
+  receive buffers are allocated directly and empty (no-op) microbatches -- inserted by the
+  solver to satisfy the bubble lemma -- are skipped by all stages without communication (the
+  reference sends a ``(1, 1, 7)`` marker tensor, ``multi_lora_schedule.py:36,575-579``).
+* **Overlapped p2p.**  Forward activations and backward gradients travel on two separate
+  process groups (independent communicators and streams), receives for the next microbatch
+  are posted before the current one is computed, and sends are waited on lazily.
+* **Per-adapter optimizer steps inside the schedule**: after each backward the manager
+  retires the oldest in-flight microbatch and steps every adapter whose global batch is
+  complete; the bubble lemma guarantees no in-flight microbatch still reads those weights.
+
+A stage is anything with ``forward(batch, h_in) -> (h_out, saved)``,
+``loss_and_grad(out, batch) -> (loss, dh)`` and ``backward(saved, dh, batch) -> dh_in``
+(:class:`lorafusion_b200.models.decoder.DecoderStage` or a CPU toy stage in the tests).
+"""
+
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+from typing import Any, Callable, Optional, Sequence
+
+import torch
+import torch.distributed as dist
+
+from .layout import ParallelState
+
+
+def even_layer_partition(num_layers: int, num_stages: int) -> list:
+    """``[(start, end)]`` per stage; the first ``num_layers % num_stages`` stages get one
+    extra layer (``lorafusion/pipeline_parallel/pipe_module.py:98-154``)."""
+    base, extra = divmod(num_layers, num_stages)
+    out, start = [], 0
+    for s in range(num_stages):
+        n = base + (1 if s < extra else 0)
+        out.append((start, start + n))
+        start += n
+    return out
+
+
+def get_pipeline_stage_layer_indices(num_layers: int, num_stages: int, stage_idx: int) -> list:
+    s, e = even_layer_partition(num_layers, num_stages)[stage_idx]
+    return list(range(s, e))
+
+
+@dataclass
+class PipelineMicrobatch:
+    """What one stage needs to know about a microbatch: its device batch (``None`` for an
+    empty no-op) and the padded token count that fixes the activation shape."""
+
+    batch: Any
+    num_tokens: int
+    is_empty: bool = False
+
+
+@dataclass
+class PipelineStats:
+    loss_sum: float = 0.0
+    real_tokens: int = 0
+    forward_s: float = 0.0
+    backward_s: float = 0.0
+    total_s: float = 0.0
+    stepped: list = field(default_factory=list)
+
+    @property
+    def bubble_ratio(self) -> float:
+        return 1.0 - (self.forward_s + self.backward_s) / self.total_s if self.total_s > 0 else 0.0
+
+
+class _P2P:
+    """Asynchronous activation / gradient exchange with the neighbouring stages."""
+
+    def __init__(self, state: ParallelState, fwd_group, bwd_group, hidden: int, dtype, device):
+        self.state, self.fwd_group, self.bwd_group = state, fwd_group, bwd_group
+        self.hidden, self.dtype, self.device = hidden, dtype, device
+        self._pending_sends: list = []
+
+    def _buf(self, tokens: int) -> torch.Tensor:
+        return torch.empty((tokens, self.hidden), dtype=self.dtype, device=self.device)
+
+    def post_recv_forward(self, tokens: int):
+        if self.state.is_first_stage:
+            return None
+        buf = self._buf(tokens)
+        return buf, dist.irecv(buf, src=self.state.prev_rank, group=self.fwd_group)
+
+    def post_recv_backward(self, tokens: int):
+        if self.state.is_last_stage:
+            return None
+        buf = self._buf(tokens)
+        return buf, dist.irecv(buf, src=self.state.next_rank, group=self.bwd_group)
+
+    def send_forward(self, t: torch.Tensor) -> None:
+        if not self.state.is_last_stage:
+            self._pending_sends.append((t, dist.isend(t.contiguous(), dst=self.state.next_rank, group=self.fwd_group)))
+
+    def send_backward(self, t: Optional[torch.Tensor]) -> None:
+        if not self.state.is_first_stage and t is not None:
+            self._pending_sends.append((t, dist.isend(t.contiguous(), dst=self.state.prev_rank, group=self.bwd_group)))
+
+    @staticmethod
+    def wait(handle):
+        if handle is None:
+            return None
+        buf, req = handle
+        req.wait()
+        return buf
+
+    def drain(self) -> None:
+        for _, req in self._pending_sends:
+            req.wait()
+        self._pending_sends.clear()
+
+    def reap(self) -> None:
+        """Drop completed sends (keeps tensors alive only while in flight)."""
+        self._pending_sends = [(t, r) for t, r in self._pending_sends if not r.is_completed()]
+
+
+class PipelineRuntime:
+    def __init__(self, stage, state: ParallelState, *, hidden_size: int, dtype=torch.bfloat16, device="cuda",
+                 manager=None, fwd_group=None, bwd_group=None, use_timers: bool = False):
+        self.stage, self.state, self.manager = stage, state, manager
+        self.device = torch.device(device)
+        self.p2p = _P2P(state, fwd_group, bwd_group, hidden_size, dtype, self.device)
+        self.use_timers = use_timers
+
+    # ------------------------------------------------------------------ timing helper
+    def _tick(self) -> float:
+        if self.use_timers and self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
+        return time.perf_counter()
+
+    # ------------------------------------------------------------------ single ops
+    def _forward(self, mb: PipelineMicrobatch, recv_handle, stats: PipelineStats):
+        if self.manager is not None:
+            self.manager.mark_forward_pass_started()
+            self.manager.add_batch_info(mb.batch.info)
+        h_in = self.p2p.wait(recv_handle)
+        t0 = self._tick()
+        out, saved = self.stage.forward(mb.batch, h_in)
+        entry = dict(saved=saved, out=None, dh=None)
+        if self.state.is_last_stage:
+            loss, dh = self.stage.loss_and_grad(out, mb.batch)
+            entry["dh"] = dh
+            stats.loss_sum = stats.loss_sum + loss
+            stats.real_tokens += getattr(mb.batch, "num_real_tokens", 0)
+        else:
+            self.p2p.send_forward(out)
+        stats.forward_s += self._tick() - t0
+        return entry
+
+    def _backward(self, mb: PipelineMicrobatch, entry, recv_handle, stats: PipelineStats):
+        if self.manager is not None:
+            self.manager.mark_backward_pass_started()
+        dh = entry["dh"] if self.state.is_last_stage else self.p2p.wait(recv_handle)
+        t0 = self._tick()
+        dh_in = self.stage.backward(entry["saved"], dh, mb.batch)
+        self.p2p.send_backward(dh_in)
+        stats.backward_s += self._tick() - t0
+        if self.manager is not None:
+            self.manager.pop_oldest_batch_info()
+            stats.stepped += self.manager.maybe_reduce_grad_and_optimizer_step()
+
+    # ------------------------------------------------------------------ schedules
+    def run(self, microbatches: Sequence[PipelineMicrobatch]) -> PipelineStats:
+        """Execute one list of microbatches with 1F1B (or plainly when there is one stage)."""
+        stats = PipelineStats()
+        t_start = self._tick()
+        work = [m for m in microbatches if not m.is_empty]
+        pp = self.state.layout.pp
+        M = len(work)
+        warm = min(pp - self.state.pp_rank - 1, M)
+        steady = M - warm
+        in_flight: list = []
+        nf = nb = 0  # next forward / backward microbatch index
+
+        recv_f = self.p2p.post_recv_forward(work[0].num_tokens) if M else None
+        for _ in range(warm):
+            entry = self._forward(work[nf], recv_f, stats)
+            in_flight.append(entry)
+            nf += 1
+            recv_f = self.p2p.post_recv_forward(work[nf].num_tokens) if nf < M else None
+        recv_b = None
+        for i in range(steady):
+            entry = self._forward(work[nf], recv_f, stats)
+            in_flight.append(entry)
+            nf += 1
+            recv_b = self.p2p.post_recv_backward(work[nb].num_tokens)
+            recv_f = self.p2p.post_recv_forward(work[nf].num_tokens) if nf < M else None
+            self._backward(work[nb], in_flight.pop(0), recv_b, stats)
+            nb += 1
+            self.p2p.reap()
+        for _ in range(warm):
+            recv_b = self.p2p.post_recv_backward(work[nb].num_tokens)
+            self._backward(work[nb], in_flight.pop(0), recv_b, stats)
+            nb += 1
+        self.p2p.drain()
+        if self.manager is not None:
+            self.manager.clear_batch_info()
+        stats.total_s = self._tick() - t_start
+        return stats
+
+
+def multi_lora_get_forward_backward_func(runtime: PipelineRuntime) -> Callable:
+    """Returns the callable that runs a list of microbatches through this rank's stage
+    (name kept from ``lorafusion/pipeline_parallel/multi_lora_schedule.py:130``)."""
+    return runtime.run
