@@ -46,7 +46,8 @@ def parse_args():
     ap.add_argument("--microbatches", type=int, default=2, help="microbatches per step per GPU")
     ap.add_argument("--dropout", type=float, default=0.1)
     ap.add_argument("--no-quantize", action="store_true")
-    ap.add_argument("--no-recompute", action="store_true")
+    ap.add_argument("--recompute", default="auto", choices=["auto", "all", "none"],
+                    help="activation recomputation: all layers, none, or as memory allows")
     ap.add_argument("--skip-e2e", action="store_true")
     return ap.parse_args()
 
@@ -176,7 +177,7 @@ def main():
     adapters = [AdapterSpec(f"lora_{i}", r=16, lora_alpha=32.0, dropout=args.dropout) for i in range(4)]
     t0 = time.time()
     trainer = MultiLoRATrainer(cfg, adapters, device, quantize=not args.no_quantize,
-                               recompute=not args.no_recompute, optim=OptimizerConfig(lr=1e-4),
+                               recompute={'auto': 'auto', 'all': True, 'none': False}[args.recompute], optim=OptimizerConfig(lr=1e-4),
                                dp_group=dist.group.WORLD if world > 1 else None, seed=1234, init_b_std=0.01)
     torch.cuda.synchronize()
     if rank == 0:
@@ -256,7 +257,8 @@ def main():
             "seq_len": "lognormal medians 256/512/1024/2048, sigma 0.5-0.8, clip [32,8192], packed",
             "parallelism": f"dp{world}",
             "adapters": "4 x LoRA r16 alpha32 dropout %.2f on q,k,v,o,gate,up,down" % args.dropout,
-            "recompute": not args.no_recompute,
+            "recompute": args.recompute,
+            "layers_without_recompute": trainer.stage._plan_keep(args.capacity),
             "l2": "inputs (frozen base weights) far larger than L2",
             "baseline": "vs_baseline = value / (n_gpus * 1278.85 tok/s/GPU), the reference's published "
                         "70B-mixed LoRAFusion throughput on 4xH100 per GPU",

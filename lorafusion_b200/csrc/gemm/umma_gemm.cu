@@ -102,7 +102,10 @@ __global__ void __launch_bounds__(MASK_A ? (192 + 32 * kNumMaskWarps) : 192, 1)
                      const __grid_constant__ CUtensorMap tmB2) {
   using Plan = SmemPlan<BN>;
   constexpr int STAGES = Plan::STAGES;
-  constexpr int TMEM_COLS = BN * NACC * 2;
+  // Two accumulator buffers whenever TMEM (512 columns) has room; the 256-wide
+  // two-accumulator variant runs single-buffered.
+  constexpr int NBUF = (BN * NACC * 2 <= 512) ? 2 : 1;
+  constexpr int TMEM_COLS = BN * NACC * NBUF;
   static_assert(TMEM_COLS <= 512, "TMEM budget");
   constexpr uint32_t TMEM_ALLOC = TMEM_COLS <= 32 ? 32 : TMEM_COLS <= 64 ? 64 : TMEM_COLS <= 128 ? 128 : TMEM_COLS <= 256 ? 256 : 512;
 
@@ -215,8 +218,8 @@ __global__ void __launch_bounds__(MASK_A ? (192 + 32 * kNumMaskWarps) : 192, 1)
         const int nkb2 = (t.adapter >= 0) ? p.nkb2 : 0;
         const int nkb = (t.adapter < 0 && p.b_adapter_rows > 0) ? 0 : t.nkb;
         const int total = nkb + nkb2;
-        const int buf = tile_iter & 1;
-        const uint32_t bph = (tile_iter >> 1) & 1;
+        const int buf = tile_iter % NBUF;
+        const uint32_t bph = (tile_iter / NBUF) & 1;
         if (!mbar_wait(&tempty[buf], bph ^ 1, ctx, ERR_WAIT_TMEM_EMPTY)) {
           ok = false;
           break;
@@ -271,8 +274,8 @@ __global__ void __launch_bounds__(MASK_A ? (192 + 32 * kNumMaskWarps) : 192, 1)
       const int nkb = (t.adapter < 0 && p.b_adapter_rows > 0) ? 0 : t.nkb;
       const bool has_work = (nkb + nkb2) > 0;
       const bool has_slab = nkb2 > 0;
-      const int buf = tile_iter & 1;
-      const uint32_t bph = (tile_iter >> 1) & 1;
+      const int buf = tile_iter % NBUF;
+      const uint32_t bph = (tile_iter / NBUF) & 1;
       if (!mbar_wait(&tfull[buf], bph, ctx, ERR_WAIT_TMEM_FULL)) {
         ok = false;
         break;
@@ -576,6 +579,7 @@ extern "C" int lf_gemm(const LfGemmArgs* a) {
     LF_CASE(128, 1, 0, 1, 1, LF_EPI_BF16, 0)
     // dX with the dropout mask regenerated in the epilogue
     LF_CASE(128, 2, 0, 1, 1, LF_EPI_BF16_DROPMIX, 0)
+    LF_CASE(256, 2, 0, 1, 1, LF_EPI_BF16_DROPMIX, 0)
 #define LF_SKINNY(bn)                                                \
     /* S' = alpha * dropout(X) A^T */                                  \
     LF_CASE(bn, 1, 0, 0, 0, LF_EPI_BF16_ADAPTER_SCALE, 0)              \

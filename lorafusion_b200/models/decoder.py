@@ -104,8 +104,8 @@ class DecoderStage:
     def __init__(self, cfg: ModelConfig, adapters: Sequence[AdapterSpec], device, *,
                  layer_start: int = 0, layer_end: Optional[int] = None, quantize: bool = False,
                  double_quant: bool = True, init_std: float = 0.02, init_b_std: float = 0.0,
-                 seed: int = 0, recompute: bool = True, with_optimizer_state: bool = True,
-                 head_chunk_tokens: int = 2048):
+                 seed: int = 0, recompute=True, with_optimizer_state: bool = True,
+                 head_chunk_tokens: int = 2048, max_inflight: int = 1, reserve_bytes: int = 24 << 30):
         self.cfg = cfg
         self.device = torch.device(device)
         self.layer_start = layer_start
@@ -113,7 +113,10 @@ class DecoderStage:
         self.is_first = self.layer_start == 0
         self.is_last = self.layer_end == cfg.num_layers
         self.quantize = quantize
-        self.recompute = recompute
+        self.recompute = recompute  # True | False | "auto"
+        self.max_inflight = max(1, max_inflight)
+        self.reserve_bytes = reserve_bytes
+        self._keep_plan: dict = {}
         self.head_chunk_tokens = head_chunk_tokens
         self.training = True
         self.adapters = list(adapters)
@@ -189,8 +192,10 @@ class DecoderStage:
                                      stream_id=self._sid(l, "down"), training=tr)
         full = None
         if keep:
-            full = dict(x1=x1, rstd1=rstd1, qkv=qkv, attn=attn, lse=lse, s_qkv=s_qkv, s_o=s_o,
-                        h_mid=h_mid, x2=x2, rstd2=rstd2, gu=gu, act=act, s_gu=s_gu, s_d=s_d)
+            full = dict(rstd1=rstd1, qkv=qkv, attn=attn, lse=lse, s_qkv=s_qkv, s_o=s_o,
+                        h_mid=h_mid, rstd2=rstd2, gu=gu, s_gu=s_gu, s_d=s_d)
+            if keep != "cheap":  # "cheap" drops what one elementwise kernel can rebuild
+                full.update(x1=x1, x2=x2, act=act)
         return h_mid, d, LayerSaved(h_in, full)
 
     def _layer_backward(self, li: int, saved: LayerSaved, dh: torch.Tensor, batch: PackedBatch,
@@ -201,6 +206,11 @@ class DecoderStage:
         if sv is None:
             _, _, re = self._layer_forward(li, None, saved.h_in, batch, keep=True)
             sv = re.full
+        elif "x1" not in sv:
+            sv = dict(sv)
+            sv["x1"] = ew.rmsnorm_fwd(saved.h_in, lw.ln1, cfg.rms_eps, want_rstd=False)[0]
+            sv["x2"] = ew.rmsnorm_fwd(sv["h_mid"], lw.ln2, cfg.rms_eps, want_rstd=False)[0]
+            sv["act"] = ew.swiglu_fwd(sv["gu"])
         d_act = lora_linear_backward(dh, sv["act"], sv["s_d"], lw.down, self._stack(l, "down"), info,
                                      stream_id=self._sid(l, "down"), training=tr)
         d_gu = ew.swiglu_bwd(d_act, sv["gu"])
@@ -221,6 +231,34 @@ class DecoderStage:
             return None
         return ew.rmsnorm_bwd(d_x1, saved.h_in, lw.ln1, sv["rstd1"], dres=dh_mid)
 
+    # ------------------------------------------------------------------ activation memory plan
+    def saved_bytes_per_layer(self, tokens: int) -> int:
+        """Bytes a layer keeps between forward and backward in the "cheap" mode (GEMM and
+        attention outputs; the elementwise results are rebuilt)."""
+        c = self.cfg
+        return tokens * (c.qkv_size + c.q_size + c.hidden_size + 2 * c.intermediate_size) * 2 \
+            + c.num_heads * tokens * 4 + tokens * 4 * 256 * 2
+
+    def _plan_keep(self, tokens: int) -> int:
+        """How many (trailing) layers keep their activations instead of recomputing them.
+        ``recompute=True`` -> 0, ``False`` -> all, ``"auto"`` -> as many as fit in the free
+        device memory after reserving room for one layer's working set, divided by the
+        number of microbatches this stage holds in flight."""
+        if self.recompute is True:
+            return 0
+        if self.recompute is False:
+            return len(self.layers)
+        key = (tokens,)
+        if key not in self._keep_plan:
+            free, _ = torch.cuda.mem_get_info(self.device)
+            free += torch.cuda.memory_reserved(self.device) - torch.cuda.memory_allocated(self.device)
+            per = self.saved_bytes_per_layer(tokens)
+            h_in_all = len(self.layers) * tokens * self.cfg.hidden_size * 2
+            budget = free - self.reserve_bytes - 3 * per - h_in_all * self.max_inflight
+            n = int(max(0, budget) // (per * self.max_inflight))
+            self._keep_plan[key] = max(0, min(len(self.layers), n))
+        return self._keep_plan[key]
+
     # ------------------------------------------------------------------ stage forward / backward
     def forward(self, batch: PackedBatch, h_in: Optional[torch.Tensor] = None):
         """Run this stage.  Returns ``(h_out, saved)``; on the last stage ``h_out`` is the
@@ -231,8 +269,11 @@ class DecoderStage:
         else:
             delta, res = h_in, None
         saved = []
+        n_keep = self._plan_keep(batch.num_tokens)
+        first_keep = len(self.layers) - n_keep
         for li in range(len(self.layers)):
-            res, delta, sv = self._layer_forward(li, res, delta, batch, keep=not self.recompute)
+            keep = False if li < first_keep else ("cheap" if self.recompute == "auto" else True)
+            res, delta, sv = self._layer_forward(li, res, delta, batch, keep=keep)
             saved.append(sv)
         if self.is_last:
             return (res, delta), saved

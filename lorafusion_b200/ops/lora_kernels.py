@@ -44,6 +44,9 @@ from .philox import dropout_threshold
 RANK_PAD = 64
 RANK_PADS = (64, 128, 192, 256)  # stacked-rank widths the skinny kernels are built for
 TILE_M = 128
+# N tile of the dX kernel with dropout: 256 = two single-buffered accumulators,
+# 128 = two double-buffered accumulators
+DROPMIX_BN = int(__import__('os').environ.get('LORAFUSION_B200_DROPMIX_BN', '256'))
 
 
 @dataclass
@@ -205,7 +208,8 @@ def base_lora_dx(dy: torch.Tensor, w: torch.Tensor, ds: Optional[torch.Tensor],
         assert K2 == K and ds.shape == (M, R)
         kw = dict(a2=ds, b2=_flat2d(a_all), K2=R, b2_adapter_rows=R, tile_adapter=tile_adapter)
     if ds is not None and dropout.active:
-        launch_gemm(a=dy, b=w, out=out, M=M, N=K, K=N, b_mn=True, b2_mn=True, bn=128, nacc=2,
+        launch_gemm(a=dy, b=w, out=out, M=M, N=K, K=N, b_mn=True, b2_mn=True,
+                    bn=DROPMIX_BN if K >= 256 else 128, nacc=2,
                     epi=nv.EPI_BF16_DROPMIX, **kw, **dropout.kwargs())
     else:
         launch_gemm(a=dy, b=w, out=out, M=M, N=K, K=N, b_mn=True, b2_mn=True,

@@ -32,7 +32,7 @@ class OptimizerConfig:
 
 class MultiLoRATrainer:
     def __init__(self, cfg: ModelConfig, adapters: Sequence[AdapterSpec], device, *,
-                 quantize: bool = False, recompute: bool = True, optim: Optional[OptimizerConfig] = None,
+                 quantize: bool = False, recompute=True, optim: Optional[OptimizerConfig] = None,
                  dp_group=None, seed: int = 0, init_b_std: float = 0.0, grad_sync: str = "auto"):
         self.cfg = cfg
         self.adapters = list(adapters)

@@ -38,13 +38,18 @@ def test_engine_matches_autograd_oracle(model, quantize):
                                 max_mismatch_ratio=5e-3, msg=f"dB {key}")
 
 
-def test_recompute_is_bitwise_equivalent():
+@pytest.mark.parametrize("mode", [False, "auto"])
+def test_recompute_is_bitwise_equivalent(mode):
+    """Full recomputation, keeping everything, and the memory-planned mix (which keeps GEMM /
+    attention outputs and rebuilds the elementwise ones) must give identical gradients."""
     s1, batch = _setup(recompute=True)
-    s2, _ = _setup(recompute=False)
+    s2, _ = _setup(recompute=mode)
     l1 = s1.forward_backward(batch)
     l2 = s2.forward_backward(batch)
     assert float(l1) == float(l2)
     assert torch.equal(s1.arena.grad, s2.arena.grad)
+    if mode == "auto":
+        assert s2._plan_keep(batch.num_tokens) == len(s2.layers)
 
 
 def test_loss_decreases_with_adam():
