@@ -1,0 +1,242 @@
+// Data-parallel LoRA gradient reduction fused with the optimizer step, over NVLink peer
+// memory: one kernel = reduce-scatter of the adapter's gradients + gradient scaling + AdamW on
+// the rank's shard + all-gather of the updated bf16 weights.
+//
+// The reference reduces each adapter's gradients with Megatron DDP (bucketed NCCL all-reduce,
+// no overlap) and then runs torch AdamW on every rank
+// (lorafusion/ops/multi_lora.py:166-184, benchmarks_paper/bench_multi_gpu.py:135-149,225-230).
+// Here the gradient and bf16 weight arenas live in symmetric memory (same offsets on every
+// rank, peer pointers known to the kernel).  For every chunk of the adapter (see AdamChunk in
+// loss_optim.cu) rank r owns the r-th contiguous slice of the chunk's elements and
+//   1. loads that slice of the gradient from every rank (P2P loads, or one
+//      multimem.ld_reduce through NVSwitch), sums in fp32 in a fixed rank order,
+//   2. clears the slice in every rank's gradient arena,
+//   3. applies AdamW to its local fp32 master / m / v (optimizer state is only ever touched
+//      by the owner, i.e. it is sharded ZeRO-1 style even though the arenas are full-size),
+//   4. stores the new bf16 weight into every rank's working copy (P2P stores or multimem.st).
+// Cross-rank ordering uses epoch flags in a symmetric signal pad: "gradients ready" before
+// step 1 and "weights written" after step 4.  All waits are bounded and report through the
+// error word.  With sync_mode 0 the flags are skipped: that mode runs the ranks one after
+// another on ONE GPU (for tests) or with a single rank.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "../common/ptx.cuh"
+
+namespace lf {
+
+constexpr int kMaxRanks = 8;
+
+struct ArAdamChunk {
+  long long offset, rows, ld, col0, cols;
+};
+
+struct ArAdamParams {
+  const ArAdamChunk* chunks;
+  int num_chunks;
+  int rank, world;
+  float* grad[kMaxRanks];            // peer pointers to the fp32 gradient arenas
+  __nv_bfloat16* work[kMaxRanks];    // peer pointers to the bf16 working copies
+  float* grad_mc;                    // multicast address of the gradient arena (or null)
+  __nv_bfloat16* work_mc;            // multicast address of the working copy (or null)
+  float* master;
+  float* m;
+  float* v;
+  int* flags[kMaxRanks];             // peer pointers to the signal pads: int[2 * kMaxRanks]
+  int epoch;
+  int sync_mode;                     // 0 = no cross-rank flags, 1 = flags
+  int use_multimem;
+  unsigned int* done_counter;        // local, zero before launch, reset by the kernel
+  float lr, beta1, beta2, eps, weight_decay, bias_c1, bias_c2, grad_scale;
+  int* err;
+};
+
+__device__ __forceinline__ float4 multimem_ld_reduce_f32x4(const float* mc_ptr) {
+  float4 r;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(r.x), "=f"(r.y), "=f"(r.z), "=f"(r.w)
+               : "l"(mc_ptr)
+               : "memory");
+  return r;
+}
+__device__ __forceinline__ void multimem_st_f32x4(float* mc_ptr, float4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_ptr),
+               "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w)
+               : "memory");
+}
+__device__ __forceinline__ void multimem_st_b32x2(void* mc_ptr, uint32_t a, uint32_t b) {
+  asm volatile("multimem.st.relaxed.sys.global.v2.f32 [%0], {%1, %2};" ::"l"(mc_ptr),
+               "f"(__uint_as_float(a)), "f"(__uint_as_float(b))
+               : "memory");
+}
+
+__device__ __forceinline__ float adam_update(float g, float& w, float& mi, float& vi,
+                                             const ArAdamParams& p, float inv_c1, float inv_sqrt_c2) {
+  mi = p.beta1 * mi + (1.f - p.beta1) * g;
+  vi = p.beta2 * vi + (1.f - p.beta2) * g * g;
+  w -= p.lr * p.weight_decay * w;
+  w -= p.lr * (mi * inv_c1) / (sqrtf(vi) * inv_sqrt_c2 + p.eps);
+  return w;
+}
+
+__global__ void __launch_bounds__(256)
+allreduce_adam_kernel(const ArAdamParams p, int blocks_per_chunk) {
+  __shared__ int abort_smem;
+  if (threadIdx.x == 0) abort_smem = 0;
+  __syncthreads();
+  AbortCtx ctx{p.err, &abort_smem};
+
+  // ---- phase 0: every rank's gradients are complete ---------------------------------
+  if (p.sync_mode) {
+    if (blockIdx.x == 0 && threadIdx.x < p.world) {
+      __threadfence_system();
+      st_release_sys(p.flags[threadIdx.x] + p.rank, p.epoch);
+    }
+    if (threadIdx.x < p.world) {
+      wait_flag_ge(p.flags[p.rank] + threadIdx.x, p.epoch, ctx);
+    }
+    __syncthreads();
+  }
+
+  if (!aborted(ctx)) {
+    const int chunk = blockIdx.x / blocks_per_chunk;
+    const int sub = blockIdx.x % blocks_per_chunk;
+    const ArAdamChunk c = p.chunks[chunk];
+    const float inv_c1 = 1.f / p.bias_c1;
+    const float inv_sqrt_c2 = rsqrtf(p.bias_c2);
+    // the chunk is cut in `world` slices of whole 4-element groups; this rank owns slice `rank`
+    const long long total4 = (c.rows * c.ld) >> 2;   // ld and offsets are multiples of 4
+    const long long per = (total4 + p.world - 1) / p.world;
+    const long long lo4 = min(total4, per * p.rank), hi4 = min(total4, per * (p.rank + 1));
+    for (long long i4 = lo4 + sub * 256LL + threadIdx.x; i4 < hi4; i4 += blocks_per_chunk * 256LL) {
+      const long long e = c.offset + (i4 << 2);
+      float4 g;
+      if (p.use_multimem) {
+        g = multimem_ld_reduce_f32x4(p.grad_mc + e);
+        multimem_st_f32x4(p.grad_mc + e, make_float4(0.f, 0.f, 0.f, 0.f));
+      } else {
+        g = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int r = 0; r < p.world; ++r) {
+          float4* src = reinterpret_cast<float4*>(p.grad[r] + e);
+          const float4 t = *src;
+          g.x += t.x;
+          g.y += t.y;
+          g.z += t.z;
+          g.w += t.w;
+          *src = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+      }
+      float gv[4] = {g.x * p.grad_scale, g.y * p.grad_scale, g.z * p.grad_scale, g.w * p.grad_scale};
+      const long long col0 = (i4 << 2) % c.ld;
+      float4 w4 = *reinterpret_cast<float4*>(p.master + e);
+      float4 m4 = *reinterpret_cast<float4*>(p.m + e);
+      float4 v4 = *reinterpret_cast<float4*>(p.v + e);
+      float wv[4] = {w4.x, w4.y, w4.z, w4.w}, mv[4] = {m4.x, m4.y, m4.z, m4.w},
+            vv[4] = {v4.x, v4.y, v4.z, v4.w};
+      bool any = false;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const long long col = col0 + j;
+        if (col >= c.col0 && col < c.col0 + c.cols) {
+          adam_update(gv[j], wv[j], mv[j], vv[j], p, inv_c1, inv_sqrt_c2);
+          any = true;
+        }
+      }
+      if (!any) continue;
+      *reinterpret_cast<float4*>(p.master + e) = make_float4(wv[0], wv[1], wv[2], wv[3]);
+      *reinterpret_cast<float4*>(p.m + e) = make_float4(mv[0], mv[1], mv[2], mv[3]);
+      *reinterpret_cast<float4*>(p.v + e) = make_float4(vv[0], vv[1], vv[2], vv[3]);
+      const uint32_t lo = pack_bf16x2(wv[0], wv[1]), hi = pack_bf16x2(wv[2], wv[3]);
+      if (p.use_multimem) {
+        multimem_st_b32x2(p.work_mc + e, lo, hi);
+      } else {
+        for (int r = 0; r < p.world; ++r)
+          *reinterpret_cast<uint2*>(p.work[r] + e) = make_uint2(lo, hi);
+      }
+    }
+  }
+
+  // ---- phase 2: everyone's weights are written before this kernel ends ---------------
+  if (p.sync_mode) {
+    __threadfence_system();
+    __syncthreads();
+    __shared__ int is_last;
+    if (threadIdx.x == 0) {
+      const unsigned int prev = atomicAdd(p.done_counter, 1u);
+      is_last = (prev == gridDim.x - 1);
+    }
+    __syncthreads();
+    if (is_last) {
+      if (threadIdx.x < p.world) {
+        __threadfence_system();
+        st_release_sys(p.flags[threadIdx.x] + kMaxRanks + p.rank, p.epoch);
+        wait_flag_ge(p.flags[p.rank] + kMaxRanks + threadIdx.x, p.epoch, ctx);
+      }
+      if (threadIdx.x == 0) *p.done_counter = 0u;
+    }
+  }
+}
+
+}  // namespace lf
+
+using namespace lf;
+
+typedef struct LfArAdamArgs {
+  const void* chunks;
+  void* grad[8];
+  void* work[8];
+  void* grad_mc;
+  void* work_mc;
+  void* master;
+  void* m;
+  void* v;
+  void* flags[8];
+  void* done_counter;
+  void* err;
+  void* stream;
+  int num_chunks, rank, world, epoch, sync_mode, use_multimem, step, pad0;
+  float lr, beta1, beta2, eps, weight_decay, grad_scale;
+} LfArAdamArgs;
+
+extern "C" int lf_allreduce_adam(const LfArAdamArgs* a) {
+  if (a == nullptr || a->num_chunks <= 0) return 0;
+  if (a->world < 1 || a->world > kMaxRanks || a->rank < 0 || a->rank >= a->world) return -1;
+  ArAdamParams p;
+  p.chunks = (const ArAdamChunk*)a->chunks;
+  p.num_chunks = a->num_chunks;
+  p.rank = a->rank;
+  p.world = a->world;
+  for (int r = 0; r < kMaxRanks; ++r) {
+    p.grad[r] = (float*)a->grad[r];
+    p.work[r] = (__nv_bfloat16*)a->work[r];
+    p.flags[r] = (int*)a->flags[r];
+  }
+  p.grad_mc = (float*)a->grad_mc;
+  p.work_mc = (__nv_bfloat16*)a->work_mc;
+  p.master = (float*)a->master;
+  p.m = (float*)a->m;
+  p.v = (float*)a->v;
+  p.epoch = a->epoch;
+  p.sync_mode = a->sync_mode;
+  p.use_multimem = (a->use_multimem && a->grad_mc != nullptr && a->work_mc != nullptr) ? 1 : 0;
+  p.done_counter = (unsigned int*)a->done_counter;
+  p.lr = a->lr;
+  p.beta1 = a->beta1;
+  p.beta2 = a->beta2;
+  p.eps = a->eps;
+  p.weight_decay = a->weight_decay;
+  p.bias_c1 = 1.f - powf(a->beta1, (float)a->step);
+  p.bias_c2 = 1.f - powf(a->beta2, (float)a->step);
+  p.grad_scale = a->grad_scale;
+  p.err = (int*)a->err;
+  if (p.sync_mode && p.done_counter == nullptr) return -2;
+  int bpc = (148 * 4 + a->num_chunks - 1) / a->num_chunks;
+  if (bpc < 1) bpc = 1;
+  if (bpc > 32) bpc = 32;
+  // Blocks only ever wait on flags written by other GPUs, never on sibling blocks, so the
+  // grid may exceed what is resident at once.
+  allreduce_adam_kernel<<<a->num_chunks * bpc, 256, 0, (cudaStream_t)a->stream>>>(p, bpc);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}

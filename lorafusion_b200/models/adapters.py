@@ -61,7 +61,11 @@ class StackView:
 
 class LoRAArena:
     def __init__(self, cfg: ModelConfig, adapters: Sequence[AdapterSpec], layers: Sequence[int],
-                 device, *, init_b_std: float = 0.0, seed: int = 0, with_optimizer_state: bool = True):
+                 device, *, init_b_std: float = 0.0, seed: int = 0, with_optimizer_state: bool = True,
+                 shared_alloc=None):
+        """``shared_alloc(numel, dtype) -> 1-D tensor`` (optional) provides the memory of the
+        two arenas other ranks must reach -- the fp32 gradients and the bf16 working copy --
+        e.g. from NVLink symmetric memory; everything else is ordinary device memory."""
         self.cfg = cfg
         self.adapters = list(adapters)
         self.layers = list(layers)
@@ -84,8 +88,14 @@ class LoRAArena:
                 self.views[(l, proj)] = StackView(l, proj, K, N, R, self.slot, list(subs), a_off, b_off)
         off = (off + 127) // 128 * 128
         self.numel = off
-        self.work = torch.zeros(off, dtype=torch.bfloat16, device=self.device)
-        self.grad = torch.zeros(off, dtype=torch.float32, device=self.device)
+        if shared_alloc is not None:
+            self.work = shared_alloc(off, torch.bfloat16)
+            self.grad = shared_alloc(off, torch.float32)
+            self.work.zero_()
+            self.grad.zero_()
+        else:
+            self.work = torch.zeros(off, dtype=torch.bfloat16, device=self.device)
+            self.grad = torch.zeros(off, dtype=torch.float32, device=self.device)
         if with_optimizer_state:
             self.master = torch.zeros(off, dtype=torch.float32, device=self.device)
             self.m = torch.zeros(off, dtype=torch.float32, device=self.device)

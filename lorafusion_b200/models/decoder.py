@@ -105,7 +105,8 @@ class DecoderStage:
                  layer_start: int = 0, layer_end: Optional[int] = None, quantize: bool = False,
                  double_quant: bool = True, init_std: float = 0.02, init_b_std: float = 0.0,
                  seed: int = 0, recompute=True, with_optimizer_state: bool = True,
-                 head_chunk_tokens: int = 2048, max_inflight: int = 1, reserve_bytes: int = 24 << 30):
+                 head_chunk_tokens: int = 2048, max_inflight: int = 1, reserve_bytes: int = 24 << 30,
+                 shared_alloc=None):
         self.cfg = cfg
         self.device = torch.device(device)
         self.layer_start = layer_start
@@ -148,7 +149,8 @@ class DecoderStage:
         self.cos, self.sin = rope_tables(cfg, self.device)
         self.arena = LoRAArena(cfg, self.adapters, range(self.layer_start, self.layer_end), self.device,
                                init_b_std=init_b_std, seed=seed,
-                               with_optimizer_state=with_optimizer_state) if self.adapters else None
+                               with_optimizer_state=with_optimizer_state,
+                               shared_alloc=shared_alloc) if self.adapters else None
 
     # ------------------------------------------------------------------ helpers
     def _stack(self, layer: int, proj: str):

@@ -1,0 +1,127 @@
+"""Fused gradient reduce + AdamW + weight broadcast kernel.
+
+On one GPU the data-parallel ranks are emulated by running the kernel once per rank, one
+after another, over all ranks' arenas with the cross-rank flags switched off (kernels that
+wait on one another must never be launched separately on one GPU).  The 2-GPU test launches
+real ranks as child processes with NCCL's NVLS off and plain peer loads in the kernel.
+"""
+
+import os
+import socket
+import subprocess
+import sys
+
+import pytest
+import torch
+
+from lorafusion_b200.models.adapters import LoRAArena
+from lorafusion_b200.models.config import AdapterSpec, get_model_config
+from lorafusion_b200.utils.testing import assert_close
+
+pytestmark = pytest.mark.gpu
+
+
+def _arena(seed=0):
+    cfg = get_model_config("tiny")
+    adapters = [AdapterSpec("a", r=16), AdapterSpec("b", r=8, target_modules=("q_proj", "v_proj", "down_proj"))]
+    return LoRAArena(cfg, adapters, range(cfg.num_layers), "cuda", init_b_std=0.02, seed=seed)
+
+
+@pytest.mark.parametrize("world", [1, 4])
+def test_emulated_ranks_match_allreduce_plus_adamw(world):
+    from lorafusion_b200.parallel.dp_sync import launch_allreduce_adam
+
+    arenas = [_arena() for _ in range(world)]
+    ref = _arena()
+    hp = dict(lr=1e-2, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.05)
+    for step in range(1, 3):
+        g = torch.Generator(device="cuda").manual_seed(step)
+        total = torch.zeros_like(ref.grad)
+        for a in arenas:
+            a.grad.copy_(torch.randn(a.numel, generator=g, device="cuda"))
+            total += a.grad
+        for adapter in range(2):
+            ref.grad.copy_(total)
+            ref.adam_step(adapter, grad_scale=0.25, **hp)
+            for r, a in enumerate(arenas):
+                launch_allreduce_adam(
+                    chunks=a.chunk_table(adapter), grad_ptrs=[x.grad.data_ptr() for x in arenas],
+                    work_ptrs=[x.work.data_ptr() for x in arenas], grad_mc=0, work_mc=0, master=a.master, m=a.m,
+                    v=a.v, flag_ptrs=None, done_counter=None, rank=r, world=world, epoch=0, sync=False,
+                    use_multimem=False, step=step, grad_scale=0.25, device="cuda", **hp)
+            # restore the other adapter's gradients consumed from `total` bookkeeping
+            chunks = ref.chunk_table(adapter).cpu()
+            for off, rows, ld, _, _ in chunks.tolist():
+                total[off:off + rows * ld] = 0
+                for a in arenas:
+                    assert float(a.grad[off:off + rows * ld].abs().max()) == 0.0
+    for a in arenas:
+        assert_close(a.work, ref.work, msg="bf16 working copies after the fused step")
+    # every optimizer-state element is owned by exactly one rank: stitched masters == reference
+    stitched = torch.zeros_like(ref.master)
+    touched = torch.zeros_like(ref.master, dtype=torch.bool)
+    base = _arena()
+    for a in arenas:
+        diff = a.master != base.master
+        stitched[diff] = a.master[diff]
+        touched |= diff
+    assert_close(stitched[touched], ref.master[touched], rtol=1e-5, atol=1e-6, msg="sharded master weights")
+
+
+_CHILD = r"""
+import os, sys, torch, torch.distributed as dist
+os.environ["NCCL_NVLS_ENABLE"] = "0"
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(rank)
+dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
+from lorafusion_b200.models.adapters import LoRAArena
+from lorafusion_b200.models.config import AdapterSpec, get_model_config
+from lorafusion_b200.parallel.dp_sync import FusedGradSync
+from lorafusion_b200.parallel.symmetric import SymmetricAllocator
+from lorafusion_b200.train.trainer import OptimizerConfig
+from lorafusion_b200.ops import _native
+cfg = get_model_config("tiny")
+adapters = [AdapterSpec("a", r=16), AdapterSpec("b", r=8)]
+alloc = SymmetricAllocator(f"cuda:{rank}", dist.group.WORLD)
+arena = LoRAArena(cfg, adapters, range(cfg.num_layers), f"cuda:{rank}", init_b_std=0.02, seed=0, shared_alloc=alloc)
+ref = LoRAArena(cfg, adapters, range(cfg.num_layers), f"cuda:{rank}", init_b_std=0.02, seed=0)
+opt = OptimizerConfig(lr=1e-2, beta1=0.9, beta2=0.95, weight_decay=0.05)
+sync = FusedGradSync(arena, alloc, dist.group.WORLD, opt, use_multimem=False)
+for step in range(1, 4):
+    g = torch.Generator(device="cuda").manual_seed(100 * step + rank)
+    arena.grad.copy_(torch.randn(arena.numel, generator=g, device="cuda"))
+    total = arena.grad.clone()
+    dist.all_reduce(total)
+    for adapter in range(2):
+        ref.grad.copy_(total)
+        ref.adam_step(adapter, lr=opt.lr, beta1=opt.beta1, beta2=opt.beta2, eps=opt.eps,
+                      weight_decay=opt.weight_decay, grad_scale=0.5)
+        sync.reduce_and_step(adapter, grad_scale=0.5)
+    torch.cuda.synchronize()
+    _native.check_device_errors()
+    err = (arena.work.float() - ref.work.float()).abs().max().item()
+    assert err < 1e-2, f"rank {rank} step {step}: work copy differs by {err}"
+    assert arena.grad.abs().max().item() == 0.0
+dist.barrier()
+dist.destroy_process_group()
+print(f"rank {rank} ok")
+"""
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_two_real_ranks_over_peer_memory(tmp_path):
+    script = tmp_path / "child.py"
+    script.write_text(_CHILD)
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    procs = []
+    for r in range(2):
+        env = dict(os.environ, RANK=str(r), WORLD_SIZE="2", LOCAL_RANK=str(r), MASTER_ADDR="127.0.0.1",
+                   MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0",
+                   PYTHONPATH=os.pathsep.join([os.getcwd(), os.environ.get("PYTHONPATH", "")]))
+        procs.append(subprocess.Popen([sys.executable, str(script)], env=env, stdout=subprocess.PIPE,
+                                      stderr=subprocess.STDOUT, text=True))
+    outs = [p.communicate(timeout=300)[0] for p in procs]
+    for r, (p, o) in enumerate(zip(procs, outs)):
+        assert p.returncode == 0, f"rank {r} failed:\n{o[-3000:]}"
