@@ -49,6 +49,9 @@ def parse_args():
     ap.add_argument("--recompute", default="auto", choices=["auto", "all", "none"],
                     help="activation recomputation: all layers, none, or as memory allows")
     ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--grad-sync", default="auto", choices=["auto", "fused", "nccl"],
+                    help="DP gradient path: fused reduce+Adam kernel over peer memory, or NCCL all-reduce")
+    ap.add_argument("--multimem", action="store_true", help="use NVLS multimem loads/stores in the fused sync")
     return ap.parse_args()
 
 
@@ -178,7 +181,8 @@ def main():
     t0 = time.time()
     trainer = MultiLoRATrainer(cfg, adapters, device, quantize=not args.no_quantize,
                                recompute={'auto': 'auto', 'all': True, 'none': False}[args.recompute], optim=OptimizerConfig(lr=1e-4),
-                               dp_group=dist.group.WORLD if world > 1 else None, seed=1234, init_b_std=0.01)
+                               dp_group=dist.group.WORLD if world > 1 else None, seed=1234, init_b_std=0.01,
+                               grad_sync=args.grad_sync, use_multimem=args.multimem)
     torch.cuda.synchronize()
     if rank == 0:
         print(f"[bench] model {cfg.name} built in {time.time() - t0:.1f}s, base weights "
@@ -257,6 +261,7 @@ def main():
             "seq_len": "lognormal medians 256/512/1024/2048, sigma 0.5-0.8, clip [32,8192], packed",
             "parallelism": f"dp{world}",
             "adapters": "4 x LoRA r16 alpha32 dropout %.2f on q,k,v,o,gate,up,down" % args.dropout,
+            "grad_sync": trainer.grad_sync,
             "recompute": args.recompute,
             "layers_without_recompute": trainer.stage._plan_keep(args.capacity),
             "l2": "inputs (frozen base weights) far larger than L2",

@@ -33,18 +33,32 @@ class OptimizerConfig:
 class MultiLoRATrainer:
     def __init__(self, cfg: ModelConfig, adapters: Sequence[AdapterSpec], device, *,
                  quantize: bool = False, recompute=True, optim: Optional[OptimizerConfig] = None,
-                 dp_group=None, seed: int = 0, init_b_std: float = 0.0, grad_sync: str = "auto"):
+                 dp_group=None, seed: int = 0, init_b_std: float = 0.0, grad_sync: str = "auto",
+                 use_multimem: bool = False):
         self.cfg = cfg
         self.adapters = list(adapters)
         self.device = torch.device(device)
         self.optim = optim or OptimizerConfig()
         self.dp_group = dp_group
         self.dp_size = dist.get_world_size(dp_group) if (dist.is_initialized() and dp_group is not None) else 1
+        # grad_sync: "fused" = one reduce+Adam+broadcast kernel per adapter over NVLink peer
+        # memory (default when dp > 1), "nccl" = NCCL all-reduce then the local Adam kernel
+        # (the unfused baseline), "auto" = fused when dp > 1.
+        self.grad_sync = ("fused" if self.dp_size > 1 else "local") if grad_sync == "auto" else grad_sync
+        alloc = None
+        if self.grad_sync == "fused":
+            from ..parallel.symmetric import SymmetricAllocator
+
+            alloc = SymmetricAllocator(self.device, dp_group)
         self.stage = DecoderStage(cfg, adapters, device, quantize=quantize, recompute=recompute, seed=seed,
-                                  init_b_std=init_b_std)
-        self.grad_sync = grad_sync
+                                  init_b_std=init_b_std, shared_alloc=alloc)
         self.step_count = 0
         self._fused_sync = None
+        if self.grad_sync == "fused" and self.stage.arena is not None:
+            from ..parallel.dp_sync import FusedGradSync
+
+            self._fused_sync = FusedGradSync(self.stage.arena, alloc, dp_group, self.optim,
+                                             use_multimem=use_multimem)
 
     # ------------------------------------------------------------------ data movement
     def stage_batches(self, specs: Sequence[MicroBatchSpec], seed: int) -> list:
@@ -76,11 +90,11 @@ class MultiLoRATrainer:
         active = range(len(self.adapters)) if active_adapters is None else active_adapters
         scale = 1.0 / (max(num_microbatches, 1) * self.dp_size)
         o = self.optim
+        if self._fused_sync is not None:
+            for a in active:
+                self._fused_sync.reduce_and_step(a, grad_scale=scale)
+            return
         if self.dp_size > 1:
-            if self._fused_sync is not None:
-                for a in active:
-                    self._fused_sync.reduce_and_step(a, grad_scale=scale)
-                return
             dist.all_reduce(arena.grad, group=self.dp_group)
         for a in active:
             arena.adam_step(a, lr=o.lr, beta1=o.beta1, beta2=o.beta2, eps=o.eps,
