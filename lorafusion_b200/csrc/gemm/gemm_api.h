@@ -57,6 +57,37 @@ typedef struct LfGemmArgs {
 // Returns 0 on success, negative on argument/launch errors.
 int lf_gemm(const LfGemmArgs* args);
 
+// Extra arguments of the tensor-parallel fused variants.  Token rows are split into `world`
+// shards of `tiles_per_shard` 128-row tiles.  All "peer" arrays hold, per rank of the TP
+// group, that rank's device pointer to the same symmetric buffer (entry `rank` is local).
+//   mode 1 (all-gather -> GEMM): `ag_src` is this rank's gathered A buffer [M, ag_cols]
+//     (own shard already in place); the kernel pushes the own shard to `ag_peer_dst[q]` and
+//     signals `ag_peer_flags[q][rank * tiles_per_shard + tile] = epoch`; it waits on its own
+//     `ag_flags`.  `ag2_*` optionally gathers the LoRA slab operand the same way.
+//   mode 2 (GEMM -> reduce-scatter): partial tiles go to `rs_peer_stage[owner]`
+//     ([world, M / world, N] bf16), counters `rs_peer_cnt[owner][rank * tiles_per_shard + tile]`
+//     are incremented once per N tile, and rows owned by this rank are reduced into `rs_out`
+//     (+ optional `rs_residual`) when `rs_cnt` reaches `rs_target`.
+typedef struct LfTpArgs {
+  const void* ag_flags;
+  void* ag_peer_flags[8];
+  const void* ag_src;
+  int64_t ag_ld;
+  void* ag_peer_dst[8];
+  const void* ag2_src;
+  int64_t ag2_ld;
+  void* ag2_peer_dst[8];
+  void* rs_peer_stage[8];
+  void* rs_peer_cnt[8];
+  const void* rs_cnt;
+  void* rs_out;
+  int64_t rs_ldo;
+  const void* rs_residual;
+  int32_t mode, rank, world, tiles_per_shard, epoch, rs_target, ag_cols, ag2_cols;
+} LfTpArgs;
+
+int lf_gemm_tp(const LfGemmArgs* args, const LfTpArgs* tp);
+
 #ifdef __cplusplus
 }
 #endif

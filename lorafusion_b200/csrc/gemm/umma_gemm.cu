@@ -51,7 +51,40 @@ struct GemmKParams {
   float inv_keep;
   uint32_t seed_lo, seed_hi, stream_id;
   int row_offset, col_offset;
+  int m_rotate;  // dense mode: M tiles are visited starting from this tile (wraps around)
   int* err;
+};
+
+// Tensor-parallel fusion (TP != 0).  Token rows are split in `world` shards of
+// `tiles_per_shard` 128-row tiles; shard q belongs to rank q.
+//  TP == 1  all-gather -> GEMM: the A operand (and the LoRA S' operand) of the other ranks'
+//           shards is pushed into this GPU's gathered buffer by their kernels while this one
+//           computes; extra warps push this rank's shard to every peer with plain stores over
+//           NVLink and raise one flag per row tile; the TMA producer waits for the flag of a
+//           tile's source rank before loading it (own shard first).
+//  TP == 2  GEMM -> reduce-scatter: the epilogue stores each bf16 partial tile straight into
+//           the staging buffer of the rank that owns those token rows (peer stores), bumps a
+//           per-(source, row tile) counter there, and once its GEMM tiles are done every CTA
+//           sums the partials of the rows this rank owns (fp32) as they arrive.
+struct TpParams {
+  int rank, world, tiles_per_shard, epoch;
+  const int* ag_flags;
+  int* ag_peer_flags[8];
+  const __nv_bfloat16* ag_src;
+  long long ag_ld;
+  int ag_cols;
+  __nv_bfloat16* ag_peer_dst[8];
+  const __nv_bfloat16* ag2_src;
+  long long ag2_ld;
+  int ag2_cols;
+  __nv_bfloat16* ag2_peer_dst[8];
+  __nv_bfloat16* rs_peer_stage[8];
+  int* rs_peer_cnt[8];
+  const int* rs_cnt;
+  int rs_target;
+  __nv_bfloat16* rs_out;
+  long long rs_ldo;
+  const __nv_bfloat16* rs_residual;
 };
 
 struct TileCoord {
@@ -74,8 +107,10 @@ __device__ __forceinline__ TileCoord decode_tile(const GemmKParams& p, int idx) 
   const int first_m = g * p.group_m;
   const int gsz = min(p.group_m, p.num_m_tiles - first_m);
   const int r = idx - g * per_group;
-  const int m_tile = first_m + r % gsz;
+  int m_tile = first_m + r % gsz;
   const int n_tile = r / gsz;
+  m_tile += p.m_rotate;
+  if (m_tile >= p.num_m_tiles) m_tile -= p.num_m_tiles;
   t.m0 = m_tile * BM;
   t.n0 = n_tile;  // multiplied by BN by the caller (BN is a template constant there)
   t.k0 = 0;
@@ -94,12 +129,16 @@ struct SmemPlan {
   static constexpr int TOTAL = STAGES * STAGE_BYTES + BAR_BYTES + 1024;  // + alignment slack
 };
 
-template <int BN, int NACC, bool A_MN, bool B_MN, bool B2_MN, int EPI, bool MASK_A>
-__global__ void __launch_bounds__(MASK_A ? (192 + 32 * kNumMaskWarps) : 192, 1)
+constexpr int kNumCommWarps = 4;
+
+template <int BN, int NACC, bool A_MN, bool B_MN, bool B2_MN, int EPI, bool MASK_A, int TP = 0>
+__global__ void __launch_bounds__(MASK_A ? (192 + 32 * kNumMaskWarps)
+                                         : (TP == 1 ? 192 + 32 * kNumCommWarps : 192), 1)
     umma_gemm_kernel(const GemmKParams p, const __grid_constant__ CUtensorMap tmA,
                      const __grid_constant__ CUtensorMap tmB,
                      const __grid_constant__ CUtensorMap tmA2,
-                     const __grid_constant__ CUtensorMap tmB2) {
+                     const __grid_constant__ CUtensorMap tmB2, const TpParams tp) {
+  static_assert(!(MASK_A && TP != 0), "dropout-in-smem and TP fusion are not combined");
   using Plan = SmemPlan<BN>;
   constexpr int STAGES = Plan::STAGES;
   // Two accumulator buffers whenever TMEM (512 columns) has room; the 256-wide
@@ -166,6 +205,18 @@ __global__ void __launch_bounds__(MASK_A ? (192 + 32 * kNumMaskWarps) : 192, 1)
         const int by2 = (t.adapter >= 0) ? t.adapter * p.b2_adapter_rows : 0;
         const int nkb = (t.adapter < 0 && p.b_adapter_rows > 0) ? 0 : t.nkb;
         const int total = nkb + nkb2;
+        if (TP == 1) {
+          const int mt = t.m0 / BM;
+          const int src = mt / tp.tiles_per_shard;
+          if (src != tp.rank) {
+            if (!wait_flag_ge(tp.ag_flags + src * tp.tiles_per_shard + (mt - src * tp.tiles_per_shard),
+                              tp.epoch, ctx)) {
+              ok = false;
+              break;
+            }
+            fence_proxy_async_all();
+          }
+        }
         for (int kb = 0; kb < total; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
@@ -357,6 +408,11 @@ __global__ void __launch_bounds__(MASK_A ? (192 + 32 * kNumMaskWarps) : 192, 1)
           }
           if (row < p.M) {
             __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.out) + (long long)row * p.ldo;
+            if (TP == 2) {
+              const int ms = tp.tiles_per_shard * BM;
+              const int owner = row / ms;
+              out = tp.rs_peer_stage[owner] + ((long long)tp.rank * ms + (row - owner * ms)) * p.N;
+            }
 #pragma unroll
             for (int g = 0; g < 4; ++g) {
               const int col = col0 + g * 8;
@@ -375,6 +431,98 @@ __global__ void __launch_bounds__(MASK_A ? (192 + 32 * kNumMaskWarps) : 192, 1)
       }
       tc_fence_before_sync();
       mbar_arrive(&tempty[buf]);
+      if (TP == 2) {
+        // all 128 epilogue threads have stored their rows of this partial tile
+        __threadfence_system();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (threadIdx.x == 64) {
+          const int mt = t.m0 / BM;
+          const int owner = mt / tp.tiles_per_shard;
+          red_release_sys_add(tp.rs_peer_cnt[owner] + tp.rank * tp.tiles_per_shard +
+                                  (mt - owner * tp.tiles_per_shard), 1);
+        }
+      }
+    }
+    if (TP == 2 && ok) {
+      // ---- reduce the partials of the rows this rank owns, as they arrive ----
+      const int et = threadIdx.x - 64;  // 0..127
+      const int ms = tp.tiles_per_shard * BM;
+      const int items = tp.tiles_per_shard * p.num_n_tiles;
+      constexpr int VEC_PER_ROW = BN / 8;
+      for (int item = blockIdx.x; ok && item < items; item += gridDim.x) {
+        const int lt = item / p.num_n_tiles, nt = item - lt * p.num_n_tiles;
+        if (et < tp.world) {
+          if (!wait_flag_ge(tp.rs_cnt + et * tp.tiles_per_shard + lt, tp.rs_target, ctx)) ok = false;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (aborted(ctx)) {
+          ok = false;
+          break;
+        }
+        for (int v = et; v < BM * VEC_PER_ROW; v += 128) {
+          const int lr = lt * BM + v / VEC_PER_ROW;
+          const int col = nt * BN + (v % VEC_PER_ROW) * 8;
+          if (col >= p.N) continue;
+          float acc[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+          for (int src = 0; src < tp.world; ++src) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(
+                tp.rs_peer_stage[tp.rank] + ((long long)src * ms + lr) * p.N + col);
+            const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float2 f = unpack_bf16x2(w[j]);
+              acc[2 * j] += f.x;
+              acc[2 * j + 1] += f.y;
+            }
+          }
+          if (tp.rs_residual != nullptr) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(tp.rs_residual + (long long)lr * tp.rs_ldo + col);
+            const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float2 f = unpack_bf16x2(w[j]);
+              acc[2 * j] += f.x;
+              acc[2 * j + 1] += f.y;
+            }
+          }
+          st_global_v4(tp.rs_out + (long long)lr * tp.rs_ldo + col, pack_bf16x2(acc[0], acc[1]),
+                       pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7]));
+        }
+      }
+    }
+  } else if (TP == 1 && !MASK_A) {
+    // ------------- push this rank's token shard to every peer's gathered buffer -------------
+    const int ct = threadIdx.x - 192;  // 0..127
+    const int ms = tp.tiles_per_shard * BM;
+    for (int lt = blockIdx.x; lt < tp.tiles_per_shard; lt += gridDim.x) {
+      const long long row0 = (long long)tp.rank * ms + lt * BM;
+      const int vec_per_row = tp.ag_cols / 8;
+      for (int v = ct; v < BM * vec_per_row; v += 32 * kNumCommWarps) {
+        const long long off = (row0 + v / vec_per_row) * tp.ag_ld + (v % vec_per_row) * 8;
+        const uint4 val = *reinterpret_cast<const uint4*>(tp.ag_src + off);
+        for (int d = 1; d < tp.world; ++d) {
+          const int q = (tp.rank + d) % tp.world;
+          *reinterpret_cast<uint4*>(tp.ag_peer_dst[q] + off) = val;
+        }
+      }
+      if (tp.ag2_src != nullptr) {
+        const int vec2 = tp.ag2_cols / 8;
+        for (int v = ct; v < BM * vec2; v += 32 * kNumCommWarps) {
+          const long long off = (row0 + v / vec2) * tp.ag2_ld + (v % vec2) * 8;
+          const uint4 val = *reinterpret_cast<const uint4*>(tp.ag2_src + off);
+          for (int d = 1; d < tp.world; ++d) {
+            const int q = (tp.rank + d) % tp.world;
+            *reinterpret_cast<uint4*>(tp.ag2_peer_dst[q] + off) = val;
+          }
+        }
+      }
+      __threadfence_system();
+      asm volatile("bar.sync 2, 128;" ::: "memory");
+      if (ct < tp.world && ct != tp.rank) {
+        st_release_sys(tp.ag_peer_flags[ct] + tp.rank * tp.tiles_per_shard + lt, tp.epoch);
+      }
     }
   } else if (MASK_A) {
     // ------------------- dropout mask applied to the A stage in place -------------------
@@ -460,11 +608,11 @@ __global__ void __launch_bounds__(MASK_A ? (192 + 32 * kNumMaskWarps) : 192, 1)
 // ------------------------------------------------------------------------------------
 // host side
 // ------------------------------------------------------------------------------------
-template <int BN, int NACC, bool A_MN, bool B_MN, bool B2_MN, int EPI, bool MASK_A>
+template <int BN, int NACC, bool A_MN, bool B_MN, bool B2_MN, int EPI, bool MASK_A, int TP = 0>
 static int launch_variant(const GemmKParams& kp, const CUtensorMap& tA, const CUtensorMap& tB,
                           const CUtensorMap& tA2, const CUtensorMap& tB2, int grid,
-                          cudaStream_t stream) {
-  auto kern = umma_gemm_kernel<BN, NACC, A_MN, B_MN, B2_MN, EPI, MASK_A>;
+                          cudaStream_t stream, const TpParams& tp = TpParams()) {
+  auto kern = umma_gemm_kernel<BN, NACC, A_MN, B_MN, B2_MN, EPI, MASK_A, TP>;
   constexpr int smem = SmemPlan<BN>::TOTAL;
   static bool configured = false;
   if (!configured) {
@@ -475,8 +623,8 @@ static int launch_variant(const GemmKParams& kp, const CUtensorMap& tA, const CU
     }
     configured = true;
   }
-  const int threads = MASK_A ? (192 + 32 * kNumMaskWarps) : 192;
-  kern<<<grid, threads, smem, stream>>>(kp, tA, tB, tA2, tB2);
+  const int threads = MASK_A ? (192 + 32 * kNumMaskWarps) : (TP == 1 ? 192 + 32 * kNumCommWarps : 192);
+  kern<<<grid, threads, smem, stream>>>(kp, tA, tB, tA2, tB2, tp);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     fprintf(stderr, "lf_gemm: launch failed: %s\n", cudaGetErrorString(e));
@@ -498,7 +646,14 @@ static int sm_count() {
 
 }  // namespace lf
 
-extern "C" int lf_gemm(const LfGemmArgs* a) {
+static int gemm_entry(const LfGemmArgs* a, const LfTpArgs* t);
+
+extern "C" int lf_gemm(const LfGemmArgs* a) { return gemm_entry(a, nullptr); }
+
+// Tensor-parallel fused variants (all-gather -> GEMM, GEMM -> reduce-scatter).
+extern "C" int lf_gemm_tp(const LfGemmArgs* a, const LfTpArgs* t) { return gemm_entry(a, t); }
+
+static int gemm_entry(const LfGemmArgs* a, const LfTpArgs* t) {
   using namespace lf;
   if (a == nullptr || a->a == nullptr || a->b == nullptr || a->out == nullptr) return -1;
   if (a->bn != 64 && a->bn != 128 && a->bn != 192 && a->bn != 256) return -2;
@@ -554,12 +709,65 @@ extern "C" int lf_gemm(const LfGemmArgs* a) {
   kp.row_offset = a->row_offset;
   kp.col_offset = a->col_offset;
   kp.err = a->err;
+  kp.m_rotate = 0;
   if (kp.num_tiles <= 0) return 0;
 
   int grid = sm_count();
   if (a->max_ctas > 0 && a->max_ctas < grid) grid = a->max_ctas;
   if (kp.num_tiles < grid) grid = kp.num_tiles;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(a->stream);
+
+  if (t != nullptr && t->mode != 0) {
+    if (a->seg_tiles != nullptr || a->mask_a) return -6;
+    if (t->world < 1 || t->world > 8 || t->rank < 0 || t->rank >= t->world) return -7;
+    if (kp.num_m_tiles != t->world * t->tiles_per_shard) return -8;
+    TpParams tp;
+    tp.rank = t->rank;
+    tp.world = t->world;
+    tp.tiles_per_shard = t->tiles_per_shard;
+    tp.epoch = t->epoch;
+    tp.ag_flags = (const int*)t->ag_flags;
+    tp.ag_src = (const __nv_bfloat16*)t->ag_src;
+    tp.ag_ld = t->ag_ld;
+    tp.ag_cols = t->ag_cols;
+    tp.ag2_src = (const __nv_bfloat16*)t->ag2_src;
+    tp.ag2_ld = t->ag2_ld;
+    tp.ag2_cols = t->ag2_cols;
+    for (int r = 0; r < 8; ++r) {
+      tp.ag_peer_flags[r] = (int*)t->ag_peer_flags[r];
+      tp.ag_peer_dst[r] = (__nv_bfloat16*)t->ag_peer_dst[r];
+      tp.ag2_peer_dst[r] = (__nv_bfloat16*)t->ag2_peer_dst[r];
+      tp.rs_peer_stage[r] = (__nv_bfloat16*)t->rs_peer_stage[r];
+      tp.rs_peer_cnt[r] = (int*)t->rs_peer_cnt[r];
+    }
+    tp.rs_cnt = (const int*)t->rs_cnt;
+    tp.rs_target = t->rs_target;
+    tp.rs_out = (__nv_bfloat16*)t->rs_out;
+    tp.rs_ldo = t->rs_ldo;
+    tp.rs_residual = (const __nv_bfloat16*)t->rs_residual;
+    // all-gather: start with this rank's own rows; reduce-scatter: finish with them
+    kp.m_rotate = (t->mode == 1 ? t->rank : (t->rank + 1) % t->world) * t->tiles_per_shard;
+    kp.group_m = t->tiles_per_shard < kp.group_m ? t->tiles_per_shard : kp.group_m;
+    const int tkey = (t->mode << 8) | (a->nacc << 4) | ((a->b_mn ? 1 : 0) << 1) | (a->epi == LF_EPI_BF16_DROPMIX);
+    if (BN != 256 || a->a_mn) return -9;
+    switch (tkey) {
+      case (1 << 8) | (1 << 4) | 0:
+        return launch_variant<256, 1, false, false, false, LF_EPI_BF16, false, 1>(kp, tA, tB, tA2, tB2, grid, st, tp);
+      case (1 << 8) | (1 << 4) | 2:
+        return launch_variant<256, 1, false, true, true, LF_EPI_BF16, false, 1>(kp, tA, tB, tA2, tB2, grid, st, tp);
+      case (1 << 8) | (2 << 4) | 3:
+        return launch_variant<256, 2, false, true, true, LF_EPI_BF16_DROPMIX, false, 1>(kp, tA, tB, tA2, tB2, grid, st, tp);
+      case (2 << 8) | (1 << 4) | 0:
+        return launch_variant<256, 1, false, false, false, LF_EPI_BF16, false, 2>(kp, tA, tB, tA2, tB2, grid, st, tp);
+      case (2 << 8) | (1 << 4) | 2:
+        return launch_variant<256, 1, false, true, true, LF_EPI_BF16, false, 2>(kp, tA, tB, tA2, tB2, grid, st, tp);
+      case (2 << 8) | (2 << 4) | 3:
+        return launch_variant<256, 2, false, true, true, LF_EPI_BF16_DROPMIX, false, 2>(kp, tA, tB, tA2, tB2, grid, st, tp);
+      default:
+        fprintf(stderr, "lf_gemm_tp: no kernel variant for key 0x%x\n", tkey);
+        return -5;
+    }
+  }
 
   const int key = (BN << 16) | (a->nacc << 12) | ((a->a_mn ? 1 : 0) << 11) |
                   ((a->b_mn ? 1 : 0) << 10) | ((a->b2_mn ? 1 : 0) << 9) | (a->epi << 4) |

@@ -30,7 +30,7 @@ def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
     return None if t is None else t.data_ptr()
 
 
-def launch_gemm(
+def fill_gemm_args(
     *,
     a: torch.Tensor,
     b: torch.Tensor,
@@ -68,9 +68,9 @@ def launch_gemm(
     col_offset: int = 0,
     group_m: int = 8,
     max_ctas: int = 0,
-) -> None:
-    """Fill :class:`LfGemmArgs` and launch on the current stream."""
-    lib = nv.cuda_lib()
+) -> nv.LfGemmArgs:
+    """Describe one GEMM launch (operands, epilogue, dropout, scheduling) as a
+    :class:`LfGemmArgs` for the current stream."""
     _check2d(a, "a")
     _check2d(b, "b")
     args = nv.LfGemmArgs()
@@ -111,6 +111,16 @@ def launch_gemm(
     args.stream_id = stream_id & 0xFFFFFFFF
     args.row_offset, args.col_offset = row_offset, col_offset
     args.group_m, args.max_ctas = group_m, max_ctas
+    # keep the operand tensors alive until the struct has been consumed
+    args._keepalive = (a, b, a2, b2, out, tile_adapter, seg_tiles, adapter_scale, bias,
+                       adapter_thresh16, adapter_inv_keep)
+    return args
+
+
+def launch_gemm(**kwargs) -> None:
+    """Fill :class:`LfGemmArgs` (see :func:`fill_gemm_args`) and launch on the current stream."""
+    lib = nv.cuda_lib()
+    args = fill_gemm_args(**kwargs)
     nv.note_launch()
     rc = lib.lf_gemm(C.byref(args))
     if rc != 0:

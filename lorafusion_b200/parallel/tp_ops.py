@@ -1,0 +1,189 @@
+"""Tensor-parallel fused ops: all-gather -> fused base+LoRA GEMM and fused base+LoRA GEMM ->
+reduce-scatter, each as ONE kernel that moves data over NVLink peer memory while it computes
+(``csrc/gemm/umma_gemm.cu``, ``TP`` template parameter).
+
+The reference has no tensor parallelism (``tp`` is hard-wired to 1,
+``benchmarks_paper/bench_multi_gpu.py:624``); these ops exist for the TP x PP configurations
+of the 32B / 70B models.  Activations between them are sequence-parallel: every TP rank holds
+``T / tp`` token rows of the residual stream.
+
+``TpContext`` owns the symmetric buffers (allocated once, reused by every layer):
+
+* ``gather`` ``[T, K_max]``  -- destination of the all-gathered A operand (a rank writes its
+  own shard in place, peers push theirs during the consuming kernel), ``gather2`` for the
+  LoRA ``S'`` / ``dS`` operand, ``ag_flags`` one flag per (source rank, row tile);
+* ``rs_stage`` ``[tp, T / tp, N_max]`` -- where peers deposit partial output tiles for the rows
+  this rank owns, ``rs_cnt`` one counter per (source rank, row tile).
+
+Buffer reuse is safe without extra barriers because all-gather and reduce-scatter uses
+alternate: a rank can only reach the next all-gather after receiving every peer's partials of
+the reduce-scatter in between, which those peers send after they finished reading the
+previous gather (and vice versa).
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from ..ops import _native as nv
+from ..ops.gemm import fill_gemm_args
+from .symmetric import SymmetricBuffer, allocate_symmetric, local_buffer
+
+TILE = 128
+
+
+class LfTpArgs(C.Structure):
+    _fields_ = [
+        ("ag_flags", C.c_void_p),
+        ("ag_peer_flags", C.c_void_p * 8),
+        ("ag_src", C.c_void_p),
+        ("ag_ld", C.c_int64),
+        ("ag_peer_dst", C.c_void_p * 8),
+        ("ag2_src", C.c_void_p),
+        ("ag2_ld", C.c_int64),
+        ("ag2_peer_dst", C.c_void_p * 8),
+        ("rs_peer_stage", C.c_void_p * 8),
+        ("rs_peer_cnt", C.c_void_p * 8),
+        ("rs_cnt", C.c_void_p),
+        ("rs_out", C.c_void_p),
+        ("rs_ldo", C.c_int64),
+        ("rs_residual", C.c_void_p),
+        ("mode", C.c_int32), ("rank", C.c_int32), ("world", C.c_int32), ("tiles_per_shard", C.c_int32),
+        ("epoch", C.c_int32), ("rs_target", C.c_int32), ("ag_cols", C.c_int32), ("ag2_cols", C.c_int32),
+    ]
+
+
+class TpContext:
+    def __init__(self, group, device, *, max_tokens: int, max_features: int, max_rank_width: int = 256):
+        self.group = group
+        self.device = torch.device(device)
+        self.world = dist.get_world_size(group) if (dist.is_initialized() and group is not None) else 1
+        self.rank = dist.get_rank(group) if self.world > 1 else 0
+        if max_tokens % (TILE * self.world):
+            raise ValueError("token count must be a multiple of 128 * tp")
+        self.max_tokens, self.max_features, self.max_rank_width = max_tokens, max_features, max_rank_width
+        alloc = (lambda n, dt: allocate_symmetric(n, dt, self.device, group)) if self.world > 1 else \
+            (lambda n, dt: local_buffer(n, dt, self.device))
+        self.gather: SymmetricBuffer = alloc(max_tokens * max_features, torch.bfloat16)
+        self.gather2: SymmetricBuffer = alloc(max_tokens * max_rank_width, torch.bfloat16)
+        self.rs_stage: SymmetricBuffer = alloc(max_tokens * max_features, torch.bfloat16)
+        n_flags = self.world * (max_tokens // TILE)
+        self.ag_flags: SymmetricBuffer = alloc(n_flags, torch.int32)
+        self.rs_cnt: SymmetricBuffer = alloc(n_flags, torch.int32)
+        self.ag_flags.tensor.zero_()
+        self.rs_cnt.tensor.zero_()
+        self.epoch = 0
+        self.rs_total = 0
+        if self.world > 1:
+            torch.cuda.synchronize(self.device)
+            dist.barrier(group)
+
+    # ---- views a producer kernel writes its own shard into ---------------------------------
+    def shard_rows(self, tokens: int) -> tuple:
+        ms = tokens // self.world
+        return self.rank * ms, (self.rank + 1) * ms
+
+    def gather_view(self, tokens: int, cols: int) -> torch.Tensor:
+        return self.gather.tensor[:tokens * cols].view(tokens, cols)
+
+    def gather2_view(self, tokens: int, cols: int) -> torch.Tensor:
+        return self.gather2.tensor[:tokens * cols].view(tokens, cols)
+
+    def own_gather_rows(self, tokens: int, cols: int) -> torch.Tensor:
+        r0, r1 = self.shard_rows(tokens)
+        return self.gather_view(tokens, cols)[r0:r1]
+
+    def own_gather2_rows(self, tokens: int, cols: int) -> torch.Tensor:
+        r0, r1 = self.shard_rows(tokens)
+        return self.gather2_view(tokens, cols)[r0:r1]
+
+    def _base_args(self, tokens: int) -> LfTpArgs:
+        t = LfTpArgs()
+        t.rank, t.world = self.rank, self.world
+        t.tiles_per_shard = tokens // self.world // TILE
+        return t
+
+
+def _launch(gemm_kwargs: dict, tp: LfTpArgs) -> None:
+    lib = nv.cuda_lib()
+    if not getattr(lib, "_lf_tp_declared", False):
+        lib.lf_gemm_tp.argtypes = [C.POINTER(nv.LfGemmArgs), C.POINTER(LfTpArgs)]
+        lib.lf_gemm_tp.restype = C.c_int
+        lib._lf_tp_declared = True
+    args = fill_gemm_args(**gemm_kwargs)
+    nv.note_launch()
+    rc = lib.lf_gemm_tp(C.byref(args), C.byref(tp))
+    if rc != 0:
+        raise RuntimeError(f"lf_gemm_tp failed with code {rc}")
+
+
+def ag_gemm(ctx: TpContext, tokens: int, k: int, w: torch.Tensor, *, w_mn: bool = False,
+            slab_cols: int = 0, b2: Optional[torch.Tensor] = None, b2_adapter_rows: int = 0,
+            tile_adapter: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None,
+            dropout_kwargs: Optional[dict] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``out[T, N] = gathered_A[T, k] @ W (+ gathered_slab[T, R] @ B2)``.
+
+    The caller has already written this rank's rows of A into ``ctx.own_gather_rows(tokens,
+    k)`` (and of the slab operand into ``ctx.own_gather2_rows(tokens, slab_cols)``); the
+    kernel pushes them to the peers and consumes the peers' rows as they land.  ``w`` is
+    ``[N, k]`` (``w_mn=False``) or ``[k, N]`` consumed MN-major (``w_mn=True``, used for
+    ``dY_full @ W_shard`` in the backward)."""
+    a = ctx.gather_view(tokens, k)
+    N = w.shape[1] if w_mn else w.shape[0]
+    if out is None:
+        out = torch.empty((tokens, N), dtype=torch.bfloat16, device=ctx.device)
+    ctx.epoch += 1
+    tp = ctx._base_args(tokens)
+    tp.mode, tp.epoch = 1, ctx.epoch
+    tp.ag_flags = ctx.ag_flags.tensor.data_ptr()
+    tp.ag_src, tp.ag_ld, tp.ag_cols = a.data_ptr(), k, k
+    for r in range(ctx.world):
+        tp.ag_peer_flags[r] = ctx.ag_flags.peer_ptrs[r]
+        tp.ag_peer_dst[r] = ctx.gather.peer_ptrs[r]
+        tp.ag2_peer_dst[r] = ctx.gather2.peer_ptrs[r]
+    kw = dict(a=a, b=w, out=out, M=tokens, N=N, K=k, b_mn=w_mn, b2_mn=w_mn, bn=256, bias=bias,
+              tile_adapter=tile_adapter)
+    if slab_cols:
+        a2 = ctx.gather2_view(tokens, slab_cols)
+        tp.ag2_src, tp.ag2_ld, tp.ag2_cols = a2.data_ptr(), slab_cols, slab_cols
+        kw.update(a2=a2, b2=b2.reshape(-1, b2.shape[-1]), K2=slab_cols, b2_adapter_rows=b2_adapter_rows)
+    if dropout_kwargs:
+        kw.update(nacc=2, epi=nv.EPI_BF16_DROPMIX, **dropout_kwargs)
+    _launch(kw, tp)
+    return out
+
+
+def gemm_rs(ctx: TpContext, x: torch.Tensor, w: torch.Tensor, *, w_mn: bool = False,
+            s: Optional[torch.Tensor] = None, b2: Optional[torch.Tensor] = None, b2_adapter_rows: int = 0,
+            tile_adapter: Optional[torch.Tensor] = None, dropout_kwargs: Optional[dict] = None,
+            residual: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``out[T / tp, N] = reduce_scatter_over_tp(x[T, k_local] @ W_local (+ s @ B2))
+    (+ residual)``: this rank's rows of the sum of all ranks' partial products."""
+    tokens, k = x.shape
+    N = w.shape[1] if w_mn else w.shape[0]
+    ms = tokens // ctx.world
+    if out is None:
+        out = torch.empty((ms, N), dtype=torch.bfloat16, device=ctx.device)
+    n_tiles = (N + 255) // 256
+    ctx.rs_total += n_tiles
+    tp = ctx._base_args(tokens)
+    tp.mode, tp.rs_target = 2, ctx.rs_total
+    tp.rs_cnt = ctx.rs_cnt.tensor.data_ptr()
+    tp.rs_out, tp.rs_ldo = out.data_ptr(), out.stride(0)
+    tp.rs_residual = residual.data_ptr() if residual is not None else None
+    for r in range(ctx.world):
+        tp.rs_peer_stage[r] = ctx.rs_stage.peer_ptrs[r]
+        tp.rs_peer_cnt[r] = ctx.rs_cnt.peer_ptrs[r]
+    # `out` of the GEMM args is unused in this mode but must be a valid pointer
+    kw = dict(a=x, b=w, out=out, M=tokens, N=N, K=k, b_mn=w_mn, b2_mn=w_mn, bn=256, tile_adapter=tile_adapter,
+              ldo=N)
+    if s is not None:
+        kw.update(a2=s, b2=b2.reshape(-1, b2.shape[-1]), K2=s.shape[1], b2_adapter_rows=b2_adapter_rows)
+    if dropout_kwargs:
+        kw.update(nacc=2, epi=nv.EPI_BF16_DROPMIX, **dropout_kwargs)
+    _launch(kw, tp)
+    return out

@@ -1,0 +1,110 @@
+"""Tensor-parallel fused kernels (all-gather -> GEMM, GEMM -> reduce-scatter) on 2 real GPUs,
+checked against NCCL collectives + fp32 matmul.  Child processes, NVLS off, plain peer
+loads/stores in the kernels."""
+
+import os
+import socket
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+_CHILD = r"""
+import os, torch, torch.distributed as dist
+os.environ["NCCL_NVLS_ENABLE"] = "0"
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(rank)
+dev = torch.device("cuda", rank)
+dist.init_process_group("nccl", device_id=dev)
+from lorafusion_b200.parallel.tp_ops import TpContext, ag_gemm, gemm_rs
+from lorafusion_b200.ops import _native
+from lorafusion_b200.utils.testing import assert_close_two_rounds
+torch.backends.cuda.matmul.allow_tf32 = False
+
+T, K, N, R = 1024, 768, 1280, 64
+ctx = TpContext(dist.group.WORLD, dev, max_tokens=T, max_features=2048)
+ms = T // world
+def rnd(*shape, scale=1.0, seed=0):
+    g = torch.Generator(device=dev).manual_seed(seed)
+    return (torch.randn(*shape, generator=g, device=dev) * scale).to(torch.bfloat16)
+
+for it in range(3):
+    # ---------------- all-gather -> GEMM (+ LoRA slab), NT and NN weight layouts ----------------
+    x_shard = rnd(ms, K, seed=10 * it + rank)
+    s_shard = rnd(ms, R, scale=0.1, seed=100 + 10 * it + rank)
+    w = rnd(N, K, scale=0.05, seed=7 + it)            # same on all ranks (a column shard in real use)
+    b2 = rnd(1, N, R, scale=0.05, seed=8 + it)
+    ctx.own_gather_rows(T, K).copy_(x_shard)
+    ctx.own_gather2_rows(T, R).copy_(s_shard)
+    y = ag_gemm(ctx, T, K, w, slab_cols=R, b2=b2, b2_adapter_rows=N)
+    xs = [torch.empty_like(x_shard) for _ in range(world)]
+    ss = [torch.empty_like(s_shard) for _ in range(world)]
+    dist.all_gather(xs, x_shard); dist.all_gather(ss, s_shard)
+    x_full, s_full = torch.cat(xs).float(), torch.cat(ss).float()
+    ref = x_full @ w.float().t() + s_full @ b2[0].float().t()
+    torch.cuda.synchronize(); _native.check_device_errors()
+    assert_close_two_rounds(y, ref, msg=f"ag_gemm NT it{it}")
+    # gathered buffer now holds every rank's rows
+    assert torch.equal(ctx.gather_view(T, K).float(), x_full)
+
+    wt = rnd(K, N, scale=0.05, seed=9 + it)
+    ctx.own_gather_rows(T, K).copy_(x_shard)
+    y2 = ag_gemm(ctx, T, K, wt, w_mn=True)
+    torch.cuda.synchronize(); _native.check_device_errors()
+    assert_close_two_rounds(y2, x_full @ wt.float(), msg=f"ag_gemm NN it{it}")
+
+    # ---------------- GEMM -> reduce-scatter (+ LoRA slab, + residual) ----------------
+    xa = rnd(T, K, seed=200 + 10 * it + rank)         # this rank's feature shard of the input
+    wa = rnd(N, K, scale=0.05, seed=300 + 10 * it + rank)
+    sa = rnd(T, R, scale=0.1, seed=400 + 10 * it + rank)
+    res = rnd(ms, N, seed=500 + rank)
+    out = gemm_rs(ctx, xa, wa, s=sa, b2=b2, b2_adapter_rows=N, residual=res)
+    part = xa.float() @ wa.float().t() + sa.float() @ b2[0].float().t()
+    # the kernel rounds each rank's partial to bf16 before summing
+    part16 = part.to(torch.bfloat16).float()
+    tot = part16.clone(); dist.all_reduce(tot)
+    ref = tot[rank * ms:(rank + 1) * ms] + res.float()
+    torch.cuda.synchronize(); _native.check_device_errors()
+    assert_close_two_rounds(out, ref, atol=2e-2, msg=f"gemm_rs it{it}")
+dist.barrier()
+dist.destroy_process_group()
+print(f"rank {rank} ok")
+"""
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_ag_gemm_and_gemm_rs_two_ranks(tmp_path):
+    script = tmp_path / "child_tp.py"
+    script.write_text(_CHILD)
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    procs = []
+    for r in range(2):
+        env = dict(os.environ, RANK=str(r), WORLD_SIZE="2", LOCAL_RANK=str(r), MASTER_ADDR="127.0.0.1",
+                   MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0",
+                   PYTHONPATH=os.pathsep.join([os.getcwd(), os.environ.get("PYTHONPATH", "")]))
+        procs.append(subprocess.Popen([sys.executable, str(script)], env=env, stdout=subprocess.PIPE,
+                                      stderr=subprocess.STDOUT, text=True))
+    outs = [p.communicate(timeout=300)[0] for p in procs]
+    for r, (p, o) in enumerate(zip(procs, outs)):
+        assert p.returncode == 0, f"rank {r} failed:\n{o[-3000:]}"
+
+
+def test_world_one_degenerates_to_plain_gemm():
+    """With a single rank the fused variants are ordinary GEMMs (no waits, no peers)."""
+    from lorafusion_b200.parallel.tp_ops import TpContext, ag_gemm, gemm_rs
+    from lorafusion_b200.utils.testing import assert_close_two_rounds
+
+    torch.backends.cuda.matmul.allow_tf32 = False
+    T, K, N = 512, 256, 512
+    ctx = TpContext(None, "cuda", max_tokens=T, max_features=1024)
+    g = torch.Generator(device="cuda").manual_seed(0)
+    x = torch.randn(T, K, generator=g, device="cuda").to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g, device="cuda") * 0.05).to(torch.bfloat16)
+    ctx.own_gather_rows(T, K).copy_(x)
+    assert_close_two_rounds(ag_gemm(ctx, T, K, w), x.float() @ w.float().t(), msg="ag_gemm world 1")
+    assert_close_two_rounds(gemm_rs(ctx, x, w), x.float() @ w.float().t(), msg="gemm_rs world 1")
