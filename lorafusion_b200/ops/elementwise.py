@@ -16,11 +16,12 @@ def _p(t: Optional[torch.Tensor]):
 
 
 def rmsnorm_fwd(x: torch.Tensor, w: torch.Tensor, eps: float, res: Optional[torch.Tensor] = None,
-                want_rstd: bool = True):
+                want_rstd: bool = True, out: Optional[torch.Tensor] = None):
     """``h = x (+ res); y = h * rsqrt(mean(h^2) + eps) * w``.  Returns ``(y, h, rstd)``;
-    ``h`` is ``x`` itself when there is no residual."""
+    ``h`` is ``x`` itself when there is no residual.  ``out`` (contiguous ``[M, H]``) receives
+    ``y`` in place, e.g. this rank's rows of an all-gather buffer."""
     M, H = x.shape
-    y = torch.empty_like(x)
+    y = torch.empty_like(x) if out is None else out
     h = torch.empty_like(x) if res is not None else x
     rstd = torch.empty(M, dtype=torch.float32, device=x.device) if want_rstd else None
     nv.call("lf_rmsnorm_fwd", x.data_ptr(), _p(res), w.data_ptr(), y.data_ptr(),

@@ -78,9 +78,20 @@ class TpContext:
         self.rs_cnt.tensor.zero_()
         self.epoch = 0
         self.rs_total = 0
+        self._last_mode = 0
+        self._fence_word = torch.zeros(1, dtype=torch.int32, device=self.device)
         if self.world > 1:
             torch.cuda.synchronize(self.device)
             dist.barrier(group)
+
+    def order(self, mode: int) -> None:
+        """The reuse argument for the gather / stage buffers needs all-gather and
+        reduce-scatter uses to alternate.  When the same kind is requested twice in a row
+        (e.g. the last backward op of one microbatch and the first forward op of the next are
+        both all-gathers) a one-word all-reduce orders the ranks in between."""
+        if self.world > 1 and mode == self._last_mode:
+            dist.all_reduce(self._fence_word, group=self.group)
+        self._last_mode = mode
 
     # ---- views a producer kernel writes its own shard into ---------------------------------
     def shard_rows(self, tokens: int) -> tuple:
@@ -137,6 +148,7 @@ def ag_gemm(ctx: TpContext, tokens: int, k: int, w: torch.Tensor, *, w_mn: bool 
     if out is None:
         out = torch.empty((tokens, N), dtype=torch.bfloat16, device=ctx.device)
     ctx.epoch += 1
+    ctx.order(1)
     tp = ctx._base_args(tokens)
     tp.mode, tp.epoch = 1, ctx.epoch
     tp.ag_flags = ctx.ag_flags.tensor.data_ptr()
@@ -170,6 +182,7 @@ def gemm_rs(ctx: TpContext, x: torch.Tensor, w: torch.Tensor, *, w_mn: bool = Fa
         out = torch.empty((ms, N), dtype=torch.bfloat16, device=ctx.device)
     n_tiles = (N + 255) // 256
     ctx.rs_total += n_tiles
+    ctx.order(2)
     tp = ctx._base_args(tokens)
     tp.mode, tp.rs_target = 2, ctx.rs_total
     tp.rs_cnt = ctx.rs_cnt.tensor.data_ptr()

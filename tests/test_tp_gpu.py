@@ -108,3 +108,74 @@ def test_world_one_degenerates_to_plain_gemm():
     ctx.own_gather_rows(T, K).copy_(x)
     assert_close_two_rounds(ag_gemm(ctx, T, K, w), x.float() @ w.float().t(), msg="ag_gemm world 1")
     assert_close_two_rounds(gemm_rs(ctx, x, w), x.float() @ w.float().t(), msg="gemm_rs world 1")
+
+
+_CHILD_MODEL = r"""
+import os, torch, torch.distributed as dist
+os.environ["NCCL_NVLS_ENABLE"] = "0"
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(rank)
+dev = torch.device("cuda", rank)
+dist.init_process_group("nccl", device_id=dev)
+from lorafusion_b200.models.config import AdapterSpec, get_model_config
+from lorafusion_b200.models.decoder import DecoderStage
+from lorafusion_b200.models.tp_decoder import TpDecoderStage, _shard_rows
+from lorafusion_b200.train.data import MicroBatchSpec, build_packed_batch
+from lorafusion_b200.ops import _native
+from lorafusion_b200.utils.testing import assert_close_two_rounds
+
+cfg = get_model_config("tiny")
+adapters = [AdapterSpec("lora_0", r=16, lora_alpha=32, dropout=0.1), AdapterSpec("lora_1", r=8, lora_alpha=16)]
+for quantize, recompute in ((False, False), (False, True)):
+    full = DecoderStage(cfg, adapters, dev, quantize=quantize, init_b_std=0.02, seed=3, recompute=False)
+    spec = MicroBatchSpec([(0, [100, 37, 200]), (1, [129, 64, 100])])   # 384 + 384 = 768 tokens
+    batch = build_packed_batch(spec, adapters, cfg.vocab_size, dev, seed=5)
+    assert batch.num_tokens % (128 * world) == 0, batch.num_tokens
+    tp = TpDecoderStage.from_full(full, dist.group.WORLD, max_tokens=batch.num_tokens, recompute=recompute)
+    for step in range(2):          # two microbatches back to back exercise buffer reuse
+        loss_full = full.forward_backward(batch)
+        out, saved = tp.forward(batch)
+        loss_tp, dh = tp.loss_and_grad(out, batch)
+        tp.backward(saved, dh, batch)
+    tp.reduce_replicated_grads()
+    torch.cuda.synchronize(); _native.check_device_errors()
+    assert abs(float(loss_tp) - float(loss_full)) / float(loss_full) < 1e-2, (float(loss_tp), float(loss_full))
+    n = len(adapters)
+    for (l, proj), fv in full.arena.views.items():
+        lv = tp.arena.views[(l, proj)]
+        fa, fb, la, lb = fv.stack.da, fv.stack.db, lv.stack.da, lv.stack.db
+        if proj in ("qkv", "gate_up"):
+            exp_a = fa
+            parts = [s for _, s in fv.subs]
+            exp_b = torch.stack([_shard_rows(fb[i], parts, rank, world) for i in range(n)])
+        else:
+            step_k = fv.K // world
+            exp_a = fa[:, :, rank * step_k:(rank + 1) * step_k]
+            exp_b = fb
+        kw = dict(atol=3e-2, rtol=5e-2, scale_atol_by_rms=True, max_mismatch_ratio=1e-2)
+        assert_close_two_rounds(la, exp_a, msg=f"dA {l} {proj} (quantize={quantize}, recompute={recompute})", **kw)
+        assert_close_two_rounds(lb, exp_b, msg=f"dB {l} {proj} (quantize={quantize}, recompute={recompute})", **kw)
+    del full, tp
+dist.barrier()
+dist.destroy_process_group()
+print(f"rank {rank} ok")
+"""
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_tp_stage_matches_unpartitioned_stage(tmp_path):
+    script = tmp_path / "child_tp_model.py"
+    script.write_text(_CHILD_MODEL)
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    procs = []
+    for r in range(2):
+        env = dict(os.environ, RANK=str(r), WORLD_SIZE="2", LOCAL_RANK=str(r), MASTER_ADDR="127.0.0.1",
+                   MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0",
+                   PYTHONPATH=os.pathsep.join([os.getcwd(), os.environ.get("PYTHONPATH", "")]))
+        procs.append(subprocess.Popen([sys.executable, str(script)], env=env, stdout=subprocess.PIPE,
+                                      stderr=subprocess.STDOUT, text=True))
+    outs = [p.communicate(timeout=600)[0] for p in procs]
+    for r, (p, o) in enumerate(zip(procs, outs)):
+        assert p.returncode == 0, f"rank {r} failed:\n{o[-4000:]}"
