@@ -206,6 +206,22 @@ class LoRAArena:
     def zero_grad(self) -> None:
         self.grad.zero_()
 
+    def adapter_grad_regions(self, adapter: int) -> list:
+        """1-D views of the gradient arena covering every region of ``adapter``."""
+        return [self.grad[off:off + rows * ld] for off, rows, ld, _, _ in self.chunk_table(adapter).tolist()]
+
+    def all_reduce_adapter_grads(self, adapter: int, group) -> None:
+        """NCCL all-reduce of one adapter's gradients (the unfused data-parallel baseline)."""
+        import torch.distributed as dist
+
+        views = self.adapter_grad_regions(adapter)
+        flat = torch.cat(views)
+        dist.all_reduce(flat, group=group)
+        off = 0
+        for v in views:
+            v.copy_(flat[off:off + v.numel()])
+            off += v.numel()
+
     # ------------------------------------------------------------------ per-adapter tensors
     def export_adapter(self, adapter: int) -> dict[str, torch.Tensor]:
         """``{"layers.{l}.{sub}.lora_A": [r, K], "...lora_B": [N_sub, r]}`` (fp32 master if

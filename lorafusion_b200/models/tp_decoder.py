@@ -302,20 +302,21 @@ class TpDecoderStage(DecoderStage):
         return loss, ew.rmsnorm_bwd(dx, h_fin, self.final_norm, rstd)
 
     # ------------------------------------------------------------------ replicated-factor gradients
-    def replicated_grad_views(self) -> list:
+    def replicated_grad_views(self, adapter: Optional[int] = None) -> list:
         """fp32 gradient tensors that are partial sums per TP rank: A of column-parallel and
-        B of row-parallel projections."""
+        B of row-parallel projections (of one adapter, or of all)."""
         out = []
         for (l, proj), v in self.arena.views.items():
-            out.append(v.stack.da if proj in ("qkv", "gate_up") else v.stack.db)
+            g = v.stack.da if proj in ("qkv", "gate_up") else v.stack.db
+            out.append(g if adapter is None else g[adapter])
         return out
 
-    def reduce_replicated_grads(self) -> None:
-        """Sum the partial gradients of replicated LoRA factors over the TP group (call before
-        the optimizer step)."""
+    def reduce_replicated_grads(self, adapter: Optional[int] = None) -> None:
+        """Sum the partial gradients of replicated LoRA factors over the TP group (call right
+        before the optimizer step of ``adapter``; ``None`` = every adapter)."""
         if self.tp <= 1 or self.arena is None:
             return
-        views = self.replicated_grad_views()
+        views = self.replicated_grad_views(adapter)
         flat = torch.cat([v.reshape(-1) for v in views])
         dist.all_reduce(flat, group=self.tp_group)
         off = 0

@@ -93,14 +93,25 @@ class MicroBatchSpec:
 
     segments: list = field(default_factory=list)
     is_empty_marker: bool = False
+    total_multiple: int = TILE   # the packed length is rounded up to this (128 x tp under TP)
 
     @property
     def total_tokens(self) -> int:
         return sum(sum(lens) for _, lens in self.segments)
 
     @property
-    def padded_total_tokens(self) -> int:
+    def segment_padded_tokens(self) -> int:
         return sum(((sum(lens) + TILE - 1) // TILE) * TILE for _, lens in self.segments)
+
+    @property
+    def tail_pad_tokens(self) -> int:
+        """Adapter-less filler rows appended so that the total is a multiple of
+        ``total_multiple`` (their labels are ignored, they form their own sequence)."""
+        return (-self.segment_padded_tokens) % max(self.total_multiple, TILE)
+
+    @property
+    def padded_total_tokens(self) -> int:
+        return self.segment_padded_tokens + self.tail_pad_tokens
 
 
 def stage_host_batch(spec: MicroBatchSpec, vocab_size: int, seed: int, pin: bool = True):
@@ -131,6 +142,11 @@ def stage_host_batch(spec: MicroBatchSpec, vocab_size: int, seed: int, pin: bool
             pos[t:t + pad] = np.arange(pad)
             t += pad
             cu.append(t)
+    tail = spec.tail_pad_tokens
+    if tail:
+        pos[t:t + tail] = np.arange(tail)
+        t += tail
+        cu.append(t)
     assert t == T
     return host, cu, seg_tokens
 
@@ -145,6 +161,9 @@ def build_packed_batch(spec: MicroBatchSpec, adapters: Sequence[AdapterSpec], vo
     host_arr, cu, seg_tokens = host
     dev = host_arr.to(device, non_blocking=True)
     idx = [a for a, _ in spec.segments]
+    if spec.tail_pad_tokens:
+        idx = idx + [-1]
+        seg_tokens = list(seg_tokens) + [spec.tail_pad_tokens]
     info = prepare_multi_lora_batch_info(
         seg_tokens, idx, [adapters[a].r if a >= 0 else 0 for a in idx],
         [adapters[a].dropout if a >= 0 else 0.0 for a in idx],
