@@ -76,7 +76,7 @@ PRESETS: dict[str, ModelConfig] = {
     # miniatures for tests and smoke runs
     "tiny": ModelConfig("tiny", 512, 2, 4, 2, 1024, 1024, 10000.0, None),
     "tiny-qwen": ModelConfig("tiny-qwen", 512, 2, 4, 2, 1024, 1024, 10000.0, None, 1e-6, True),
-    "small": ModelConfig("small", 1024, 4, 8, 2, 2816, 32000, 500000.0, _LLAMA3_SCALING),
+    "small": ModelConfig("small", 1024, 4, 8, 2, 3072, 32000, 500000.0, _LLAMA3_SCALING),
 }
 
 ALIASES = {
