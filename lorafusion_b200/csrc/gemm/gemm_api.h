@@ -65,9 +65,10 @@ int lf_gemm(const LfGemmArgs* args);
 //     signals `ag_peer_flags[q][rank * tiles_per_shard + tile] = epoch`; it waits on its own
 //     `ag_flags`.  `ag2_*` optionally gathers the LoRA slab operand the same way.
 //   mode 2 (GEMM -> reduce-scatter): partial tiles go to `rs_peer_stage[owner]`
-//     ([world, M / world, N] bf16), counters `rs_peer_cnt[owner][rank * tiles_per_shard + tile]`
-//     are incremented once per N tile, and rows owned by this rank are reduced into `rs_out`
-//     (+ optional `rs_residual`) when `rs_cnt` reaches `rs_target`.
+//     ([world, M / world, N] bf16), the flag
+//     `rs_peer_cnt[owner][(rank * tiles_per_shard + tile) * num_n_tiles + n_tile]` is set to
+//     `epoch`, and rows owned by this rank are reduced into `rs_out` (+ optional
+//     `rs_residual`) once the matching flags in `rs_cnt` carry `epoch` (`rs_target` is unused).
 typedef struct LfTpArgs {
   const void* ag_flags;
   void* ag_peer_flags[8];

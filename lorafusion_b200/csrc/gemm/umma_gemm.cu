@@ -63,9 +63,9 @@ struct GemmKParams {
 //           NVLink and raise one flag per row tile; the TMA producer waits for the flag of a
 //           tile's source rank before loading it (own shard first).
 //  TP == 2  GEMM -> reduce-scatter: the epilogue stores each bf16 partial tile straight into
-//           the staging buffer of the rank that owns those token rows (peer stores), bumps a
-//           per-(source, row tile) counter there, and once its GEMM tiles are done every CTA
-//           sums the partials of the rows this rank owns (fp32) as they arrive.
+//           the staging buffer of the rank that owns those token rows (peer stores), raises a
+//           per-(source, row tile, column tile) epoch flag there, and once its GEMM tiles are
+//           done every CTA sums the partials of the rows this rank owns (fp32) as they arrive.
 struct TpParams {
   int rank, world, tiles_per_shard, epoch;
   const int* ag_flags;
@@ -438,8 +438,10 @@ __global__ void __launch_bounds__(MASK_A ? (192 + 32 * kNumMaskWarps)
         if (threadIdx.x == 64) {
           const int mt = t.m0 / BM;
           const int owner = mt / tp.tiles_per_shard;
-          red_release_sys_add(tp.rs_peer_cnt[owner] + tp.rank * tp.tiles_per_shard +
-                                  (mt - owner * tp.tiles_per_shard), 1);
+          st_release_sys(tp.rs_peer_cnt[owner] +
+                             (tp.rank * tp.tiles_per_shard + (mt - owner * tp.tiles_per_shard)) * p.num_n_tiles +
+                             t.n0,
+                         tp.epoch);
         }
       }
     }
@@ -452,7 +454,8 @@ __global__ void __launch_bounds__(MASK_A ? (192 + 32 * kNumMaskWarps)
       for (int item = blockIdx.x; ok && item < items; item += gridDim.x) {
         const int lt = item / p.num_n_tiles, nt = item - lt * p.num_n_tiles;
         if (et < tp.world) {
-          if (!wait_flag_ge(tp.rs_cnt + et * tp.tiles_per_shard + lt, tp.rs_target, ctx)) ok = false;
+          if (!wait_flag_ge(tp.rs_cnt + (et * tp.tiles_per_shard + lt) * p.num_n_tiles + nt, tp.epoch, ctx))
+            ok = false;
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (aborted(ctx)) {

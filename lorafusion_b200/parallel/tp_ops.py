@@ -13,7 +13,10 @@ of the 32B / 70B models.  Activations between them are sequence-parallel: every 
   own shard in place, peers push theirs during the consuming kernel), ``gather2`` for the
   LoRA ``S'`` / ``dS`` operand, ``ag_flags`` one flag per (source rank, row tile);
 * ``rs_stage`` ``[tp, T / tp, N_max]`` -- where peers deposit partial output tiles for the rows
-  this rank owns, ``rs_cnt`` one counter per (source rank, row tile).
+  this rank owns, ``rs_cnt`` one epoch flag per (source rank, row tile, column tile).
+
+Flags carry a per-context epoch that grows with every call, so microbatches of different
+sizes can reuse the same flag words.
 
 Buffer reuse is safe without extra barriers because all-gather and reduce-scatter uses
 alternate: a rank can only reach the next all-gather after receiving every peer's partials of
@@ -73,7 +76,8 @@ class TpContext:
         self.rs_stage: SymmetricBuffer = alloc(max_tokens * max_features, torch.bfloat16)
         n_flags = self.world * (max_tokens // TILE)
         self.ag_flags: SymmetricBuffer = alloc(n_flags, torch.int32)
-        self.rs_cnt: SymmetricBuffer = alloc(n_flags, torch.int32)
+        # one flag per (source rank, row tile, 256-column tile) of a reduce-scatter
+        self.rs_cnt: SymmetricBuffer = alloc(n_flags * ((max_features + 255) // 256), torch.int32)
         self.ag_flags.tensor.zero_()
         self.rs_cnt.tensor.zero_()
         self.epoch = 0
@@ -180,11 +184,12 @@ def gemm_rs(ctx: TpContext, x: torch.Tensor, w: torch.Tensor, *, w_mn: bool = Fa
     ms = tokens // ctx.world
     if out is None:
         out = torch.empty((ms, N), dtype=torch.bfloat16, device=ctx.device)
-    n_tiles = (N + 255) // 256
-    ctx.rs_total += n_tiles
+    if N > ctx.max_features or tokens > ctx.max_tokens:
+        raise ValueError("reduce-scatter larger than the TP context was sized for")
+    ctx.epoch += 1
     ctx.order(2)
     tp = ctx._base_args(tokens)
-    tp.mode, tp.rs_target = 2, ctx.rs_total
+    tp.mode, tp.epoch = 2, ctx.epoch
     tp.rs_cnt = ctx.rs_cnt.tensor.data_ptr()
     tp.rs_out, tp.rs_ldo = out.data_ptr(), out.stride(0)
     tp.rs_residual = residual.data_ptr() if residual is not None else None

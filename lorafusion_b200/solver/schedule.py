@@ -378,9 +378,11 @@ def flatten_schedule(schedule: Sequence[AdapterGroupStepInfo]) -> list:
 def bubble_lemma_violations(flat: Sequence[MicroBatchInfo], num_pipeline_stages: int) -> list:
     """Positions ``pos`` whose microbatch uses global batch ``g`` of some adapter fewer than
     ``num_pipeline_stages`` positions after the last microbatch of its batch ``g - 1`` (the
-    optimizer step of ``g - 1`` would not have finished when ``g`` enters the pipeline), or
-    that mix two global batches of one adapter."""
+    optimizer step of ``g - 1`` would not have finished when ``g`` enters the pipeline), that
+    mix two global batches of one adapter, or that return to batch ``g`` of an adapter after
+    one of its later batches has already started."""
     last_pos: dict = {}
+    newest: dict = {}
     bad = []
     for pos, mb in enumerate(flat):
         seen: dict = {}
@@ -393,6 +395,9 @@ def bubble_lemma_violations(flat: Sequence[MicroBatchInfo], num_pipeline_stages:
             prev = last_pos.get((a, g - 1))
             if prev is not None and pos - prev < num_pipeline_stages:
                 ok = False
+            if g < newest.get(a, g):
+                ok = False  # a global batch may not resume after a later one of the same adapter began
+            newest[a] = max(newest.get(a, g), g)
         if not ok:
             bad.append(pos)
         for a, g in seen.items():
@@ -435,7 +440,11 @@ def apply_merge_pass_for_adapter_group_step_infos(schedule: list, num_pipeline_s
                 moved = tgt.partial_merge(tail) > 0
             if not moved:
                 continue
-            trial = [m for s in schedule for m in s.micro_batch_infos if m.data_samples or m.is_empty_marker]
+            # judge the order the schedule will finally have: inside a group step the
+            # microbatches are sorted by padded size, largest first
+            trial = [m for s in schedule
+                     for m in sorted((x for x in s.micro_batch_infos if x.data_samples or x.is_empty_marker),
+                                     key=lambda x: x.padded_total_tokens, reverse=True)]
             if not _bubble_ok(trial, num_pipeline_stages):
                 tgt.data_samples, tail.data_samples = snap_t, snap_s
     for s in schedule:

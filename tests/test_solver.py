@@ -139,3 +139,23 @@ def test_schedule_roundtrip(tmp_path):
     for suffix in (".json", ".pkl"):
         back = S.load_schedule((tmp_path / S.schedule_name("mix", 4096, 4, 2, 8)).with_suffix(suffix))
         assert [m.data_samples for m in S.flatten_schedule(back)] == [m.data_samples for m in S.flatten_schedule(sched)]
+
+
+def test_global_batches_of_an_adapter_never_interleave():
+    """The merge pass may not push leftover samples of batch g behind microbatches of batch g+1
+    of the same adapter (the per-adapter sample counters of the runtime rely on it)."""
+    cap = 4096
+    mk = lambda a, g, k=0: S.MicroBatchInfo({(a, g, k): 1000}, cap)  # noqa: E731
+    flat = [mk(0, 0), mk(1, 0), mk(0, 1), mk(0, 0, 1)]
+    assert S.bubble_lemma_violations(flat, 1) == [3]
+    for seed in range(6):
+        data = _data(batches=4, gbs=8, seed=seed)
+        for stages in (1, 2, 4):
+            sched = S.packing_data_to_microbatches_micro_milp(data, None, 4096, stages, time_limit=0.05)
+            merged = S.apply_merge_pass_for_adapter_group_step_infos(sched, stages)
+            counts = {}
+            for mb in S.flatten_schedule(merged):
+                for (a, g, _k) in mb.data_samples:
+                    counts.setdefault(a, []).append(g)
+            for a, gs in counts.items():
+                assert gs == sorted(gs), (seed, stages, a)
