@@ -51,6 +51,8 @@ def parse_args():
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--grad-sync", default="auto", choices=["auto", "fused", "nccl"],
                     help="DP gradient path: fused reduce+Adam kernel over peer memory, or NCCL all-reduce")
+    ap.add_argument("--lora-mode", default="fused", choices=["fused", "unfused"],
+                    help="unfused = same-GPU baseline: separate base GEMM + cuBLAS LoRA GEMMs + stored mask")
     ap.add_argument("--multimem", action="store_true", help="use NVLS multimem loads/stores in the fused sync")
     return ap.parse_args()
 
@@ -174,6 +176,10 @@ def main():
     from lorafusion_b200.train.data import h2d_bytes
     from lorafusion_b200.train.trainer import MultiLoRATrainer, OptimizerConfig
 
+    if args.lora_mode == "unfused":
+        from lorafusion_b200.ops.lora import set_unfused_baseline
+
+        set_unfused_baseline(True)
     cfg = get_model_config(args.model)
     if args.layers > 0:
         cfg = cfg.with_layers(args.layers)
@@ -262,6 +268,7 @@ def main():
             "parallelism": f"dp{world}",
             "adapters": "4 x LoRA r16 alpha32 dropout %.2f on q,k,v,o,gate,up,down" % args.dropout,
             "grad_sync": trainer.grad_sync,
+            "lora_mode": args.lora_mode,
             "recompute": args.recompute,
             "layers_without_recompute": trainer.stage._plan_keep(args.capacity),
             "l2": "inputs (frozen base weights) far larger than L2",

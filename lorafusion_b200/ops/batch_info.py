@@ -57,6 +57,15 @@ class MultiLoRABatchInfo:
     total_padded_tokens: int = 0
 
     @property
+    def alpha_by_adapter(self) -> dict:
+        """Host-side ``{adapter id: LoRA scaling}`` (no device read)."""
+        return {a: self.alpha_list[i] for i, a in enumerate(self.lora_idx_list) if a >= 0}
+
+    @property
+    def dropout_by_adapter(self) -> dict:
+        return {a: self.dropout_p_list[i] for i, a in enumerate(self.lora_idx_list) if a >= 0}
+
+    @property
     def num_active_adapters(self) -> int:
         return len({i for i in self.lora_idx_list if i >= 0})
 

@@ -22,6 +22,7 @@ on CUDA tensors they always launch the native kernels.
 
 from __future__ import annotations
 
+import os
 import random
 from dataclasses import dataclass
 from typing import Optional, Sequence, Union
@@ -73,11 +74,59 @@ def materialize_weight(w: Weight) -> torch.Tensor:
     return w
 
 
+_UNFUSED = os.environ.get("LORAFUSION_B200_UNFUSED", "0") == "1"
+
+
+def set_unfused_baseline(enabled: bool) -> None:
+    """Switch every LoRA linear of the engine to the unfused baseline (separate base GEMM,
+    stored dropout mask, per-adapter cuBLAS GEMMs for the LoRA branch and elementwise adds) --
+    the stand-in for the reference's "Torch LoRA" / Megatron-LoRA arm when measuring what the
+    fusion buys on the same GPU.  Not used by any default path."""
+    global _UNFUSED
+    _UNFUSED = bool(enabled)
+
+
+def _unfused_forward(x, wd, stack, info, stream_id, bias, training):
+    y = lk.base_lora_fwd(x, wd, None, None, tile_adapter=None, bias=bias)
+    saved = []
+    for a, start, end in info.segments:
+        if a < 0:
+            continue
+        p = info.dropout_by_adapter[a] if training else 0.0
+        xs = x[start:end]
+        xh = torch.nn.functional.dropout(xs, p) if p > 0 else xs
+        mask = (xh != 0) if p > 0 else None
+        sa_ = xh @ stack.a[a].t()
+        y[start:end] += (sa_ @ stack.b[a].t()) * info.alpha_by_adapter[a]
+        saved.append((a, start, end, xh, mask, sa_, p))
+    return y, saved
+
+
+def _unfused_backward(dy, x, saved, wd, stack, info, need_dx):
+    dx = lk.base_lora_dx(dy, wd, None, None, tile_adapter=None) if need_dx else None
+    for a, start, end, xh, mask, sa_, p in saved:
+        alpha = info.alpha_by_adapter[a]
+        dys = dy[start:end]
+        ds = (dys @ stack.b[a]) * alpha
+        if stack.db is not None:
+            stack.db[a] += (dys.t() @ sa_).float() * alpha
+        if stack.da is not None:
+            stack.da[a] += (ds.t() @ xh).float()
+        if need_dx:
+            g = ds @ stack.a[a]
+            if mask is not None:
+                g = g * mask / (1.0 - p)
+            dx[start:end] += g.to(dx.dtype)
+    return dx
+
+
 def lora_linear_forward(x: torch.Tensor, w: Weight, stack: Optional[LoRAStack],
                         info: Optional[MultiLoRABatchInfo], *, stream_id: int = 0,
                         bias: Optional[torch.Tensor] = None, training: bool = True):
     """Returns ``(y, s)``; ``s`` (``[M, R]`` bf16) is what the backward needs besides ``x``."""
     wd = materialize_weight(w)
+    if _UNFUSED and stack is not None and info is not None:
+        return _unfused_forward(x, wd, stack, info, stream_id, bias, training)
     if stack is None or info is None:
         return lk.base_lora_fwd(x, wd, None, None, tile_adapter=None, bias=bias), None
     drop = info.dropout_spec(stream_id, training)
@@ -92,6 +141,8 @@ def lora_linear_backward(dy: torch.Tensor, x: torch.Tensor, s: Optional[torch.Te
                          stream_id: int = 0, need_dx: bool = True, training: bool = True):
     """Accumulates dA/dB into ``stack.da`` / ``stack.db`` and returns ``dX`` (or ``None``)."""
     wd = materialize_weight(w) if need_dx else None
+    if isinstance(s, list):
+        return _unfused_backward(dy, x, s, wd, stack, info, need_dx)
     if stack is None or info is None or s is None:
         return lk.base_lora_dx(dy, wd, None, None, tile_adapter=None) if need_dx else None
     drop = info.dropout_spec(stream_id, training)
