@@ -1,0 +1,432 @@
+// CTA-pair (tcgen05 cta_group::2) version of the hot base+LoRA GEMMs: a cluster of two CTAs
+// on neighbouring SMs computes one 256 x 256 output tile.  Each CTA stages only its own 128
+// rows of A and its own 128 of the 256 B rows (32 KB per 64-deep k-block instead of 48 KB
+// for the single-CTA 128 x 256 tile), the pair MMA reads both halves of B from both CTAs'
+// shared memory, and each CTA ends up with its 128 x 256 fp32 slice in its own TMEM.  The
+// single-CTA kernel (umma_gemm.cu) is operand-bandwidth bound -- 910 TFLOP/s with 128-wide,
+// 1300 with 256-wide tiles on the same problem -- so halving the B traffic per CTA is what
+// moves it towards the tensor-core bound.  No cluster-multicast load is used anywhere: every
+// CTA fetches its own tiles with ordinary tiled TMA loads.
+//
+// Covered ops (the ones that dominate a training step):
+//   forward  Y  = X W^T + S' B_a^T (+ bias)                 B K-major,  one accumulator
+//   dX       dX = dY W + dS A_a                             B MN-major, one accumulator
+//   dX with dropout: second accumulator for dS A_a, Philox mask regenerated in the epilogue
+// Adapters are chosen per 128-row tile, so the two CTAs of a pair may need different LoRA
+// weights: the LoRA slab is issued once per distinct adapter of the pair, and a CTA whose
+// rows belong to another adapter loads zeros for its S' rows (an out-of-range TMA box).
+//
+// Roles per CTA: warp 0 = TMA producer (both CTAs), warp 1 = TMEM allocator (both) and MMA
+// issuer (leader CTA only), warps 2..5 = epilogue (both).  Barriers: "stage full" lives in
+// the leader and is credited by both CTAs' loads; "stage empty" and "accumulator full" exist
+// in both CTAs and are signalled by two tcgen05.commit (own + peer address); "accumulator
+// empty" lives in the leader and collects 256 arrivals.  All waits are bounded.
+#include <stdio.h>
+
+#include "../common/philox.cuh"
+#include "../common/ptx.cuh"
+#include "../common/tensormap.h"
+#include "gemm_api.h"
+
+namespace lf {
+namespace pair {
+
+constexpr int BM = 128;        // rows per CTA
+constexpr int BN = 256;        // columns of the pair tile
+constexpr int BNH = 128;       // B rows staged per CTA
+constexpr int BK = 64;
+constexpr int A_BYTES = BM * BK * 2;
+constexpr int B_BYTES = BNH * BK * 2;
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int STAGES = 6;
+constexpr int SMEM_TOTAL = STAGES * STAGE_BYTES + 512 + 1024;
+
+struct Params {
+  int M, N;
+  int nkb_main, nkb2;
+  int num_pair_m, num_n_tiles, num_tiles, group_m;
+  const int* tile_adapter;  // per 128-row tile, may be null (= adapter 0)
+  int b2_adapter_rows;
+  __nv_bfloat16* out;
+  long long ldo;
+  const __nv_bfloat16* bias;
+  const uint32_t* adapter_thresh16;
+  const float* adapter_inv_keep;
+  uint32_t thresh16;
+  float inv_keep;
+  uint32_t seed_lo, seed_hi, stream_id;
+  int row_offset, col_offset;
+  int zero_row;  // a row coordinate outside A2: TMA reads zeros there
+  int* err;
+};
+
+struct Tile {
+  int pm, n_tile;   // pair-row index (256 rows) and column tile
+  int a0, a1;       // adapters of the leader's and the peer's 128 rows (-1 = none)
+};
+
+__device__ __forceinline__ Tile decode(const Params& p, int idx) {
+  Tile t;
+  const int per_group = p.group_m * p.num_n_tiles;
+  const int g = idx / per_group;
+  const int first = g * p.group_m;
+  const int gsz = min(p.group_m, p.num_pair_m - first);
+  const int r = idx - g * per_group;
+  t.pm = first + r % gsz;
+  t.n_tile = r / gsz;
+  const int mt0 = 2 * t.pm, mt1 = 2 * t.pm + 1;
+  const int n_mt = (p.M + BM - 1) / BM;
+  if (p.nkb2 == 0) {
+    t.a0 = t.a1 = -1;
+  } else if (p.tile_adapter == nullptr) {
+    t.a0 = 0;
+    t.a1 = mt1 < n_mt ? 0 : -1;
+  } else {
+    t.a0 = p.tile_adapter[mt0];
+    t.a1 = mt1 < n_mt ? p.tile_adapter[mt1] : -1;
+  }
+  return t;
+}
+
+// Slab passes of a tile: one per distinct adapter of the pair.
+__device__ __forceinline__ int slab_passes(const Tile& t, int (&ad)[2]) {
+  int n = 0;
+  if (t.a0 >= 0) ad[n++] = t.a0;
+  if (t.a1 >= 0 && t.a1 != t.a0) ad[n++] = t.a1;
+  return n;
+}
+
+template <bool B_MN, int NACC, int EPI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
+    umma_gemm_pair_kernel(const Params p, const __grid_constant__ CUtensorMap tmA,
+                          const __grid_constant__ CUtensorMap tmB,
+                          const __grid_constant__ CUtensorMap tmA2,
+                          const __grid_constant__ CUtensorMap tmB2) {
+  constexpr int NBUF = (NACC == 1) ? 2 : 1;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* full = bars;                 // used in the leader
+  uint64_t* empty = bars + STAGES;       // both
+  uint64_t* tfull = bars + 2 * STAGES;   // both [2]
+  uint64_t* tempty = tfull + 2;          // leader [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t cta = cluster_ctarank();  // 0 = leader
+  const int pair_id = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+  AbortCtx ctx{p.err, abort_flag};
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&tfull[b], 1);
+      mbar_init(&tempty[b], 256);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, 512);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_arrive();   // the peer's barriers exist before anything is signalled remotely
+  cluster_wait();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------ producer (both CTAs) ------------------------------
+    if (lane == 0) {
+      int it = 0;
+      bool ok = true;
+      for (int tile = pair_id; ok && tile < p.num_tiles; tile += num_pairs) {
+        const Tile t = decode(p, tile);
+        const int m0 = (2 * t.pm + int(cta)) * BM;
+        const int n0 = t.n_tile * BN + int(cta) * BNH;
+        int ad[2];
+        const int n_slab = slab_passes(t, ad);
+        const int my_adapter = cta == 0 ? t.a0 : t.a1;
+        const int total = p.nkb_main + n_slab * p.nkb2;
+        for (int kb = 0; kb < total; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&empty[s], ph ^ 1, ctx, ERR_WAIT_EMPTY)) {
+            ok = false;
+            break;
+          }
+          uint8_t* sA = smem + s * STAGE_BYTES;
+          uint8_t* sB = sA + A_BYTES;
+          const uint32_t fbar = mapa_shared(&full[s], 0);
+          if (cta == 0) mbar_expect_tx(&full[s], 2 * STAGE_BYTES);
+          if (kb < p.nkb_main) {
+            const int kk = kb * BK;
+            tma_load_2d_pair(sA, &tmA, fbar, kk, m0);
+            if (!B_MN) {
+              tma_load_2d_pair(sB, &tmB, fbar, kk, n0);
+            } else {
+              tma_load_2d_pair(sB, &tmB, fbar, n0, kk);
+              tma_load_2d_pair(sB + 8192, &tmB, fbar, n0 + 64, kk);
+            }
+          } else {
+            const int sp = (kb - p.nkb_main) / p.nkb2;
+            const int kk2 = ((kb - p.nkb_main) - sp * p.nkb2) * BK;
+            const int a = ad[sp];
+            // rows of another adapter contribute nothing to this pass: read zeros
+            tma_load_2d_pair(sA, &tmA2, fbar, kk2, my_adapter == a ? m0 : p.zero_row);
+            const int by2 = a * p.b2_adapter_rows;
+            if (!B_MN) {
+              tma_load_2d_pair(sB, &tmB2, fbar, kk2, by2 + n0);
+            } else {
+              tma_load_2d_pair(sB, &tmB2, fbar, n0, by2 + kk2);
+              tma_load_2d_pair(sB + 8192, &tmB2, fbar, n0 + 64, by2 + kk2);
+            }
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer (leader only) ------------------------------
+    if (cta == 0 && lane == 0) {
+      constexpr uint32_t IDESC = make_idesc_bf16(256, BN, 0, B_MN ? 1 : 0);
+      int it = 0, tile_iter = 0;
+      bool ok = true;
+      for (int tile = pair_id; ok && tile < p.num_tiles; tile += num_pairs, ++tile_iter) {
+        const Tile t = decode(p, tile);
+        int ad[2];
+        const int n_slab = slab_passes(t, ad);
+        const int total = p.nkb_main + n_slab * p.nkb2;
+        const int buf = tile_iter % NBUF;
+        const uint32_t bph = (tile_iter / NBUF) & 1;
+        if (!mbar_wait(&tempty[buf], bph ^ 1, ctx, ERR_WAIT_TMEM_EMPTY)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t acc0 = tmem_base + uint32_t(buf * BN * NACC);
+        const uint32_t acc1 = acc0 + BN;
+        for (int kb = 0; kb < total; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&full[s], ph, ctx, ERR_WAIT_FULL)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t sA = smem_u32(smem + s * STAGE_BYTES);
+          const uint32_t sB = sA + A_BYTES;
+          const bool slab = kb >= p.nkb_main;
+          const uint32_t d = (NACC == 2 && slab) ? acc1 : acc0;
+#pragma unroll
+          for (int kk = 0; kk < BK / 16; ++kk) {
+            const uint64_t da = make_smem_desc_sw128(sA + kk * 32, 16, 1024);
+            const uint64_t db = B_MN ? make_smem_desc_sw128(sB + kk * 2048, 8192, 1024)
+                                     : make_smem_desc_sw128(sB + kk * 32, 16, 1024);
+            const uint32_t accum = (NACC == 2 && slab) ? uint32_t(kb > p.nkb_main || kk > 0)
+                                                       : uint32_t(kb > 0 || kk > 0);
+            umma_bf16_ss_pair(d, da, db, IDESC, accum);
+          }
+          tc_commit_pair(mapa_shared(&empty[s], 0));
+          tc_commit_pair(mapa_shared(&empty[s], 1));
+        }
+        if (!ok) break;
+        tc_commit_pair(mapa_shared(&tfull[buf], 0));
+        tc_commit_pair(mapa_shared(&tfull[buf], 1));
+      }
+    }
+  } else {
+    // ------------------------------ epilogue (both CTAs) ------------------------------
+    const int q = warp & 3;
+    int tile_iter = 0;
+    bool ok = true;
+    for (int tile = pair_id; ok && tile < p.num_tiles; tile += num_pairs, ++tile_iter) {
+      const Tile t = decode(p, tile);
+      const int my_adapter = cta == 0 ? t.a0 : t.a1;
+      const bool has_slab = p.nkb2 > 0 && my_adapter >= 0;
+      const int buf = tile_iter % NBUF;
+      const uint32_t bph = (tile_iter / NBUF) & 1;
+      if (!mbar_wait(&tfull[buf], bph, ctx, ERR_WAIT_TMEM_FULL)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after_sync();
+      const int row = (2 * t.pm + int(cta)) * BM + q * 32 + lane;
+      const uint32_t lane_addr = uint32_t(q * 32) << 16;
+      const uint32_t acc0 = tmem_base + uint32_t(buf * BN * NACC) + lane_addr;
+      const uint32_t acc1 = acc0 + BN;
+      uint32_t thresh = p.thresh16;
+      float inv_keep = p.inv_keep;
+      if (EPI == LF_EPI_BF16_DROPMIX && my_adapter >= 0 && p.adapter_thresh16 != nullptr) {
+        thresh = p.adapter_thresh16[my_adapter];
+        inv_keep = p.adapter_inv_keep[my_adapter];
+      }
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32], r2[32];
+        tmem_ld_32x32b_x32(acc0 + c * 32, r);
+        if (NACC == 2 && has_slab) tmem_ld_32x32b_x32(acc1 + c * 32, r2);
+        tmem_ld_wait();
+        const int col0 = t.n_tile * BN + c * 32;
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+        if (EPI == LF_EPI_BF16_DROPMIX && NACC == 2 && has_slab) {
+          if (thresh == 0) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] += __uint_as_float(r2[j]);
+          } else {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              const uint32_t keep = dropout_keep8(uint32_t(row + p.row_offset),
+                                                  uint32_t((col0 + p.col_offset) >> 3) + g, p.stream_id,
+                                                  p.seed_lo, p.seed_hi, thresh);
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                if ((keep >> j) & 1u) v[g * 8 + j] += inv_keep * __uint_as_float(r2[g * 8 + j]);
+            }
+          }
+        }
+        if (EPI == LF_EPI_BF16 && p.bias != nullptr) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (col0 + j < p.N) v[j] += __bfloat162float(p.bias[col0 + j]);
+        }
+        if (row < p.M) {
+          __nv_bfloat16* out = p.out + (long long)row * p.ldo;
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            const int col = col0 + g * 8;
+            if (col + 8 <= p.N) {
+              st_global_v4(out + col, pack_bf16x2(v[g * 8 + 0], v[g * 8 + 1]),
+                           pack_bf16x2(v[g * 8 + 2], v[g * 8 + 3]), pack_bf16x2(v[g * 8 + 4], v[g * 8 + 5]),
+                           pack_bf16x2(v[g * 8 + 6], v[g * 8 + 7]));
+            } else {
+              for (int j = 0; j < 8; ++j)
+                if (col + j < p.N) out[col + j] = __float2bfloat16(v[g * 8 + j]);
+            }
+          }
+        }
+      }
+      tc_fence_before_sync();
+      mbar_arrive_cluster(mapa_shared(&tempty[buf], 0));
+    }
+  }
+
+  // ------------------------------ teardown ------------------------------
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag != 0) {
+    const unsigned long long t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  // neither CTA may exit (and release shared memory / barriers) while its partner can still
+  // signal into it
+  cluster_arrive();
+  cluster_wait();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc_pair(tmem_base, 512);
+  }
+}
+
+template <bool B_MN, int NACC, int EPI>
+static int launch(const Params& p, const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tA2,
+                  const CUtensorMap& tB2, int pairs, cudaStream_t st) {
+  auto kern = umma_gemm_pair_kernel<B_MN, NACC, EPI>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL) != cudaSuccess) {
+      fprintf(stderr, "lf_gemm_pair: cudaFuncSetAttribute failed\n");
+      return -10;
+    }
+    configured = true;
+  }
+  kern<<<2 * pairs, 192, SMEM_TOTAL, st>>>(p, tA, tB, tA2, tB2);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    fprintf(stderr, "lf_gemm_pair: launch failed: %s\n", cudaGetErrorString(e));
+    return -11;
+  }
+  return 0;
+}
+
+}  // namespace pair
+}  // namespace lf
+
+// Same argument struct as lf_gemm.  Supported: a / a2 K-major; b and b2 both K-major or both
+// MN-major; bn = 256; epilogues LF_EPI_BF16 (nacc 1) and LF_EPI_BF16_DROPMIX (nacc 2); dense
+// mode only.  Returns -5 for anything else so that callers can fall back to lf_gemm.
+extern "C" int lf_gemm_pair(const LfGemmArgs* a) {
+  using namespace lf;
+  using namespace lf::pair;
+  if (a == nullptr || a->a == nullptr || a->b == nullptr || a->out == nullptr) return -1;
+  if (a->a_mn || a->seg_tiles != nullptr || a->mask_a || a->b_adapter_rows != 0) return -5;
+  if (a->K2 % BK != 0 || (a->K2 > 0 && (a->b_mn != a->b2_mn))) return -5;
+  const bool dropmix = a->epi == LF_EPI_BF16_DROPMIX && a->nacc == 2;
+  if (!dropmix && !(a->epi == LF_EPI_BF16 && a->nacc == 1)) return -5;
+  if (a->scale != 1.0f) return -5;
+
+  CUtensorMap tA, tB, tA2, tB2;
+  int rc = make_tmap_2d_b16(&tA, a->a, a->a_rows, a->a_cols, a->a_ld, BM, 64, true);
+  if (rc != 0) return -20 + rc;
+  rc = make_tmap_2d_b16(&tB, a->b, a->b_rows, a->b_cols, a->b_ld, a->b_mn ? 64 : BNH, 64, true);
+  if (rc != 0) return -30 + rc;
+  if (a->K2 > 0) {
+    rc = make_tmap_2d_b16(&tA2, a->a2, a->a2_rows, a->a2_cols, a->a2_ld, BM, 64, true);
+    if (rc != 0) return -40 + rc;
+    rc = make_tmap_2d_b16(&tB2, a->b2, a->b2_rows, a->b2_cols, a->b2_ld, a->b2_mn ? 64 : BNH, 64, true);
+    if (rc != 0) return -50 + rc;
+  } else {
+    tA2 = tA;
+    tB2 = tB;
+  }
+  Params p;
+  p.M = a->M;
+  p.N = a->N;
+  p.nkb_main = (a->K + BK - 1) / BK;
+  p.nkb2 = a->K2 / BK;
+  p.num_pair_m = (a->M + 2 * BM - 1) / (2 * BM);
+  p.num_n_tiles = (a->N + BN - 1) / BN;
+  p.num_tiles = p.num_pair_m * p.num_n_tiles;
+  p.group_m = a->group_m > 0 ? a->group_m : 4;
+  p.tile_adapter = a->tile_adapter;
+  p.b2_adapter_rows = a->b2_adapter_rows;
+  p.out = (__nv_bfloat16*)a->out;
+  p.ldo = a->ldo;
+  p.bias = (const __nv_bfloat16*)a->bias;
+  p.adapter_thresh16 = a->adapter_thresh16;
+  p.adapter_inv_keep = a->adapter_inv_keep;
+  p.thresh16 = a->thresh16;
+  p.inv_keep = a->inv_keep;
+  p.seed_lo = a->seed_lo;
+  p.seed_hi = a->seed_hi;
+  p.stream_id = a->stream_id;
+  p.row_offset = a->row_offset;
+  p.col_offset = a->col_offset;
+  p.zero_row = int(a->a2_rows) + BM;  // beyond the last row of S': the TMA box reads zeros
+  p.err = a->err;
+  if (p.num_tiles <= 0) return 0;
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  int pairs = sms / 2;
+  if (a->max_ctas > 0 && a->max_ctas / 2 < pairs) pairs = a->max_ctas / 2;
+  if (p.num_tiles < pairs) pairs = p.num_tiles;
+  if (pairs < 1) pairs = 1;
+  cudaStream_t st = (cudaStream_t)a->stream;
+  if (dropmix) {
+    if (!a->b_mn) return -5;
+    return launch<true, 2, LF_EPI_BF16_DROPMIX>(p, tA, tB, tA2, tB2, pairs, st);
+  }
+  if (a->b_mn) return launch<true, 1, LF_EPI_BF16>(p, tA, tB, tA2, tB2, pairs, st);
+  return launch<false, 1, LF_EPI_BF16>(p, tA, tB, tA2, tB2, pairs, st);
+}

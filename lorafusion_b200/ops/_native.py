@@ -123,6 +123,8 @@ _SIGNATURES = {
 def _declare_cuda(lib: C.CDLL) -> None:
     lib.lf_gemm.argtypes = [C.POINTER(LfGemmArgs)]
     lib.lf_gemm.restype = C.c_int
+    lib.lf_gemm_pair.argtypes = [C.POINTER(LfGemmArgs)]
+    lib.lf_gemm_pair.restype = C.c_int
     for name, sig in _SIGNATURES.items():
         fn = getattr(lib, name)
         fn.argtypes = sig

@@ -9,6 +9,7 @@ a transpose copy.
 from __future__ import annotations
 
 import ctypes as C
+import os
 from typing import Optional
 
 import torch
@@ -117,11 +118,33 @@ def fill_gemm_args(
     return args
 
 
-def launch_gemm(**kwargs) -> None:
-    """Fill :class:`LfGemmArgs` (see :func:`fill_gemm_args`) and launch on the current stream."""
+# CTA-pair (tcgen05 cta_group::2, 256 x 256 tiles) kernels for the big GEMMs; "0" disables.
+_PAIR = os.environ.get("LORAFUSION_B200_PAIR", "1") == "1"
+_PAIR_MIN_ROWS = 512
+
+
+def set_pair_kernels(enabled: bool) -> None:
+    """Route eligible GEMMs (256-wide tiles, dense mode, no in-smem dropout) to the CTA-pair
+    kernels of ``csrc/gemm/umma_gemm_pair.cu`` (True) or keep everything on the single-CTA
+    template (False)."""
+    global _PAIR
+    _PAIR = bool(enabled)
+
+
+def launch_gemm(pair: Optional[bool] = None, **kwargs) -> None:
+    """Fill :class:`LfGemmArgs` (see :func:`fill_gemm_args`) and launch on the current stream.
+    ``pair`` overrides the module default for trying the CTA-pair kernel first."""
     lib = nv.cuda_lib()
     args = fill_gemm_args(**kwargs)
     nv.note_launch()
+    use_pair = _PAIR if pair is None else pair
+    if use_pair and args.bn == 256 and args.M >= _PAIR_MIN_ROWS and not args.a_mn and not args.mask_a \
+            and not args.seg_tiles:
+        rc = lib.lf_gemm_pair(C.byref(args))
+        if rc == 0:
+            return
+        if rc != -5:
+            raise RuntimeError(f"lf_gemm_pair failed with code {rc}")
     rc = lib.lf_gemm(C.byref(args))
     if rc != 0:
         raise RuntimeError(f"lf_gemm failed with code {rc}")
