@@ -33,6 +33,10 @@ struct AttnBwdParams {
 };
 
 constexpr int BWD_SMEM = ATT_TILE_BYTES * 7 + 256 + 1024;
+// TMA warp, MMA warp and 8 element-wise warps: two threads per row of S / dP, 64 columns
+// each (warps 2-5 columns 0-63, warps 6-9 columns 64-127; a warp reads the TMEM lane
+// quarter warp % 4).  The backward needs no row reductions, so the halves never talk.
+constexpr int BWD_THREADS = 64 + 256;
 
 // ----------------------------------------------------------------------------------
 __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o,
@@ -56,7 +60,7 @@ __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o,
 // ----------------------------------------------------------------------------------
 // dQ
 // ----------------------------------------------------------------------------------
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(BWD_THREADS, 1)
 attn_dq_kernel(const AttnBwdParams p, const __grid_constant__ CUtensorMap tmQKV,
                const __grid_constant__ CUtensorMap tmDO) {
   extern __shared__ uint8_t smem_raw[];
@@ -92,8 +96,8 @@ attn_dq_kernel(const AttnBwdParams p, const __grid_constant__ CUtensorMap tmQKV,
       mbar_init(&kv_empty[i], 1);
     }
     mbar_init(sdp_full, 1);
-    mbar_init(sdp_empty, 128);
-    mbar_init(ds_full, 128);
+    mbar_init(sdp_empty, 256);
+    mbar_init(ds_full, 256);
     mbar_init(dq_done, 1);
     *abort_flag = 0;
     fence_mbar_init();
@@ -150,6 +154,7 @@ attn_dq_kernel(const AttnBwdParams p, const __grid_constant__ CUtensorMap tmQKV,
     }
   } else {
     const int q = warp & 3;
+    const int c0 = ((warp - 2) >> 2) * 64;
     const int r = q * 32 + lane;
     const uint32_t lane_addr = uint32_t(q * 32) << 16;
     const long long grow = (long long)row0 + r;
@@ -169,20 +174,20 @@ attn_dq_kernel(const AttnBwdParams p, const __grid_constant__ CUtensorMap tmQKV,
       tc_fence_after_sync();
       const bool diag = (j == n_kv - 1);
 #pragma unroll 1
-      for (int cc = 0; cc < 4; ++cc) {
+      for (int cc = 0; cc < 2; ++cc) {
         uint32_t sv[32], dv[32];
-        tmem_ld_32x32b_x32(tS + lane_addr + cc * 32, sv);
-        tmem_ld_32x32b_x32(tDP + lane_addr + cc * 32, dv);
+        tmem_ld_32x32b_x32(tS + lane_addr + c0 + cc * 32, sv);
+        tmem_ld_32x32b_x32(tDP + lane_addr + c0 + cc * 32, dv);
         tmem_ld_wait();
         float ds[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          const int col = cc * 32 + i;
+          const int col = c0 + cc * 32 + i;
           float pv = exp2f(__uint_as_float(sv[i]) * p.scale_log2e - lse2);
           if (!row_valid || (diag && col > r)) pv = 0.f;
           ds[i] = pv * (__uint_as_float(dv[i]) - dlt) * p.scale;
         }
-        att_store_row_chunk(sDS, r, cc * 32, ds);
+        att_store_row_chunk(sDS, r, c0 + cc * 32, ds);
       }
       tc_fence_before_sync();
       mbar_arrive(sdp_empty);
@@ -191,11 +196,11 @@ attn_dq_kernel(const AttnBwdParams p, const __grid_constant__ CUtensorMap tmQKV,
     }
     if (ok && mbar_wait(dq_done, (n_kv - 1) & 1, ctx, ERR_WAIT_MISC)) {
       tc_fence_after_sync();
-      __nv_bfloat16* orow = p.dqkv + grow * p.ld_qkv + p.q_col0 + h * ATT_D;
+      __nv_bfloat16* orow = p.dqkv + grow * p.ld_qkv + p.q_col0 + h * ATT_D + c0;
 #pragma unroll 1
-      for (int cc = 0; cc < 4; ++cc) {
+      for (int cc = 0; cc < 2; ++cc) {
         uint32_t o[32];
-        tmem_ld_32x32b_x32(tDQ + lane_addr + cc * 32, o);
+        tmem_ld_32x32b_x32(tDQ + lane_addr + c0 + cc * 32, o);
         tmem_ld_wait();
         if (row_valid) {
 #pragma unroll
@@ -226,7 +231,7 @@ attn_dq_kernel(const AttnBwdParams p, const __grid_constant__ CUtensorMap tmQKV,
 // ----------------------------------------------------------------------------------
 // dK, dV
 // ----------------------------------------------------------------------------------
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(BWD_THREADS, 1)
 attn_dkdv_kernel(const AttnBwdParams p, const __grid_constant__ CUtensorMap tmQKV,
                  const __grid_constant__ CUtensorMap tmDO) {
   extern __shared__ uint8_t smem_raw[];
@@ -267,10 +272,10 @@ attn_dkdv_kernel(const AttnBwdParams p, const __grid_constant__ CUtensorMap tmQK
       mbar_init(&qd_empty[i], 1);
     }
     mbar_init(sdp_full, 1);
-    mbar_init(sdp_empty, 128);
-    mbar_init(p_full, 128);
+    mbar_init(sdp_empty, 256);
+    mbar_init(p_full, 256);
     mbar_init(dv_done, 1);
-    mbar_init(ds_full, 128);
+    mbar_init(ds_full, 256);
     mbar_init(dk_done, 1);
     *abort_flag = 0;
     fence_mbar_init();
@@ -336,6 +341,8 @@ attn_dkdv_kernel(const AttnBwdParams p, const __grid_constant__ CUtensorMap tmQK
     }
   } else {
     const int q = warp & 3;
+    const int half = (warp - 2) >> 2;
+    const int c0 = half * 64;
     const int r = q * 32 + lane;  // query row inside the current query tile
     const uint32_t lane_addr = uint32_t(q * 32) << 16;
     bool ok = true;
@@ -358,23 +365,23 @@ attn_dkdv_kernel(const AttnBwdParams p, const __grid_constant__ CUtensorMap tmQK
         break;
       }
       tc_fence_after_sync();
-      uint32_t pk[64];  // P of this row as packed bf16 pairs
+      uint32_t pk[32];  // P of this thread's 64 columns as packed bf16 pairs
 #pragma unroll
-      for (int cc = 0; cc < 4; ++cc) {
+      for (int cc = 0; cc < 2; ++cc) {
         uint32_t sv[32];
-        tmem_ld_32x32b_x32(tS + lane_addr + cc * 32, sv);
+        tmem_ld_32x32b_x32(tS + lane_addr + c0 + cc * 32, sv);
         tmem_ld_wait();
         float pv[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          const int col = cc * 32 + i;
+          const int col = c0 + cc * 32 + i;
           float x = exp2f(__uint_as_float(sv[i]) * p.scale_log2e - lse2);
           if (!row_valid || (diag && col > r)) x = 0.f;
           pv[i] = x;
         }
 #pragma unroll
         for (int i = 0; i < 16; ++i) pk[cc * 16 + i] = pack_bf16x2(pv[2 * i], pv[2 * i + 1]);
-        att_store_row_chunk(sPD, r, cc * 32, pv);
+        att_store_row_chunk(sPD, r, c0 + cc * 32, pv);
       }
       fence_proxy_async_smem();
       mbar_arrive(p_full);
@@ -384,9 +391,9 @@ attn_dkdv_kernel(const AttnBwdParams p, const __grid_constant__ CUtensorMap tmQK
       }
       tc_fence_after_sync();
 #pragma unroll
-      for (int cc = 0; cc < 4; ++cc) {
+      for (int cc = 0; cc < 2; ++cc) {
         uint32_t dv[32];
-        tmem_ld_32x32b_x32(tDP + lane_addr + cc * 32, dv);
+        tmem_ld_32x32b_x32(tDP + lane_addr + c0 + cc * 32, dv);
         tmem_ld_wait();
         float ds[32];
 #pragma unroll
@@ -395,7 +402,7 @@ attn_dkdv_kernel(const AttnBwdParams p, const __grid_constant__ CUtensorMap tmQK
           ds[2 * i] = pp.x * (__uint_as_float(dv[2 * i]) - dlt) * p.scale;
           ds[2 * i + 1] = pp.y * (__uint_as_float(dv[2 * i + 1]) - dlt) * p.scale;
         }
-        att_store_row_chunk(sPD, r, cc * 32, ds);
+        att_store_row_chunk(sPD, r, c0 + cc * 32, ds);
       }
       tc_fence_before_sync();
       mbar_arrive(sdp_empty);
@@ -407,8 +414,9 @@ attn_dkdv_kernel(const AttnBwdParams p, const __grid_constant__ CUtensorMap tmQK
       const long long grow = (long long)row0 + r;  // key row owned by this thread
       __nv_bfloat16* krow = p.dqkv + grow * p.ld_qkv + p.k_col0 + g * ATT_D;
       __nv_bfloat16* vrow = p.dqkv + grow * p.ld_qkv + p.v_col0 + g * ATT_D;
+      // the first half of the warps writes dV, the second dK
 #pragma unroll 1
-      for (int cc = 0; cc < 8; ++cc) {
+      for (int cc = half * 4; cc < half * 4 + 4; ++cc) {
         uint32_t o[32];
         const bool is_k = cc >= 4;
         tmem_ld_32x32b_x32((is_k ? tDK : tDV) + lane_addr + (cc & 3) * 32, o);
@@ -488,8 +496,8 @@ extern "C" int lf_attn_bwd(const void* qkv, const void* out, const void* d_out, 
   p.scale = scale;
   p.scale_log2e = scale * 1.4426950408889634f;
   p.err = err;
-  attn_dq_kernel<<<dim3(num_tiles, Hq), 192, BWD_SMEM, st>>>(p, tmQKV, tmDO);
-  attn_dkdv_kernel<<<dim3(num_tiles, Hkv), 192, BWD_SMEM, st>>>(p, tmQKV, tmDO);
+  attn_dq_kernel<<<dim3(num_tiles, Hq), BWD_THREADS, BWD_SMEM, st>>>(p, tmQKV, tmDO);
+  attn_dkdv_kernel<<<dim3(num_tiles, Hkv), BWD_THREADS, BWD_SMEM, st>>>(p, tmQKV, tmDO);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
@@ -574,7 +582,7 @@ extern "C" int lf_attn_bwd_noalloc(const void* qkv, const void* out, const void*
   p.scale = scale;
   p.scale_log2e = scale * 1.4426950408889634f;
   p.err = err;
-  attn_dq_kernel<<<dim3(num_tiles, Hq), 192, BWD_SMEM, st>>>(p, tmQKV, tmDO);
-  attn_dkdv_kernel<<<dim3(num_tiles, Hkv), 192, BWD_SMEM, st>>>(p, tmQKV, tmDO);
+  attn_dq_kernel<<<dim3(num_tiles, Hq), BWD_THREADS, BWD_SMEM, st>>>(p, tmQKV, tmDO);
+  attn_dkdv_kernel<<<dim3(num_tiles, Hkv), BWD_THREADS, BWD_SMEM, st>>>(p, tmQKV, tmDO);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }

@@ -5,9 +5,11 @@
 // One CTA handles one 128-row query tile of one sequence for one query head:
 //   warp 0      TMA producer: Q once, then (K, V) tiles through a 2-stage ring
 //   warp 1      tcgen05.mma issuer: S = Q K^T into one of two TMEM buffers, O += P V
-//   warps 2..5  softmax: read S from TMEM (one row per thread), online max/sum with lazy
-//               rescaling of O (only when the running max grows by more than 2^8), write
-//               bf16 P into swizzled shared memory for the second MMA, final normalise.
+//   warps 2..9  softmax: read S from TMEM (two threads per row, 64 key columns each), online
+//               max/sum with lazy rescaling of O (only when the running max grows by more
+//               than 2^8), write bf16 P into swizzled shared memory for the second MMA,
+//               final normalise.  The exponentials are what bounds this kernel, so the
+//               row is split over two threads rather than left to one.
 // Q/K/V are read straight out of the packed, RoPE-rotated QKV projection with one tensor
 // map; O is written token-major [M, Hq * 128]; the log-sum-exp is kept for the backward.
 #include <stdio.h>
@@ -30,9 +32,11 @@ struct AttnFwdParams {
   int* err;
 };
 
-constexpr int FWD_SMEM = ATT_TILE_BYTES * (1 + 4 + 1) + 256 + 1024;
+constexpr int FWD_THREADS = 64 + 256;  // TMA warp, MMA warp, 8 softmax warps
+constexpr int FWD_XCHG_BYTES = 3 * 256 * 4;  // row-max exchange (2 parities) + row-sum exchange
+constexpr int FWD_SMEM = ATT_TILE_BYTES * (1 + 4 + 1) + 256 + FWD_XCHG_BYTES + 1024;
 
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(FWD_THREADS, 1)
 attn_fwd_kernel(const AttnFwdParams p, const __grid_constant__ CUtensorMap tm) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -48,8 +52,10 @@ attn_fwd_kernel(const AttnFwdParams p, const __grid_constant__ CUtensorMap tm) {
   uint64_t* s_empty = bars + 7;   // [2]
   uint64_t* p_full = bars + 9;
   uint64_t* pv_done = bars + 10;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
+  uint64_t* x_full = bars + 11;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* xchg = reinterpret_cast<float*>(smem + ATT_TILE_BYTES * 6 + 256);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   AbortCtx ctx{p.err, abort_flag};
@@ -65,10 +71,11 @@ attn_fwd_kernel(const AttnFwdParams p, const __grid_constant__ CUtensorMap tm) {
       mbar_init(&kv_full[i], 1);
       mbar_init(&kv_empty[i], 1);
       mbar_init(&s_full[i], 1);
-      mbar_init(&s_empty[i], 128);
+      mbar_init(&s_empty[i], 256);
     }
-    mbar_init(p_full, 128);
+    mbar_init(p_full, 256);
     mbar_init(pv_done, 1);
+    mbar_init(x_full, 256);
     *abort_flag = 0;
     fence_mbar_init();
     tma_prefetch_desc(&tm);
@@ -132,8 +139,14 @@ attn_fwd_kernel(const AttnFwdParams p, const __grid_constant__ CUtensorMap tm) {
       }
     }
   } else {
+    // Two threads per query row: warps 2-5 take key columns 0-63 of each tile, warps 6-9
+    // columns 64-127 (a warp may only touch the TMEM lane quarter warp % 4).  The two
+    // halves agree on the running maximum through shared memory once per tile, keep
+    // private partial row sums, and each rescales / writes its own 64 columns of O.
     const int q = warp & 3;
+    const int half = (warp - 2) >> 2;
     const int r = q * 32 + lane;  // row inside the tile
+    const int c0 = half * 64;
     const uint32_t lane_addr = uint32_t(q * 32) << 16;
     float m_ref = -INFINITY, l = 0.f;
     const float c = p.scale_log2e;
@@ -145,23 +158,30 @@ attn_fwd_kernel(const AttnFwdParams p, const __grid_constant__ CUtensorMap tm) {
         break;
       }
       tc_fence_after_sync();
-      float s[128];
+      float s[64];
 #pragma unroll
-      for (int cc = 0; cc < 4; ++cc) {
+      for (int cc = 0; cc < 2; ++cc) {
         uint32_t(&dst)[32] = *reinterpret_cast<uint32_t(*)[32]>(&s[cc * 32]);
-        tmem_ld_32x32b_x32(tS[b] + lane_addr + cc * 32, dst);
+        tmem_ld_32x32b_x32(tS[b] + lane_addr + c0 + cc * 32, dst);
       }
       tmem_ld_wait();
       tc_fence_before_sync();
       mbar_arrive(&s_empty[b]);
       if (j == n_kv - 1) {
 #pragma unroll
-        for (int col = 0; col < 128; ++col)
-          if (col > r) s[col] = -INFINITY;
+        for (int col = 0; col < 64; ++col)
+          if (c0 + col > r) s[col] = -INFINITY;
       }
       float mx = s[0];
 #pragma unroll
-      for (int col = 1; col < 128; ++col) mx = fmaxf(mx, s[col]);
+      for (int col = 1; col < 64; ++col) mx = fmaxf(mx, s[col]);
+      xchg[b * 256 + half * 128 + r] = mx;
+      mbar_arrive(x_full);
+      if (!mbar_wait(x_full, j & 1, ctx, ERR_WAIT_MISC)) {
+        ok = false;
+        break;
+      }
+      mx = fmaxf(mx, xchg[b * 256 + (half ^ 1) * 128 + r]);
       float alpha = 1.f;
       bool need = false;
       if (j == 0) {
@@ -178,7 +198,7 @@ attn_fwd_kernel(const AttnFwdParams p, const __grid_constant__ CUtensorMap tm) {
       const float mc = m_ref * c;
       float sum = 0.f;
 #pragma unroll
-      for (int col = 0; col < 128; ++col) {
+      for (int col = 0; col < 64; ++col) {
         s[col] = exp2f(s[col] * c - mc);
         sum += s[col];
       }
@@ -191,19 +211,19 @@ attn_fwd_kernel(const AttnFwdParams p, const __grid_constant__ CUtensorMap tm) {
         tc_fence_after_sync();
       }
 #pragma unroll
-      for (int cc = 0; cc < 4; ++cc) {
+      for (int cc = 0; cc < 2; ++cc) {
         float(&src)[32] = *reinterpret_cast<float(*)[32]>(&s[cc * 32]);
-        att_store_row_chunk(sP, r, cc * 32, src);
+        att_store_row_chunk(sP, r, c0 + cc * 32, src);
       }
       if (warp_need) {
 #pragma unroll 1
-        for (int cc = 0; cc < 4; ++cc) {
+        for (int cc = 0; cc < 2; ++cc) {
           uint32_t o[32];
-          tmem_ld_32x32b_x32(tO + lane_addr + cc * 32, o);
+          tmem_ld_32x32b_x32(tO + lane_addr + c0 + cc * 32, o);
           tmem_ld_wait();
 #pragma unroll
           for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-          tmem_st_32x32b_x32(tO + lane_addr + cc * 32, o);
+          tmem_st_32x32b_x32(tO + lane_addr + c0 + cc * 32, o);
         }
         tmem_st_wait();
       }
@@ -211,15 +231,22 @@ attn_fwd_kernel(const AttnFwdParams p, const __grid_constant__ CUtensorMap tm) {
       tc_fence_before_sync();
       mbar_arrive(p_full);
     }
+    if (ok) {
+      // combine the two partial row sums (both were kept relative to the same m_ref)
+      xchg[512 + half * 128 + r] = l;
+      mbar_arrive(x_full);
+      ok = mbar_wait(x_full, n_kv & 1, ctx, ERR_WAIT_MISC);
+      if (ok) l += xchg[512 + (half ^ 1) * 128 + r];
+    }
     if (ok && mbar_wait(pv_done, (n_kv - 1) & 1, ctx, ERR_WAIT_MISC)) {
       tc_fence_after_sync();
       const float inv_l = 1.f / l;
       const long long grow = (long long)row0 + r;
-      __nv_bfloat16* orow = p.out + grow * p.ldo + h * ATT_D;
+      __nv_bfloat16* orow = p.out + grow * p.ldo + h * ATT_D + c0;
 #pragma unroll 1
-      for (int cc = 0; cc < 4; ++cc) {
+      for (int cc = 0; cc < 2; ++cc) {
         uint32_t o[32];
-        tmem_ld_32x32b_x32(tO + lane_addr + cc * 32, o);
+        tmem_ld_32x32b_x32(tO + lane_addr + c0 + cc * 32, o);
         tmem_ld_wait();
         if (r < rows) {
 #pragma unroll
@@ -232,7 +259,7 @@ attn_fwd_kernel(const AttnFwdParams p, const __grid_constant__ CUtensorMap tm) {
           }
         }
       }
-      if (r < rows) p.lse[(long long)h * p.M_total + grow] = m_ref * p.scale + __logf(l);
+      if (half == 0 && r < rows) p.lse[(long long)h * p.M_total + grow] = m_ref * p.scale + __logf(l);
     }
   }
 
@@ -286,6 +313,6 @@ extern "C" int lf_attn_fwd(const void* qkv, long long M, long long ld_qkv, int q
   p.scale_log2e = scale * 1.4426950408889634f;
   p.err = err;
   dim3 grid(num_tiles, Hq);
-  attn_fwd_kernel<<<grid, 192, FWD_SMEM, (cudaStream_t)stream>>>(p, tm);
+  attn_fwd_kernel<<<grid, FWD_THREADS, FWD_SMEM, (cudaStream_t)stream>>>(p, tm);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }

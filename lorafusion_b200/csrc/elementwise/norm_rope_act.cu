@@ -56,6 +56,9 @@ __device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&f)[8]) {
 constexpr int NORM_THREADS = 256;
 constexpr int NORM_MAX_VEC = 8;  // supports H up to 256 * 8 * 8 = 16384
 
+// NV = 16-byte vectors per thread (ceil(H / 8 / 256)); a template so that the row fits in
+// as few registers as the hidden size needs (occupancy is what hides the DRAM latency here).
+template <int NV>
 __global__ void __launch_bounds__(NORM_THREADS)
 rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res,
                    const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y,
@@ -65,10 +68,10 @@ rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
   const long long row = blockIdx.x;
   const __nv_bfloat16* xr = x + row * H;
   const int nvec = H / 8;
-  float v[NORM_MAX_VEC][8];
+  float v[NV][8];
   float ss = 0.f;
 #pragma unroll
-  for (int i = 0; i < NORM_MAX_VEC; ++i) {
+  for (int i = 0; i < NV; ++i) {
     const int c = threadIdx.x + i * NORM_THREADS;
     if (c < nvec) {
       load8(xr + c * 8, v[i]);
@@ -97,7 +100,7 @@ rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
   const float rstd = rsqrtf(ss / float(H) + eps);
   if (threadIdx.x == 0 && rstd_out != nullptr) rstd_out[row] = rstd;
 #pragma unroll
-  for (int i = 0; i < NORM_MAX_VEC; ++i) {
+  for (int i = 0; i < NV; ++i) {
     const int c = threadIdx.x + i * NORM_THREADS;
     if (c < nvec) {
       float wv[8], o[8];
@@ -111,6 +114,7 @@ rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
 
 // RMSNorm backward (no weight grad):
 //   g = dy * w;  dx = rstd * (g - xhat * mean(g * xhat))  (+ dres),  xhat = h * rstd
+template <int NV>
 __global__ void __launch_bounds__(NORM_THREADS)
 rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ h,
                    const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd_in,
@@ -119,10 +123,10 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
   const long long row = blockIdx.x;
   const int nvec = H / 8;
   const float rstd = rstd_in[row];
-  float g[NORM_MAX_VEC][8], xh[NORM_MAX_VEC][8];
+  float g[NV][8], xh[NV][8];
   float dot = 0.f;
 #pragma unroll
-  for (int i = 0; i < NORM_MAX_VEC; ++i) {
+  for (int i = 0; i < NV; ++i) {
     const int c = threadIdx.x + i * NORM_THREADS;
     if (c < nvec) {
       float wv[8];
@@ -139,7 +143,7 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
   }
   dot = block_sum<NORM_THREADS>(dot, red) / float(H);
 #pragma unroll
-  for (int i = 0; i < NORM_MAX_VEC; ++i) {
+  for (int i = 0; i < NV; ++i) {
     const int c = threadIdx.x + i * NORM_THREADS;
     if (c < nvec) {
       float o[8];
@@ -290,9 +294,17 @@ int lf_rmsnorm_fwd(const void* x, const void* res, const void* w, void* y, void*
                    float* rstd, long long M, int H, float eps, void* stream) {
   if (H % 8 != 0 || H > NORM_THREADS * NORM_MAX_VEC * 8) return -1;
   if (M == 0) return 0;
-  rmsnorm_fwd_kernel<<<(unsigned)M, NORM_THREADS, 0, (cudaStream_t)stream>>>(
-      (const __nv_bfloat16*)x, (const __nv_bfloat16*)res, (const __nv_bfloat16*)w,
-      (__nv_bfloat16*)y, (__nv_bfloat16*)h_out, rstd, H, eps);
+  const int nv = (H / 8 + NORM_THREADS - 1) / NORM_THREADS;
+#define LF_NORM_FWD(NVV)                                                                        \
+  rmsnorm_fwd_kernel<NVV><<<(unsigned)M, NORM_THREADS, 0, (cudaStream_t)stream>>>(               \
+      (const __nv_bfloat16*)x, (const __nv_bfloat16*)res, (const __nv_bfloat16*)w,              \
+      (__nv_bfloat16*)y, (__nv_bfloat16*)h_out, rstd, H, eps)
+  if (nv <= 1) LF_NORM_FWD(1);
+  else if (nv == 2) LF_NORM_FWD(2);
+  else if (nv == 3) LF_NORM_FWD(3);
+  else if (nv == 4) LF_NORM_FWD(4);
+  else LF_NORM_FWD(8);
+#undef LF_NORM_FWD
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
@@ -300,9 +312,17 @@ int lf_rmsnorm_bwd(const void* dy, const void* h, const void* w, const float* rs
                    const void* dres, void* dx, long long M, int H, void* stream) {
   if (H % 8 != 0 || H > NORM_THREADS * NORM_MAX_VEC * 8) return -1;
   if (M == 0) return 0;
-  rmsnorm_bwd_kernel<<<(unsigned)M, NORM_THREADS, 0, (cudaStream_t)stream>>>(
-      (const __nv_bfloat16*)dy, (const __nv_bfloat16*)h, (const __nv_bfloat16*)w, rstd,
-      (const __nv_bfloat16*)dres, (__nv_bfloat16*)dx, H);
+  const int nv = (H / 8 + NORM_THREADS - 1) / NORM_THREADS;
+#define LF_NORM_BWD(NVV)                                                                        \
+  rmsnorm_bwd_kernel<NVV><<<(unsigned)M, NORM_THREADS, 0, (cudaStream_t)stream>>>(               \
+      (const __nv_bfloat16*)dy, (const __nv_bfloat16*)h, (const __nv_bfloat16*)w, rstd,         \
+      (const __nv_bfloat16*)dres, (__nv_bfloat16*)dx, H)
+  if (nv <= 1) LF_NORM_BWD(1);
+  else if (nv == 2) LF_NORM_BWD(2);
+  else if (nv == 3) LF_NORM_BWD(3);
+  else if (nv == 4) LF_NORM_BWD(4);
+  else LF_NORM_BWD(8);
+#undef LF_NORM_BWD
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
