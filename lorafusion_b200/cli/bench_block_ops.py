@@ -27,7 +27,7 @@ def run(args):
     dev = torch.device("cuda")
     torch.manual_seed(0)
     T, H, I = args.tokens, cfg.hidden_size, cfg.intermediate_size
-    hq, hkv, d = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+    hq, hkv, d = cfg.num_heads, cfg.num_kv_heads, cfg.head_dim
     n_seq = max(1, T // args.seq_len)
     lens = [args.seq_len] * n_seq
     if sum(lens) < T:

@@ -30,7 +30,7 @@ namespace lf {
 constexpr int kMaxRanks = 8;
 
 struct ArAdamChunk {
-  long long offset, rows, ld, col0, cols;
+  long long offset, rows, ld, col0, cols, state;
 };
 
 struct ArAdamParams {
@@ -107,6 +107,7 @@ allreduce_adam_kernel(const ArAdamParams p, int blocks_per_chunk) {
     const float inv_c1 = 1.f / p.bias_c1;
     const float inv_sqrt_c2 = rsqrtf(p.bias_c2);
     // the chunk is cut in `world` slices of whole 4-element groups; this rank owns slice `rank`
+    const bool aligned4 = ((c.cols | c.col0 | c.state) & 3) == 0;
     const long long total4 = (c.rows * c.ld) >> 2;   // ld and offsets are multiples of 4
     const long long per = (total4 + p.world - 1) / p.world;
     const long long lo4 = min(total4, per * p.rank), hi4 = min(total4, per * (p.rank + 1));
@@ -130,24 +131,37 @@ allreduce_adam_kernel(const ArAdamParams p, int blocks_per_chunk) {
       }
       float gv[4] = {g.x * p.grad_scale, g.y * p.grad_scale, g.z * p.grad_scale, g.w * p.grad_scale};
       const long long col0 = (i4 << 2) % c.ld;
-      float4 w4 = *reinterpret_cast<float4*>(p.master + e);
-      float4 m4 = *reinterpret_cast<float4*>(p.m + e);
-      float4 v4 = *reinterpret_cast<float4*>(p.v + e);
-      float wv[4] = {w4.x, w4.y, w4.z, w4.w}, mv[4] = {m4.x, m4.y, m4.z, m4.w},
-            vv[4] = {v4.x, v4.y, v4.z, v4.w};
-      bool any = false;
+      const long long row = (i4 << 2) / c.ld;
+      if (col0 + 4 <= c.col0 || col0 >= c.col0 + c.cols) continue;  // padding: cleared only
+      // optimizer state is dense over the trainable window: (row, col) -> state + row*cols + col-col0
+      const long long s0 = c.state + row * c.cols + (col0 - c.col0);
+      float wv[4], mv[4], vv[4];
+      if (aligned4) {  // the whole group is inside the window and 16-byte aligned
+        const float4 w4 = *reinterpret_cast<const float4*>(p.master + s0);
+        const float4 m4 = *reinterpret_cast<const float4*>(p.m + s0);
+        const float4 v4 = *reinterpret_cast<const float4*>(p.v + s0);
+        wv[0] = w4.x, wv[1] = w4.y, wv[2] = w4.z, wv[3] = w4.w;
+        mv[0] = m4.x, mv[1] = m4.y, mv[2] = m4.z, mv[3] = m4.w;
+        vv[0] = v4.x, vv[1] = v4.y, vv[2] = v4.z, vv[3] = v4.w;
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const long long col = col0 + j;
-        if (col >= c.col0 && col < c.col0 + c.cols) {
-          adam_update(gv[j], wv[j], mv[j], vv[j], p, inv_c1, inv_sqrt_c2);
-          any = true;
+        for (int j = 0; j < 4; ++j) adam_update(gv[j], wv[j], mv[j], vv[j], p, inv_c1, inv_sqrt_c2);
+        *reinterpret_cast<float4*>(p.master + s0) = make_float4(wv[0], wv[1], wv[2], wv[3]);
+        *reinterpret_cast<float4*>(p.m + s0) = make_float4(mv[0], mv[1], mv[2], mv[3]);
+        *reinterpret_cast<float4*>(p.v + s0) = make_float4(vv[0], vv[1], vv[2], vv[3]);
+      } else {
+        const uint2 cur = *reinterpret_cast<const uint2*>(p.work[p.rank] + e);
+        const float2 c01 = unpack_bf16x2(cur.x), c23 = unpack_bf16x2(cur.y);
+        wv[0] = c01.x, wv[1] = c01.y, wv[2] = c23.x, wv[3] = c23.y;  // padding keeps its value
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const long long col = col0 + j;
+          if (col < c.col0 || col >= c.col0 + c.cols) continue;
+          float w = p.master[s0 + j], mi = p.m[s0 + j], vi = p.v[s0 + j];
+          adam_update(gv[j], w, mi, vi, p, inv_c1, inv_sqrt_c2);
+          p.master[s0 + j] = w, p.m[s0 + j] = mi, p.v[s0 + j] = vi;
+          wv[j] = w;
         }
       }
-      if (!any) continue;
-      *reinterpret_cast<float4*>(p.master + e) = make_float4(wv[0], wv[1], wv[2], wv[3]);
-      *reinterpret_cast<float4*>(p.m + e) = make_float4(mv[0], mv[1], mv[2], mv[3]);
-      *reinterpret_cast<float4*>(p.v + e) = make_float4(vv[0], vv[1], vv[2], vv[3]);
       const uint32_t lo = pack_bf16x2(wv[0], wv[1]), hi = pack_bf16x2(wv[2], wv[3]);
       if (p.use_multimem) {
         multimem_st_b32x2(p.work_mc + e, lo, hi);

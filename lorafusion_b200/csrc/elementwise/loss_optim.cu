@@ -129,12 +129,15 @@ cross_entropy_kernel(__nv_bfloat16* __restrict__ logits, const int* __restrict__
 // Its gradient is always cleared; only columns [col0, col0 + cols) of each row are
 // trainable (block-diagonal B matrices of merged projections keep their off-diagonal
 // blocks at zero this way).  A flat tensor is rows = 1, ld = cols = length, col0 = 0.
+// `grad` and `work` use the padded layout (`offset`); master / m / v hold the trainable
+// elements only, densely: element (row, col) lives at state + row * cols + (col - col0).
 struct AdamChunk {
   long long offset;
   long long rows;
   long long ld;
   long long col0;
   long long cols;
+  long long state;
 };
 
 struct AdamHyper {
@@ -160,14 +163,15 @@ adam_chunks_kernel(const AdamChunk* __restrict__ chunks, int num_chunks, float* 
     grad[e] = 0.f;
     const long long col = i % c.ld;
     if (col < c.col0 || col >= c.col0 + c.cols) continue;
-    float w = master[e];
-    const float mi = h.beta1 * m[e] + (1.f - h.beta1) * g;
-    const float vi = h.beta2 * v[e] + (1.f - h.beta2) * g * g;
-    m[e] = mi;
-    v[e] = vi;
+    const long long se = c.state + (i / c.ld) * c.cols + (col - c.col0);
+    float w = master[se];
+    const float mi = h.beta1 * m[se] + (1.f - h.beta1) * g;
+    const float vi = h.beta2 * v[se] + (1.f - h.beta2) * g * g;
+    m[se] = mi;
+    v[se] = vi;
     w -= h.lr * h.weight_decay * w;
     w -= h.lr * (mi * inv_c1) / (sqrtf(vi) * inv_sqrt_c2 + h.eps);
-    master[e] = w;
+    master[se] = w;
     work[e] = __float2bfloat16(w);
   }
 }
@@ -187,7 +191,7 @@ int lf_cross_entropy(void* logits, const int* labels, float* loss, long long M, 
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
-// chunks: device array of AdamChunk {int64 offset, rows, ld, col0, cols}
+// chunks: device array of AdamChunk {int64 offset, rows, ld, col0, cols, state}
 int lf_adam_chunks(const void* chunks, int num_chunks, float* grad, float* master, float* m,
                    float* v, void* work, float lr, float beta1, float beta2, float eps,
                    float weight_decay, int step, float grad_scale, void* stream) {

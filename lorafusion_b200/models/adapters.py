@@ -3,16 +3,24 @@
 The reference keeps adapters as PEFT modules named ``lora_{i}`` and, for multi-LoRA data
 parallelism, wraps each adapter's parameters in a fake ``nn.Module`` with its own Megatron
 DDP grad buffer and AdamW (``benchmarks_paper/bench_multi_gpu.py:162-203,276-287``).  Here
-all adapters live in five parallel 1-D arenas with identical element offsets:
+all adapters live in flat 1-D arenas.  Two of them share one rank-padded layout, the one
+the GEMM kernels address:
 
-    work (bf16, read by the GEMM kernels) | master | m | v | grad   (fp32)
+    work (bf16, read by the GEMM kernels) | grad (fp32, accumulated by the GEMM kernels)
+
+and three hold ONLY the trainable elements, packed densely (a rank-16 adapter fills a quarter
+of its rank-64 slot, so the padded layout would quadruple the optimizer state):
+
+    master | m | v   (fp32, indexed through the ``state`` field of the chunk table)
 
 Per merged projection the arena holds stacks ``A [n, R, K]`` and ``B [n, N, R]``
 (``ops/lora.py``).  Merged projections (q|k|v and gate|up) keep one LoRA per sub-projection:
 adapter ``i`` with rank ``r_i`` uses rows ``[j * slot, j * slot + r_i)`` of ``A`` for
 sub-projection ``j`` and the matching columns of the rows of ``B`` that belong to ``j``
 (block-diagonal ``B``); everything else stays zero and is excluded from the optimizer through
-the chunk table (``AdamChunk`` regions: offset, rows, ld, col0, cols).
+the chunk table (``AdamChunk`` regions: offset, rows, ld, col0, cols, state -- element
+``(row, col)`` of the trainable window has its optimizer state at
+``state + row * cols + (col - col0)``).
 
 One chunk table per adapter lets a single kernel launch apply Adam to -- or a single fused
 kernel reduce across data-parallel ranks -- all tensors of that adapter.
@@ -96,10 +104,11 @@ class LoRAArena:
         else:
             self.work = torch.zeros(off, dtype=torch.bfloat16, device=self.device)
             self.grad = torch.zeros(off, dtype=torch.float32, device=self.device)
+        self._build_chunk_rows()
         if with_optimizer_state:
-            self.master = torch.zeros(off, dtype=torch.float32, device=self.device)
-            self.m = torch.zeros(off, dtype=torch.float32, device=self.device)
-            self.v = torch.zeros(off, dtype=torch.float32, device=self.device)
+            self.master = torch.zeros(self.state_numel, dtype=torch.float32, device=self.device)
+            self.m = torch.zeros(self.state_numel, dtype=torch.float32, device=self.device)
+            self.v = torch.zeros(self.state_numel, dtype=torch.float32, device=self.device)
         else:
             self.master = self.m = self.v = None
         for v in self.views.values():
@@ -133,54 +142,88 @@ class LoRAArena:
     # ------------------------------------------------------------------ init
     def _init_weights(self, init_b_std: float, seed: int) -> None:
         """PEFT's default LoRA init: A ~ kaiming-uniform(a = sqrt 5) i.e. U(-1/sqrt K, 1/sqrt K),
-        B = 0 (or N(0, init_b_std) when a non-zero B is wanted for testing/benchmarks)."""
+        B = 0 (or N(0, init_b_std) when a non-zero B is wanted for testing/benchmarks).  The
+        fp32 master starts as the bf16-rounded value the kernels read."""
         g = torch.Generator(device=self.device).manual_seed(seed)
-        target = self.master if self.master is not None else torch.zeros(
-            self.numel, dtype=torch.float32, device=self.device)
+        n = self.num_adapters
         for v in self.views.values():
-            n = self.num_adapters
-            a = target[v.a_offset:v.a_offset + n * v.R * v.K].view(n, v.R, v.K)
-            b = target[v.b_offset:v.b_offset + n * v.N * v.R].view(n, v.N, v.R)
             bound = 1.0 / math.sqrt(v.K)
             for i in range(n):
-                for _, n0, size, c0, r in self.sub_slices(v, i):
-                    a[i, c0:c0 + r].uniform_(-bound, bound, generator=g)
+                for name, n0, size, c0, r in self.sub_slices(v, i):
+                    a = torch.empty(r, v.K, dtype=torch.float32, device=self.device)
+                    a.uniform_(-bound, bound, generator=g)
+                    v.stack.a[i, c0:c0 + r].copy_(a)
                     if init_b_std > 0:
-                        b[i, n0:n0 + size, c0:c0 + r].normal_(0.0, init_b_std, generator=g)
-        self.work.copy_(target)
-        if self.master is not None:
-            # keep master consistent with the bf16 copy the kernels read
-            self.master.copy_(self.work.float())
+                        b = torch.empty(size, r, dtype=torch.float32, device=self.device)
+                        b.normal_(0.0, init_b_std, generator=g)
+                        v.stack.b[i, n0:n0 + size, c0:c0 + r].copy_(b)
+        self.sync_master_from_work()
+
+    def sync_master_from_work(self, adapter: Optional[int] = None) -> None:
+        """Set the fp32 master weights to the current bf16 working values."""
+        if self.master is None:
+            return
+        for i in (range(self.num_adapters) if adapter is None else [adapter]):
+            for v in self.views.values():
+                for name, n0, size, c0, r in self.sub_slices(v, i):
+                    sa, sb = self.state_offsets[(v.layer, v.proj, i, name)]
+                    self.master[sa:sa + r * v.K].view(r, v.K).copy_(v.stack.a[i, c0:c0 + r])
+                    self.master[sb:sb + size * r].view(size, r).copy_(v.stack.b[i, n0:n0 + size, c0:c0 + r])
 
     # ------------------------------------------------------------------ chunk tables
-    def chunk_table(self, adapter: int) -> torch.Tensor:
-        """int64 ``[n_chunks, 5]`` regions (offset, rows, ld, col0, cols) covering every
-        tensor of ``adapter``; the gradient of the whole region is consumed, only the
-        trainable window is updated."""
-        t = self._chunks.get(adapter)
-        if t is None:
+    def _build_chunk_rows(self) -> None:
+        """Lay out every adapter's regions and assign its dense optimizer-state offsets.
+        Adapter ``i`` owns the contiguous state range ``state_range[i]``."""
+        self._chunk_rows: dict[int, list] = {}
+        self.state_offsets: dict[tuple, tuple[int, int]] = {}
+        self.state_range: dict[int, tuple[int, int]] = {}
+        state = 0
+
+        def take(count: int) -> int:
+            nonlocal state
+            at = state
+            state += (count + 3) // 4 * 4  # keep every region 16-byte aligned
+            return at
+
+        for adapter in range(self.num_adapters):
             rows = []
+            lo = state
             for v in self.views.values():
                 a_base = v.a_offset + adapter * v.R * v.K
                 b_base = v.b_offset + adapter * v.N * v.R
+                a_state = {}
                 # A: whole [R, K] block is cleared; trainable rows are contiguous per sub
                 covered = 0
-                for _, _, _, c0, r in self.sub_slices(v, adapter):
+                for name, _, _, c0, r in self.sub_slices(v, adapter):
                     if c0 > covered:  # untargeted slot rows: clear only
-                        rows.append((a_base + covered * v.K, 1, (c0 - covered) * v.K, 0, 0))
-                    rows.append((a_base + c0 * v.K, 1, r * v.K, 0, r * v.K))
+                        rows.append((a_base + covered * v.K, 1, (c0 - covered) * v.K, 0, 0, 0))
+                    a_state[name] = take(r * v.K)
+                    rows.append((a_base + c0 * v.K, 1, r * v.K, 0, r * v.K, a_state[name]))
                     covered = c0 + r
                 if covered < v.R:
-                    rows.append((a_base + covered * v.K, 1, (v.R - covered) * v.K, 0, 0))
+                    rows.append((a_base + covered * v.K, 1, (v.R - covered) * v.K, 0, 0, 0))
                 # B: per sub-projection a row block with a column window
                 n0 = 0
                 for j, (name, size) in enumerate(v.subs):
                     if self.targets(adapter, name):
-                        rows.append((b_base + n0 * v.R, size, v.R, j * v.slot, self.adapters[adapter].r))
+                        r = self.adapters[adapter].r
+                        b_state = take(size * r)
+                        rows.append((b_base + n0 * v.R, size, v.R, j * v.slot, r, b_state))
+                        self.state_offsets[(v.layer, v.proj, adapter, name)] = (a_state[name], b_state)
                     else:
-                        rows.append((b_base + n0 * v.R, size, v.R, 0, 0))
+                        rows.append((b_base + n0 * v.R, size, v.R, 0, 0, 0))
                     n0 += size
-            t = torch.tensor(rows, dtype=torch.int64, device=self.device)
+            self._chunk_rows[adapter] = rows
+            self.state_range[adapter] = (lo, state)
+        self.state_numel = max(state, 4)
+
+    def chunk_table(self, adapter: int) -> torch.Tensor:
+        """int64 ``[n_chunks, 6]`` regions (offset, rows, ld, col0, cols, state) covering every
+        tensor of ``adapter``; the gradient of the whole region is consumed, only the
+        trainable window is updated, with its optimizer state at ``state``."""
+        t = self._chunks.get(adapter)
+        if t is None:
+            t = torch.tensor(self._chunk_rows[adapter], dtype=torch.int64, device=self.device).view(-1, 6)
             self._chunks[adapter] = t
         return t
 
@@ -208,7 +251,7 @@ class LoRAArena:
 
     def adapter_grad_regions(self, adapter: int) -> list:
         """1-D views of the gradient arena covering every region of ``adapter``."""
-        return [self.grad[off:off + rows * ld] for off, rows, ld, _, _ in self.chunk_table(adapter).tolist()]
+        return [self.grad[off:off + rows * ld] for off, rows, ld, _, _, _ in self._chunk_rows[adapter]]
 
     def all_reduce_adapter_grads(self, adapter: int, group) -> None:
         """NCCL all-reduce of one adapter's gradients (the unfused data-parallel baseline)."""
@@ -226,28 +269,29 @@ class LoRAArena:
     def export_adapter(self, adapter: int) -> dict[str, torch.Tensor]:
         """``{"layers.{l}.{sub}.lora_A": [r, K], "...lora_B": [N_sub, r]}`` (fp32 master if
         present, else the bf16 working copy)."""
-        src = self.master if self.master is not None else self.work
         out = {}
-        n = self.num_adapters
         for (l, _), v in self.views.items():
-            a = src[v.a_offset:v.a_offset + n * v.R * v.K].view(n, v.R, v.K)[adapter]
-            b = src[v.b_offset:v.b_offset + n * v.N * v.R].view(n, v.N, v.R)[adapter]
             for name, n0, size, c0, r in self.sub_slices(v, adapter):
-                out[f"layers.{l}.{name}.lora_A"] = a[c0:c0 + r].clone()
-                out[f"layers.{l}.{name}.lora_B"] = b[n0:n0 + size, c0:c0 + r].clone()
+                if self.master is not None:
+                    sa, sb = self.state_offsets[(v.layer, v.proj, adapter, name)]
+                    a = self.master[sa:sa + r * v.K].view(r, v.K)
+                    b = self.master[sb:sb + size * r].view(size, r)
+                else:
+                    a = v.stack.a[adapter, c0:c0 + r]
+                    b = v.stack.b[adapter, n0:n0 + size, c0:c0 + r]
+                out[f"layers.{l}.{name}.lora_A"] = a.clone()
+                out[f"layers.{l}.{name}.lora_B"] = b.clone()
         return out
 
     def import_adapter(self, adapter: int, tensors: dict[str, torch.Tensor]) -> None:
-        n = self.num_adapters
         for (l, _), v in self.views.items():
             for name, n0, size, c0, r in self.sub_slices(v, adapter):
                 ka, kb = f"layers.{l}.{name}.lora_A", f"layers.{l}.{name}.lora_B"
                 if ka not in tensors or kb not in tensors:
                     raise KeyError(f"missing {ka} / {kb}")
-                for arena in (self.master, self.work):
-                    if arena is None:
-                        continue
-                    a = arena[v.a_offset:v.a_offset + n * v.R * v.K].view(n, v.R, v.K)
-                    b = arena[v.b_offset:v.b_offset + n * v.N * v.R].view(n, v.N, v.R)
-                    a[adapter, c0:c0 + r].copy_(tensors[ka])
-                    b[adapter, n0:n0 + size, c0:c0 + r].copy_(tensors[kb])
+                v.stack.a[adapter, c0:c0 + r].copy_(tensors[ka])
+                v.stack.b[adapter, n0:n0 + size, c0:c0 + r].copy_(tensors[kb])
+                if self.master is not None:
+                    sa, sb = self.state_offsets[(v.layer, v.proj, adapter, name)]
+                    self.master[sa:sa + r * v.K].view(r, v.K).copy_(tensors[ka])
+                    self.master[sb:sb + size * r].view(size, r).copy_(tensors[kb])

@@ -102,28 +102,27 @@ def load_adapter(arena: LoRAArena, adapter: int, in_dir: str | Path) -> None:
 
 def save_training_state(arena: LoRAArena, adapter: int, path: str | Path, *, data_cursor: int = 0,
                         extra: Optional[dict] = None) -> None:
-    """fp32 master / Adam moments of one adapter (only its own regions), step count, cursor."""
-    chunks = arena.chunk_table(adapter).cpu().tolist()
-    state = {"step": arena.steps[adapter], "data_cursor": data_cursor, "extra": extra or {}, "regions": []}
-    for off, rows, ld, _, _ in chunks:
-        n = rows * ld
-        state["regions"].append({
-            "offset": off, "numel": n,
-            "master": arena.master[off:off + n].cpu().clone(),
-            "m": arena.m[off:off + n].cpu().clone(),
-            "v": arena.v[off:off + n].cpu().clone(),
-        })
+    """fp32 master / Adam moments of one adapter (its dense optimizer-state range), step
+    count and data cursor."""
+    lo, hi = arena.state_range[adapter]
+    state = {"step": arena.steps[adapter], "data_cursor": data_cursor, "extra": extra or {},
+             "numel": hi - lo,
+             "master": arena.master[lo:hi].cpu().clone(),
+             "m": arena.m[lo:hi].cpu().clone(),
+             "v": arena.v[lo:hi].cpu().clone()}
     Path(path).parent.mkdir(parents=True, exist_ok=True)
     torch.save(state, str(path))
 
 
 def load_training_state(arena: LoRAArena, adapter: int, path: str | Path) -> dict:
     state = torch.load(str(path), map_location="cpu", weights_only=False)
-    for reg in state["regions"]:
-        off, n = reg["offset"], reg["numel"]
-        arena.master[off:off + n].copy_(reg["master"])
-        arena.m[off:off + n].copy_(reg["m"])
-        arena.v[off:off + n].copy_(reg["v"])
-        arena.work[off:off + n].copy_(reg["master"].to(torch.bfloat16))
+    lo, hi = arena.state_range[adapter]
+    if int(state["numel"]) != hi - lo:
+        raise ValueError(f"checkpoint holds {state['numel']} optimizer elements, adapter {adapter} has {hi - lo}")
+    arena.master[lo:hi].copy_(state["master"])
+    arena.m[lo:hi].copy_(state["m"])
+    arena.v[lo:hi].copy_(state["v"])
+    # the bf16 working copy follows the restored master weights
+    arena.import_adapter(adapter, arena.export_adapter(adapter))
     arena.steps[adapter] = int(state["step"])
     return {"step": state["step"], "data_cursor": state["data_cursor"], "extra": state["extra"]}

@@ -94,8 +94,11 @@ def cross_entropy_inplace(logits: torch.Tensor, labels: torch.Tensor, grad_scale
 def adam_chunks(chunks: torch.Tensor, grad: torch.Tensor, master: torch.Tensor, m: torch.Tensor,
                 v: torch.Tensor, work: torch.Tensor, *, lr: float, beta1: float, beta2: float,
                 eps: float, weight_decay: float, step: int, grad_scale: float = 1.0) -> None:
-    """AdamW over the regions listed in ``chunks`` (int64 ``[n, 5]``: offset, rows, ld, col0,
-    cols) of the parallel arenas; consumes and clears the gradient."""
+    """AdamW over the regions listed in ``chunks`` (int64 ``[n, 6]``: offset, rows, ld, col0,
+    cols, state).  ``grad`` and ``work`` are addressed by ``offset`` (padded layout), ``master`` /
+    ``m`` / ``v`` by ``state`` (dense over the trainable window); consumes and clears the gradient."""
+    if chunks.dim() != 2 or chunks.shape[1] != 6:
+        raise ValueError("chunk table must be int64 [n, 6]")
     nv.call("lf_adam_chunks", chunks.data_ptr(), chunks.shape[0], grad.data_ptr(),
             master.data_ptr(), m.data_ptr(), v.data_ptr(), work.data_ptr(), lr, beta1, beta2, eps,
             weight_decay, step, grad_scale, nv.current_stream_ptr())

@@ -39,11 +39,21 @@ def test_chunk_table_covers_each_adapter_exactly():
         chunks = arena.chunk_table(adapter).tolist()
         covered = torch.zeros(arena.numel, dtype=torch.int32)
         trainable = torch.zeros(arena.numel, dtype=torch.bool)
-        for off, rows, ld, c0, cols in chunks:
+        state_seen = torch.zeros(arena.state_numel, dtype=torch.int32)
+        for off, rows, ld, c0, cols, state in chunks:
             covered[off:off + rows * ld] += 1
             blk = torch.zeros(rows, ld, dtype=torch.bool)
             blk[:, c0:c0 + cols] = True
             trainable[off:off + rows * ld] |= blk.view(-1)
+            if cols:
+                assert state % 4 == 0
+                state_seen[state:state + rows * cols] += 1
+                # the dense fp32 master mirrors the trainable window of the bf16 working copy
+                win = arena.work[off:off + rows * ld].view(rows, ld)[:, c0:c0 + cols].float()
+                assert torch.equal(arena.master[state:state + rows * cols].view(rows, cols), win)
+        lo, hi = arena.state_range[adapter]
+        assert int(state_seen.max()) == 1 and int(state_seen[:lo].sum()) == 0 and int(state_seen[hi:].sum()) == 0
+        assert int(state_seen.sum()) == arena.trainable_numel(adapter)
         n = arena.num_adapters
         expect = torch.zeros(arena.numel, dtype=torch.bool)
         for v in arena.views.values():
@@ -54,7 +64,7 @@ def test_chunk_table_covers_each_adapter_exactly():
         assert torch.equal(covered > 0, expect) and int(covered.max()) == 1
         assert int(trainable.sum()) == arena.trainable_numel(adapter)
         # every initialised (non-zero) weight lies inside the trainable window
-        nz = arena.master != 0
+        nz = arena.work != 0
         assert not bool((nz & expect & ~trainable).any())
     assert arena.trainable_numel(0) == sum(16 * (len(v.subs) * v.K + v.N) for v in arena.views.values())
 
@@ -91,9 +101,12 @@ def test_training_state_roundtrip(tmp_path):
     other, _ = _arena(seed=4)
     meta = peft_io.load_training_state(other, 0, tmp_path / "state0.pt")
     assert meta == {"step": 7, "data_cursor": 123, "extra": {"lr": 1e-4}} and other.steps[0] == 7
-    for off, rows, ld, _, _ in arena.chunk_table(0).tolist():
-        sl = slice(off, off + rows * ld)
-        assert torch.equal(other.m[sl], arena.m[sl]) and torch.equal(other.master[sl], arena.master[sl])
+    sl = slice(*arena.state_range[0])
+    assert torch.equal(other.m[sl], arena.m[sl]) and torch.equal(other.master[sl], arena.master[sl])
+    for k, t in arena.export_adapter(0).items():
+        assert torch.equal(other.export_adapter(0)[k], t)
+    st, ot = arena.stack(0, "qkv"), other.stack(0, "qkv")
+    assert torch.equal(st.a[0], ot.a[0]) and torch.equal(st.b[0], ot.b[0])
     # adapter 1's state was not touched
-    off, rows, ld, _, _ = arena.chunk_table(1).tolist()[0]
-    assert not torch.equal(other.m[off:off + rows * ld], arena.m[off:off + rows * ld])
+    sl1 = slice(*arena.state_range[1])
+    assert not torch.equal(other.m[sl1], arena.m[sl1])

@@ -51,7 +51,7 @@ def test_emulated_ranks_match_allreduce_plus_adamw(world):
                     use_multimem=False, step=step, grad_scale=0.25, device="cuda", **hp)
             # restore the other adapter's gradients consumed from `total` bookkeeping
             chunks = ref.chunk_table(adapter).cpu()
-            for off, rows, ld, _, _ in chunks.tolist():
+            for off, rows, ld, _, _, _ in chunks.tolist():
                 total[off:off + rows * ld] = 0
                 for a in arenas:
                     assert float(a.grad[off:off + rows * ld].abs().max()) == 0.0

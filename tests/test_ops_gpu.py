@@ -100,19 +100,25 @@ def test_adam_chunks_matches_torch():
 
     n = 5000
     torch.manual_seed(0)
-    master = torch.randn(n, device="cuda")
-    ref = master.clone().requires_grad_(True)
+    init = torch.randn(n, device="cuda")
+    ref = init.clone().requires_grad_(True)
     opt = torch.optim.AdamW([ref], lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
-    m, v = torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda")
-    work = master.to(torch.bfloat16)
-    # two regions: a flat one and a 2-D one where only columns [8, 24) of 32 are trainable
-    chunks = torch.tensor([[0, 1, 1000, 0, 1000], [1024, 100, 32, 8, 16]], dtype=torch.int64,
+    # two regions: a flat one and a 2-D one where only columns [8, 24) of 32 are trainable;
+    # the optimizer state is dense: 1000 elements, then the 100 x 16 window row by row
+    chunks = torch.tensor([[0, 1, 1000, 0, 1000, 0], [1024, 100, 32, 8, 16, 1000]], dtype=torch.int64,
                           device="cuda")
     trainable = torch.zeros(n, dtype=torch.bool, device="cuda")
     trainable[:1000] = True
     blk = torch.zeros(100, 32, dtype=torch.bool, device="cuda")
     blk[:, 8:24] = True
     trainable[1024:1024 + 3200] = blk.view(-1)
+
+    def dense(t):
+        return torch.cat([t[:1000], t[1024:4224].view(100, 32)[:, 8:24].reshape(-1)])
+
+    master = dense(init).clone()
+    m, v = torch.zeros_like(master), torch.zeros_like(master)
+    work = init.to(torch.bfloat16)
     for step in range(1, 4):
         g = torch.randn(n, device="cuda")
         grad = g.clone()
@@ -121,9 +127,9 @@ def test_adam_chunks_matches_torch():
         ew.adam_chunks(chunks, grad, master, m, v, work, lr=1e-2, beta1=0.9, beta2=0.95, eps=1e-8,
                        weight_decay=0.1, step=step, grad_scale=0.5)
         assert float(grad[:1000].abs().max()) == 0.0 and float(grad[1024:4224].abs().max()) == 0.0
-    exp = torch.where(trainable, ref.detach(), master)
-    assert_close(master[trainable], exp[trainable], rtol=1e-4, atol=1e-5, msg="adam master")
-    assert_close(work[trainable], exp[trainable].to(torch.bfloat16), msg="adam bf16 copy")
+    assert_close(master, dense(ref.detach()), rtol=1e-4, atol=1e-5, msg="adam master")
+    assert_close(work[trainable], ref.detach()[trainable].to(torch.bfloat16), msg="adam bf16 copy")
+    assert torch.equal(work[~trainable], init.to(torch.bfloat16)[~trainable])
 
 
 @pytest.mark.parametrize("double_quant", [False, True])
