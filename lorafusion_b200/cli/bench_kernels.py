@@ -80,7 +80,57 @@ def torch_lora(x, w, dy, a, b, p, mode):
     return dx, da, db
 
 
+def run_nf4_compare(args):
+    """Base GEMM on an NF4 weight: dequantise to scratch then the bf16 kernel, against the
+    kernel that expands NF4 inside its main loop, forward and input gradient."""
+    from ..ops import nf4
+    from ..ops.lora import materialize_weight, set_nf4_fused_max_tokens
+
+    rows = []
+    for shape in args.shapes:
+        K, N = (int(v) for v in shape.lower().split("x"))
+        w = (torch.randn(N, K, device="cuda") * 0.02).to(torch.bfloat16)
+        qw = nf4.quantize_nf4(w)
+        qw.fp32_block_scales()
+        for M in args.tokens:
+            x = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+            dy = torch.randn(M, N, device="cuda").to(torch.bfloat16)
+            kw = dict(warmup=args.warmup, number=args.number, flush=True)
+
+            def scratch_fwd():
+                set_nf4_fused_max_tokens(0)
+                return lk.base_lora_fwd(x, materialize_weight(qw, M), None, None, tile_adapter=None)
+
+            def fused_fwd_():
+                return lk.base_lora_fwd(x, qw, None, None, tile_adapter=None)
+
+            def scratch_dx():
+                set_nf4_fused_max_tokens(0)
+                return lk.base_lora_dx(dy, materialize_weight(qw, M), None, None, tile_adapter=None)
+
+            def fused_dx():
+                return lk.base_lora_dx(dy, qw, None, None, tile_adapter=None)
+
+            if args.profile_only == "nf4_fwd":
+                for _ in range(args.number):
+                    fused_fwd_()
+                torch.cuda.synchronize()
+                return []
+            row = {"shape": f"[{M}x{K}x{N}] NF4", "scratch_fwd_s": benchmark(scratch_fwd, **kw),
+                   "fused_fwd_s": benchmark(fused_fwd_, **kw), "scratch_dx_s": benchmark(scratch_dx, **kw),
+                   "fused_dx_s": benchmark(fused_dx, **kw)}
+            row["fused_fwd_tflops"] = 2 * M * K * N / row["fused_fwd_s"] / 1e12
+            rows.append(row)
+            print(json.dumps(row))
+    from ..ops import _native
+
+    _native.check_device_errors()
+    return rows
+
+
 def run(args):
+    if args.nf4_compare or args.profile_only == "nf4_fwd":
+        return run_nf4_compare(args)
     torch.manual_seed(0)
     results = []
     for shape in args.shapes:
@@ -130,7 +180,10 @@ def main(argv=None):
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--number", type=int, default=20)
     ap.add_argument("--csv", default=None)
-    ap.add_argument("--profile-only", default=None, choices=["fused_fwd", "fused_fwd_bwd", "multi_fwd_bwd"])
+    ap.add_argument("--nf4-compare", action="store_true",
+                    help="time the NF4 base GEMM: dequantise-to-scratch + bf16 kernel vs NF4 expanded in the main loop")
+    ap.add_argument("--profile-only", default=None,
+                    choices=["fused_fwd", "fused_fwd_bwd", "multi_fwd_bwd", "nf4_fwd"])
     run(ap.parse_args(argv))
 
 

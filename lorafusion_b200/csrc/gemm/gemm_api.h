@@ -89,6 +89,19 @@ typedef struct LfTpArgs {
 
 int lf_gemm_tp(const LfGemmArgs* args, const LfTpArgs* tp);
 
+// NF4 main loop: `args->b` points at the PACKED weight (uint8 [w_rows, w_cols / 2], two 4-bit
+// codes per byte, even element in the high nibble) while b_rows / b_cols / b_ld / b_mn describe
+// it as if it were the bf16 [w_rows, w_cols] matrix.  `block_scales` holds one fp32 scale per
+// 64 consecutive elements of a row (double quantisation already undone).  bn must be 256;
+// variants: K-major weight (forward) and MN-major weight (input gradient, with or without
+// the dropout-mixing epilogue).
+typedef struct LfNf4Args {
+  const float* block_scales;
+  int64_t w_rows, w_cols;
+} LfNf4Args;
+
+int lf_gemm_nf4(const LfGemmArgs* args, const LfNf4Args* nf4);
+
 #ifdef __cplusplus
 }
 #endif

@@ -53,6 +53,17 @@ struct GemmKParams {
   int row_offset, col_offset;
   int m_rotate;  // dense mode: M tiles are visited starting from this tile (wraps around)
   int* err;
+  // NF4 main loop: fp32 scale of every 64-element block of the [nf4_rows, 64 * blocks] weight
+  const float* nf4_scales;
+  long long nf4_rows, nf4_blocks_per_row;
+};
+
+// The sixteen NF4 code values (bitsandbytes' normal-float table).
+__constant__ float kNf4Values[16] = {
+    -1.0f, -0.6961928009986877f, -0.5250730514526367f, -0.39491748809814453f,
+    -0.28444138169288635f, -0.18477343022823334f, -0.09105003625154495f, 0.0f,
+    0.07958029955625534f, 0.16093020141124725f, 0.24611230194568634f, 0.33791524171829224f,
+    0.44070982933044434f, 0.5626170039176941f, 0.7229568362236023f, 1.0f,
 };
 
 // Tensor-parallel fusion (TP != 0).  Token rows are split in `world` shards of
@@ -119,11 +130,13 @@ __device__ __forceinline__ TileCoord decode_tile(const GemmKParams& p, int idx) 
   return t;
 }
 
-template <int BN>
+template <int BN, bool NF4B = false>
 struct SmemPlan {
   static constexpr int A_BYTES = BM * BK * 2;
   static constexpr int B_BYTES = BN * BK * 2;
-  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  // NF4 variant: the packed 4-bit B tile lands behind the bf16 tile it is expanded into
+  static constexpr int PACK_BYTES = NF4B ? BN * BK / 2 : 0;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + PACK_BYTES;
   static constexpr int STAGES = (BN == 256) ? 4 : (BN == 192 ? 5 : (BN == 128 ? 6 : 8));
   static constexpr int BAR_BYTES = 512;
   static constexpr int TOTAL = STAGES * STAGE_BYTES + BAR_BYTES + 1024;  // + alignment slack
@@ -131,15 +144,21 @@ struct SmemPlan {
 
 constexpr int kNumCommWarps = 4;
 
-template <int BN, int NACC, bool A_MN, bool B_MN, bool B2_MN, int EPI, bool MASK_A, int TP = 0>
-__global__ void __launch_bounds__(MASK_A ? (192 + 32 * kNumMaskWarps)
-                                         : (TP == 1 ? 192 + 32 * kNumCommWarps : 192), 1)
+template <int BN, int NACC, bool A_MN, bool B_MN, bool B2_MN, int EPI, bool MASK_A, int TP = 0,
+          bool NF4B = false>
+__global__ void __launch_bounds__((MASK_A || NF4B) ? (192 + 32 * kNumMaskWarps)
+                                                   : (TP == 1 ? 192 + 32 * kNumCommWarps : 192), 1)
     umma_gemm_kernel(const GemmKParams p, const __grid_constant__ CUtensorMap tmA,
                      const __grid_constant__ CUtensorMap tmB,
                      const __grid_constant__ CUtensorMap tmA2,
                      const __grid_constant__ CUtensorMap tmB2, const TpParams tp) {
   static_assert(!(MASK_A && TP != 0), "dropout-in-smem and TP fusion are not combined");
-  using Plan = SmemPlan<BN>;
+  static_assert(!NF4B || (BN == 256 && !MASK_A && TP == 0 && !A_MN),
+                "the NF4 main loop exists for 256-wide dense tiles only");
+  using Plan = SmemPlan<BN, NF4B>;
+  constexpr bool XFORM = MASK_A || NF4B;  // extra warps rewrite a stage before the MMA reads it
+  __shared__ float nf4_lut[16];
+  if (NF4B && threadIdx.x < 16) nf4_lut[threadIdx.x] = kNf4Values[threadIdx.x];
   constexpr int STAGES = Plan::STAGES;
   // Two accumulator buffers whenever TMEM (512 columns) has room; the 256-wide
   // two-accumulator variant runs single-buffered.
@@ -226,7 +245,8 @@ __global__ void __launch_bounds__(MASK_A ? (192 + 32 * kNumMaskWarps)
           }
           uint8_t* sA = smem + s * Plan::STAGE_BYTES;
           uint8_t* sB = sA + Plan::A_BYTES;
-          mbar_expect_tx(&full[s], Plan::STAGE_BYTES);
+          mbar_expect_tx(&full[s], (NF4B && kb < nkb) ? Plan::A_BYTES + Plan::PACK_BYTES
+                                                       : Plan::A_BYTES + Plan::B_BYTES);
           if (kb < nkb) {
             const int kk = t.k0 + kb * BK;
             if (!A_MN) {
@@ -235,7 +255,13 @@ __global__ void __launch_bounds__(MASK_A ? (192 + 32 * kNumMaskWarps)
               tma_load_2d(sA, &tmA, &full[s], t.m0, kk);
               tma_load_2d(sA + 8192, &tmA, &full[s], t.m0 + 64, kk);
             }
-            if (!B_MN) {
+            if (NF4B) {
+              // packed bytes (two codes each): K-major W -> [256 rows x 32 B],
+              // MN-major W -> [64 rows x 128 B]; tmB is a byte map here
+              uint8_t* sP = sB + Plan::B_BYTES;
+              if (!B_MN) tma_load_2d(sP, &tmB, &full[s], kk >> 1, n0);
+              else tma_load_2d(sP, &tmB, &full[s], n0 >> 1, kk);
+            } else if (!B_MN) {
               tma_load_2d(sB, &tmB, &full[s], kk, by + n0);
             } else {
 #pragma unroll
@@ -281,8 +307,8 @@ __global__ void __launch_bounds__(MASK_A ? (192 + 32 * kNumMaskWarps)
         for (int kb = 0; kb < total; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
-          if (!mbar_wait(MASK_A ? &ready[s] : &full[s], ph, ctx,
-                         MASK_A ? ERR_WAIT_READY : ERR_WAIT_FULL)) {
+          if (!mbar_wait(XFORM ? &ready[s] : &full[s], ph, ctx,
+                         XFORM ? ERR_WAIT_READY : ERR_WAIT_FULL)) {
             ok = false;
             break;
           }
@@ -527,6 +553,76 @@ __global__ void __launch_bounds__(MASK_A ? (192 + 32 * kNumMaskWarps)
         st_release_sys(tp.ag_peer_flags[ct] + tp.rank * tp.tiles_per_shard + lt, tp.epoch);
       }
     }
+  } else if (NF4B) {
+    // ------------- NF4 -> bf16 expansion of the main-loop B stage (256 threads) -------------
+    // Thread tt owns 64 consecutive codes along the quantisation direction: one row of a
+    // K-major tile, or a quarter row (one 64-column block) of an MN-major tile.  They share
+    // one block scale, fetched before the wait so that its latency hides behind the TMA.
+    const int tt = threadIdx.x - 192;
+    int it = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+      TileCoord t = decode_tile(p, tile);
+      const int n0 = t.n0 * BN;
+      const int nkb2 = (t.adapter >= 0) ? p.nkb2 : 0;
+      const int nkb = t.nkb;
+      const int total = nkb + nkb2;
+      for (int kb = 0; kb < total; ++kb, ++it) {
+        const int s = it % STAGES;
+        const uint32_t ph = (it / STAGES) & 1;
+        float scale = 0.f;
+        if (kb < nkb) {
+          const int kk = kb * BK;
+          long long wrow, wblk;
+          if (!B_MN) {
+            wrow = n0 + tt;
+            wblk = kk >> 6;
+          } else {
+            wrow = kk + (tt >> 2);
+            wblk = (n0 >> 6) + (tt & 3);
+          }
+          if (wrow < p.nf4_rows && wblk < p.nf4_blocks_per_row)
+            scale = __ldg(p.nf4_scales + wrow * p.nf4_blocks_per_row + wblk);
+        }
+        if (!mbar_wait(&full[s], ph, ctx, ERR_WAIT_FULL)) {
+          ok = false;
+          break;
+        }
+        if (kb < nkb) {
+          uint8_t* sB = smem + s * Plan::STAGE_BYTES + Plan::A_BYTES;
+          const uint8_t* sP = sB + Plan::B_BYTES;
+          const uint8_t* src;
+          uint8_t* dst;
+          int sw;
+          if (!B_MN) {
+            src = sP + tt * 32;
+            dst = sB + tt * 128;
+            sw = tt & 7;
+          } else {
+            const int kr = tt >> 2, h = tt & 3;
+            src = sP + kr * 128 + h * 32;
+            dst = sB + h * 8192 + kr * 128;
+            sw = kr & 7;
+          }
+          const uint4 w0 = *reinterpret_cast<const uint4*>(src);
+          const uint4 w1 = *reinterpret_cast<const uint4*>(src + 16);
+          const uint32_t w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            uint32_t o[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const uint32_t byte = (w[c] >> (8 * i)) & 0xffu;
+              // even element in the high nibble
+              o[i] = pack_bf16x2(nf4_lut[byte >> 4] * scale, nf4_lut[byte & 15u] * scale);
+            }
+            *reinterpret_cast<uint4*>(dst + ((c ^ sw) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+          }
+          fence_proxy_async_smem();
+        }
+        mbar_arrive(&ready[s]);
+      }
+    }
   } else if (MASK_A) {
     // ------------------- dropout mask applied to the A stage in place -------------------
     const int mt = threadIdx.x - 192;  // 0 .. 32*kNumMaskWarps-1
@@ -611,12 +707,13 @@ __global__ void __launch_bounds__(MASK_A ? (192 + 32 * kNumMaskWarps)
 // ------------------------------------------------------------------------------------
 // host side
 // ------------------------------------------------------------------------------------
-template <int BN, int NACC, bool A_MN, bool B_MN, bool B2_MN, int EPI, bool MASK_A, int TP = 0>
+template <int BN, int NACC, bool A_MN, bool B_MN, bool B2_MN, int EPI, bool MASK_A, int TP = 0,
+          bool NF4B = false>
 static int launch_variant(const GemmKParams& kp, const CUtensorMap& tA, const CUtensorMap& tB,
                           const CUtensorMap& tA2, const CUtensorMap& tB2, int grid,
                           cudaStream_t stream, const TpParams& tp = TpParams()) {
-  auto kern = umma_gemm_kernel<BN, NACC, A_MN, B_MN, B2_MN, EPI, MASK_A, TP>;
-  constexpr int smem = SmemPlan<BN>::TOTAL;
+  auto kern = umma_gemm_kernel<BN, NACC, A_MN, B_MN, B2_MN, EPI, MASK_A, TP, NF4B>;
+  constexpr int smem = SmemPlan<BN, NF4B>::TOTAL;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -626,7 +723,7 @@ static int launch_variant(const GemmKParams& kp, const CUtensorMap& tA, const CU
     }
     configured = true;
   }
-  const int threads = MASK_A ? (192 + 32 * kNumMaskWarps) : (TP == 1 ? 192 + 32 * kNumCommWarps : 192);
+  const int threads = (MASK_A || NF4B) ? (192 + 32 * kNumMaskWarps) : (TP == 1 ? 192 + 32 * kNumCommWarps : 192);
   kern<<<grid, threads, smem, stream>>>(kp, tA, tB, tA2, tB2, tp);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
@@ -649,26 +746,46 @@ static int sm_count() {
 
 }  // namespace lf
 
-static int gemm_entry(const LfGemmArgs* a, const LfTpArgs* t);
+static int gemm_entry(const LfGemmArgs* a, const LfTpArgs* t, const LfNf4Args* q);
 
-extern "C" int lf_gemm(const LfGemmArgs* a) { return gemm_entry(a, nullptr); }
+extern "C" int lf_gemm(const LfGemmArgs* a) { return gemm_entry(a, nullptr, nullptr); }
 
 // Tensor-parallel fused variants (all-gather -> GEMM, GEMM -> reduce-scatter).
-extern "C" int lf_gemm_tp(const LfGemmArgs* a, const LfTpArgs* t) { return gemm_entry(a, t); }
+extern "C" int lf_gemm_tp(const LfGemmArgs* a, const LfTpArgs* t) { return gemm_entry(a, t, nullptr); }
 
-static int gemm_entry(const LfGemmArgs* a, const LfTpArgs* t) {
+// Base weight read as NF4 and expanded to bf16 inside the main loop (no bf16 copy of the
+// weight ever exists in global memory).
+extern "C" int lf_gemm_nf4(const LfGemmArgs* a, const LfNf4Args* q) {
+  if (q == nullptr || q->block_scales == nullptr) return -1;
+  return gemm_entry(a, nullptr, q);
+}
+
+static int gemm_entry(const LfGemmArgs* a, const LfTpArgs* t, const LfNf4Args* q) {
   using namespace lf;
   if (a == nullptr || a->a == nullptr || a->b == nullptr || a->out == nullptr) return -1;
   if (a->bn != 64 && a->bn != 128 && a->bn != 192 && a->bn != 256) return -2;
   if (a->K2 % BK != 0) return -3;
   const int BN = a->bn;
+  if (q != nullptr) {
+    // whole 64-code blocks per tile row, dense tiles, adapters only on the slab operand
+    if (BN != 256 || a->a_mn || a->mask_a || a->seg_tiles != nullptr || a->b_adapter_rows != 0) return -12;
+    if (q->w_cols % 256 != 0 || q->w_rows % 64 != 0 || a->K % BK != 0) return -13;
+    if (a->b_mn ? (a->N != q->w_cols || a->K != q->w_rows) : (a->N != q->w_rows || a->K != q->w_cols)) return -14;
+    if (!a->b_mn && a->N % 256 != 0) return -13;
+  }
 
   CUtensorMap tA, tB, tA2, tB2;
   int rc;
   // A: K-major box = [128 rows x 64 cols]; MN-major box = [64 rows(k) x 64 cols(mn)]
   rc = make_tmap_2d_b16(&tA, a->a, a->a_rows, a->a_cols, a->a_ld, a->a_mn ? 64 : BM, 64, true);
   if (rc != 0) return -20 + rc;
-  rc = make_tmap_2d_b16(&tB, a->b, a->b_rows, a->b_cols, a->b_ld, a->b_mn ? 64 : BN, 64, true);
+  if (q == nullptr) {
+    rc = make_tmap_2d_b16(&tB, a->b, a->b_rows, a->b_cols, a->b_ld, a->b_mn ? 64 : BN, 64, true);
+  } else {
+    // byte view of the packed weight [w_rows, w_cols / 2]
+    rc = make_tmap_2d_u8(&tB, a->b, (uint64_t)q->w_rows, (uint64_t)q->w_cols / 2, (uint64_t)q->w_cols / 2,
+                         a->b_mn ? 64 : 256, a->b_mn ? 128 : 32);
+  }
   if (rc != 0) return -30 + rc;
   if (a->K2 > 0) {
     if (a->a2 == nullptr || a->b2 == nullptr) return -4;
@@ -713,6 +830,9 @@ static int gemm_entry(const LfGemmArgs* a, const LfTpArgs* t) {
   kp.col_offset = a->col_offset;
   kp.err = a->err;
   kp.m_rotate = 0;
+  kp.nf4_scales = q != nullptr ? q->block_scales : nullptr;
+  kp.nf4_rows = q != nullptr ? q->w_rows : 0;
+  kp.nf4_blocks_per_row = q != nullptr ? q->w_cols / 64 : 0;
   if (kp.num_tiles <= 0) return 0;
 
   int grid = sm_count();
@@ -768,6 +888,24 @@ static int gemm_entry(const LfGemmArgs* a, const LfTpArgs* t) {
         return launch_variant<256, 2, false, true, true, LF_EPI_BF16_DROPMIX, false, 2>(kp, tA, tB, tA2, tB2, grid, st, tp);
       default:
         fprintf(stderr, "lf_gemm_tp: no kernel variant for key 0x%x\n", tkey);
+        return -5;
+    }
+  }
+
+  if (q != nullptr) {
+    const int qkey = (a->nacc << 4) | ((a->b_mn ? 1 : 0) << 1) | (a->epi == LF_EPI_BF16_DROPMIX);
+    if (a->K2 > 0 && (a->b2_mn != a->b_mn)) return -5;
+    switch (qkey) {
+      case (1 << 4) | 0:
+        if (a->epi != LF_EPI_BF16) return -5;
+        return launch_variant<256, 1, false, false, false, LF_EPI_BF16, false, 0, true>(kp, tA, tB, tA2, tB2, grid, st);
+      case (1 << 4) | 2:
+        if (a->epi != LF_EPI_BF16) return -5;
+        return launch_variant<256, 1, false, true, true, LF_EPI_BF16, false, 0, true>(kp, tA, tB, tA2, tB2, grid, st);
+      case (2 << 4) | 3:
+        return launch_variant<256, 2, false, true, true, LF_EPI_BF16_DROPMIX, false, 0, true>(kp, tA, tB, tA2, tB2, grid, st);
+      default:
+        fprintf(stderr, "lf_gemm_nf4: no kernel variant for key 0x%x\n", qkey);
         return -5;
     }
   }

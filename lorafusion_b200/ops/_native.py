@@ -62,6 +62,10 @@ def cuda_available() -> bool:
 # ----------------------------------------------------------------------------------------
 # struct mirrors (keep in sync with csrc/gemm/gemm_api.h)
 # ----------------------------------------------------------------------------------------
+class LfNf4Args(C.Structure):
+    _fields_ = [("block_scales", C.c_void_p), ("w_rows", C.c_int64), ("w_cols", C.c_int64)]
+
+
 class LfGemmArgs(C.Structure):
     _fields_ = [
         ("a", C.c_void_p), ("a_rows", C.c_int64), ("a_cols", C.c_int64), ("a_ld", C.c_int64),
@@ -125,6 +129,8 @@ def _declare_cuda(lib: C.CDLL) -> None:
     lib.lf_gemm.restype = C.c_int
     lib.lf_gemm_pair.argtypes = [C.POINTER(LfGemmArgs)]
     lib.lf_gemm_pair.restype = C.c_int
+    lib.lf_gemm_nf4.argtypes = [C.POINTER(LfGemmArgs), C.POINTER(LfNf4Args)]
+    lib.lf_gemm_nf4.restype = C.c_int
     for name, sig in _SIGNATURES.items():
         fn = getattr(lib, name)
         fn.argtypes = sig

@@ -73,10 +73,14 @@ def fill_gemm_args(
     """Describe one GEMM launch (operands, epilogue, dropout, scheduling) as a
     :class:`LfGemmArgs` for the current stream."""
     _check2d(a, "a")
-    _check2d(b, "b")
     args = nv.LfGemmArgs()
     args.a, args.a_rows, args.a_cols, args.a_ld = a.data_ptr(), a.shape[0], a.shape[1], a.stride(0)
-    args.b, args.b_rows, args.b_cols, args.b_ld = b.data_ptr(), b.shape[0], b.shape[1], b.stride(0)
+    if hasattr(b, "packed"):
+        # NF4 weight: the packed bytes stand in for the bf16 [rows, cols] matrix
+        args.b, args.b_rows, args.b_cols, args.b_ld = b.packed.data_ptr(), b.shape[0], b.shape[1], b.shape[1]
+    else:
+        _check2d(b, "b")
+        args.b, args.b_rows, args.b_cols, args.b_ld = b.data_ptr(), b.shape[0], b.shape[1], b.stride(0)
     if K2 > 0:
         _check2d(a2, "a2")
         _check2d(b2, "b2")
@@ -133,10 +137,21 @@ def set_pair_kernels(enabled: bool) -> None:
 
 def launch_gemm(pair: Optional[bool] = None, **kwargs) -> None:
     """Fill :class:`LfGemmArgs` (see :func:`fill_gemm_args`) and launch on the current stream.
-    ``pair`` overrides the module default for trying the CTA-pair kernel first."""
+    ``pair`` overrides the module default for trying the CTA-pair kernel first.  When ``b`` is
+    an :class:`~lorafusion_b200.ops.nf4.NF4Weight` the kernel that expands NF4 inside its main
+    loop runs (``lf_gemm_nf4``)."""
     lib = nv.cuda_lib()
     args = fill_gemm_args(**kwargs)
     nv.note_launch()
+    qw = kwargs["b"]
+    if hasattr(qw, "packed"):
+        q = nv.LfNf4Args()
+        scales = qw.fp32_block_scales()
+        q.block_scales, q.w_rows, q.w_cols = scales.data_ptr(), qw.shape[0], qw.shape[1]
+        rc = lib.lf_gemm_nf4(C.byref(args), C.byref(q))
+        if rc != 0:
+            raise RuntimeError(f"lf_gemm_nf4 failed with code {rc}")
+        return
     use_pair = _PAIR if pair is None else pair
     if use_pair and args.bn == 256 and args.M >= _PAIR_MIN_ROWS and not args.a_mn and not args.mask_a \
             and not args.seg_tiles:

@@ -61,10 +61,34 @@ class LoRAStack:
 _WEIGHT_SCRATCH: dict[tuple, torch.Tensor] = {}
 
 
-def materialize_weight(w: Weight) -> torch.Tensor:
+# Token count up to which an NF4 base weight is expanded inside the GEMM main loop
+# (``lf_gemm_nf4``) instead of into scratch memory first.  0 (the default) keeps the fused
+# kernel off: on B200 every 128-token tile has to re-expand the weight tile it multiplies and
+# the 64 table look-ups + multiplies per row per stage take about 2.6x as long as the stage's
+# tcgen05 MMAs, so the kernel ran at ~525 TFLOP/s against ~1400 for dequantise-to-scratch +
+# bf16 GEMM at 16384 tokens and was still 1.5x slower at 256 tokens (8192 x 8192 weight;
+# ``python -m lorafusion_b200.cli.bench_kernels --nf4-compare``).  One dequantisation pass per
+# call costs about 2 % of a 70B training step.
+_NF4_FUSED_MAX_TOKENS = int(os.environ.get("LORAFUSION_B200_NF4_FUSED_TOKENS", "0"))
+
+
+def set_nf4_fused_max_tokens(tokens: int) -> None:
+    global _NF4_FUSED_MAX_TOKENS
+    _NF4_FUSED_MAX_TOKENS = int(tokens)
+
+
+def _nf4_fusable(w: "NF4Weight") -> bool:
+    return w.packed.is_cuda and w.shape[0] % 256 == 0 and w.shape[1] % 256 == 0
+
+
+def materialize_weight(w: Weight, tokens: Optional[int] = None) -> Weight:
     """bf16 ``[N, K]`` view of a frozen weight; NF4 weights are expanded into scratch memory
-    that the next call with the same shape overwrites (safe under stream ordering)."""
+    that the next call with the same shape overwrites (safe under stream ordering) -- unless
+    the call is small enough (``tokens``) for the kernel that expands NF4 in its main loop,
+    in which case the quantised weight itself is handed on."""
     if isinstance(w, NF4Weight):
+        if tokens is not None and tokens <= _NF4_FUSED_MAX_TOKENS and _nf4_fusable(w):
+            return w
         key = (w.shape, w.device)
         buf = _WEIGHT_SCRATCH.get(key)
         if buf is None:
@@ -124,8 +148,9 @@ def lora_linear_forward(x: torch.Tensor, w: Weight, stack: Optional[LoRAStack],
                         info: Optional[MultiLoRABatchInfo], *, stream_id: int = 0,
                         bias: Optional[torch.Tensor] = None, training: bool = True):
     """Returns ``(y, s)``; ``s`` (``[M, R]`` bf16) is what the backward needs besides ``x``."""
-    wd = materialize_weight(w)
-    if _UNFUSED and stack is not None and info is not None:
+    unfused = _UNFUSED and stack is not None and info is not None
+    wd = materialize_weight(w, None if unfused else x.shape[0])
+    if unfused:
         return _unfused_forward(x, wd, stack, info, stream_id, bias, training)
     if stack is None or info is None:
         return lk.base_lora_fwd(x, wd, None, None, tile_adapter=None, bias=bias), None
@@ -140,7 +165,7 @@ def lora_linear_backward(dy: torch.Tensor, x: torch.Tensor, s: Optional[torch.Te
                          stack: Optional[LoRAStack], info: Optional[MultiLoRABatchInfo], *,
                          stream_id: int = 0, need_dx: bool = True, training: bool = True):
     """Accumulates dA/dB into ``stack.da`` / ``stack.db`` and returns ``dX`` (or ``None``)."""
-    wd = materialize_weight(w) if need_dx else None
+    wd = materialize_weight(w, None if isinstance(s, list) else dy.shape[0]) if need_dx else None
     if isinstance(s, list):
         return _unfused_backward(dy, x, s, wd, stack, info, need_dx)
     if stack is None or info is None or s is None:

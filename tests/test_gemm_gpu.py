@@ -127,3 +127,55 @@ def test_dropout_keep_fraction():
 
     m = keep_mask(512, 1024, 0.1, seed=0)
     assert abs(float(m.float().mean()) - 0.9) < 5e-3
+
+
+@pytest.mark.parametrize("double_quant", [False, True])
+@pytest.mark.parametrize("p", [0.0, 0.1])
+def test_nf4_mainloop_gemm_matches_dequantize_then_gemm(double_quant, p):
+    """The kernels that expand NF4 inside the main loop (forward, dX, dropout-mixed dX) against
+    the same ops on the weight dequantised by plain PyTorch; the LoRA slab rides along."""
+    from lorafusion_b200.ops import lora_kernels as lk
+    from lorafusion_b200.ops import nf4
+    from lorafusion_b200.ops.philox import keep_mask
+
+    N, K, n = 768, 1024, 4
+    seg_adapters, seg_tiles = [2, 0, -1, 3, 1], [2, 1, 1, 3, 2]
+    M = 128 * sum(seg_tiles)
+    tile_adapter = _tile_adapters(seg_adapters, seg_tiles)
+    x, w = _rand(M, K, seed=30), _rand(N, K, scale=0.03, seed=31)
+    dy = _rand(M, N, seed=32)
+    a_all, b_all = _adapters(n, N, K)
+    s, ds = _rand(M, 64, scale=0.1, seed=33), _rand(M, 64, scale=0.1, seed=34)
+    bias = _rand(N, seed=35)
+    qw = nf4.quantize_nf4(w, double_quant=double_quant)
+    wd = nf4.dequantize_nf4_reference(qw)  # bf16, torch
+    drop = lk.DropoutSpec(seed=99, stream_id=3, p=p)
+    keep = keep_mask(M, K, p, 99, 3).cuda()
+    row_adapter = tile_adapter.repeat_interleave(128).long()
+
+    y = lk.base_lora_fwd(x, qw, s, b_all, tile_adapter=tile_adapter, bias=bias)
+    dx = lk.base_lora_dx(dy, qw, ds, a_all, tile_adapter=tile_adapter, dropout=drop)
+    dx_plain = lk.base_lora_dx(dy, qw, None, None, tile_adapter=None)
+
+    y_ref = _f32mm(x, wd.t()) + bias.float()
+    dx_ref = _f32mm(dy, wd)
+    assert_close_two_rounds(dx_plain, dx_ref, msg="nf4 dX (no adapters)")
+    inv = 1.0 / (1.0 - p)
+    for a in range(n):
+        rows = row_adapter == a
+        y_ref[rows] += _f32mm(s[rows], b_all[a].t())
+        dx_ref[rows] += torch.where(keep[rows], _f32mm(ds[rows], a_all[a]) * inv,
+                                    torch.zeros((), device="cuda"))
+    assert_close_two_rounds(y, y_ref, msg="nf4 forward")
+    assert_close_two_rounds(dx, dx_ref, msg="nf4 dX")
+    # same tiles, same arithmetic: identical to dequantise-to-scratch followed by the bf16 kernel
+    from lorafusion_b200.ops import gemm as gemm_mod
+
+    wd_native = nf4.dequantize_nf4(qw)
+    was = gemm_mod._PAIR
+    gemm_mod.set_pair_kernels(False)  # same single-CTA template for both
+    try:
+        y2 = lk.base_lora_fwd(x, wd_native, s, b_all, tile_adapter=tile_adapter, bias=bias)
+    finally:
+        gemm_mod.set_pair_kernels(was)
+    assert torch.equal(y, y2)
