@@ -152,6 +152,23 @@ class DecoderStage:
                                with_optimizer_state=with_optimizer_state,
                                shared_alloc=shared_alloc) if self.adapters else None
 
+    def adopt_weights(self, full: "DecoderStage") -> "DecoderStage":
+        """Make this stage a slice of ``full`` (a stage covering at least the same layers):
+        frozen weights are shared, adapter weights are copied.  Used to compare a partitioned
+        model with the unpartitioned one."""
+        off = self.layer_start - full.layer_start
+        if off < 0 or self.layer_end > full.layer_end:
+            raise ValueError("the source stage does not cover these layers")
+        self.layers = full.layers[off:off + (self.layer_end - self.layer_start)]
+        if self.is_first:
+            self.embed = full.embed
+        if self.is_last:
+            self.final_norm, self.lm_head = full.final_norm, full.lm_head
+        if self.arena is not None:
+            for i in range(len(self.adapters)):
+                self.arena.import_adapter(i, full.arena.export_adapter(i))
+        return self
+
     # ------------------------------------------------------------------ helpers
     def _stack(self, layer: int, proj: str):
         return self.arena.stack(layer, proj) if self.arena is not None else None

@@ -61,3 +61,13 @@ def test_loss_decreases_with_adam():
             stage.arena.adam_step(a, lr=2e-3)
     assert losses[-1] < losses[0] - 0.05, losses
     assert float(stage.arena.grad.abs().max()) == 0.0
+
+
+def test_pipeline_demo_chained_stages_match_whole_model():
+    """Four stages run back to back on one GPU reproduce the unpartitioned model."""
+    from lorafusion_b200.cli import pp_demo
+
+    res = pp_demo.run("small", 4)
+    assert res["layers_per_stage"] == [1, 1, 1, 1]
+    assert abs(res["loss_whole"] - res["loss_chained"]) <= 1e-3 * abs(res["loss_whole"])
+    assert res["max_rel_grad_diff"] < 2e-2

@@ -1,0 +1,75 @@
+"""CPU tests of the result tooling: SVG charts, dataset-distribution generator, result parser and
+the Nsight Compute summariser."""
+
+import csv
+import json
+import xml.dom.minidom as minidom
+
+from lorafusion_b200.cli import gen_sample_distribution, parse_results, summarize_ncu
+from lorafusion_b200.train.data import MockDataset
+from lorafusion_b200.utils.plotting import GroupedBarChart, MultiLinePlot, PipelineGantt, StackedBarChart
+
+
+def test_charts_are_valid_svg(tmp_path):
+    charts = [
+        GroupedBarChart(["8B", "70B"], ["base", "ours"], [[1.0, 2.0], [1.5, 3.9]], title="a<b", normalize_to="base"),
+        StackedBarChart(["x", "y"], ["gemm", "attn"], [[3, 4], [1, 2]], ylabel="ms"),
+        MultiLinePlot(["s1", "s2"], [[1, 2, 4, 8]] * 2, [[1, 2, 4, 7.9], [1, 1.8, 3.1, 5]], logx=True),
+        PipelineGantt([[(0, 1), (1, 2)], [(1, 2), (2, 3)]], [[(4, 6), (6, 8)], [(3, 4), (4, 6)]], title="1F1B"),
+    ]
+    for i, c in enumerate(charts):
+        path = c.save(tmp_path / f"c{i}.svg")
+        doc = minidom.parse(str(path))
+        assert doc.documentElement.tagName == "svg" and len(doc.getElementsByTagName("rect")) >= 1
+    # normalisation: the baseline series becomes 1.0 everywhere
+    assert charts[0].values[0] == [1.0, 1.0] and abs(charts[0].values[1][1] - 1.95) < 1e-9
+
+
+def test_gen_sample_distribution_layout(tmp_path, capsys):
+    out = tmp_path / "d.json"
+    gen_sample_distribution.main(["--out", str(out), "--datasets", "xsum", "wikisum", "mix", "het", "--seeds", "0", "3",
+                                  "--permutations", "2", "--num-samples", "120", "--plot"])
+    data = json.loads(out.read_text())
+    assert set(data) == {"xsum", "wikisum", "mix", "het"} and set(data["mix"]) == {"seed_0", "seed_3"}
+    p1, p2 = data["xsum"]["seed_0"]["permutation_1"], data["xsum"]["seed_0"]["permutation_2"]
+    assert len(p1) == 120 and sorted(p1) == sorted(p2) and p1 != p2 and max(p1) <= 4096
+    # readable by the dataset loader
+    ds = MockDataset.from_distribution_file(out, "wikisum", seed=3, permutation=2)
+    assert len(ds) == 120 and out.with_suffix(".svg").exists()
+    rows = [json.loads(ln) for ln in capsys.readouterr().out.strip().splitlines()]
+    assert {r["dataset"] for r in rows} == {"xsum", "wikisum", "mix", "het"}
+
+
+def test_parse_results_speedups(tmp_path, capsys):
+    fields = ["model", "layout", "world", "adapters", "capacity", "microbatches", "tokens", "time_ms",
+              "throughput_tokens_per_s", "throughput_per_gpu", "peak_memory_gib", "bubble_ratio",
+              "optimizer_steps", "quantized", "schedule"]
+    path = tmp_path / "results.csv"
+    with open(path, "w", newline="") as f:
+        w = csv.DictWriter(f, fieldnames=fields)
+        w.writeheader()
+        for sched, tps in (("solver", 1500.0), ("mlora", 1000.0), ("solver", 1400.0)):
+            w.writerow(dict(model="m", layout="dp1pp4tp1", world=4, adapters=4, capacity=16384, microbatches=10,
+                            tokens=1e5, time_ms=1.0, throughput_tokens_per_s=tps, throughput_per_gpu=tps / 4,
+                            peak_memory_gib=10.0, bubble_ratio="", optimizer_steps="{}", quantized=False,
+                            schedule=sched))
+    sp = parse_results.main([str(path), "--plot", str(tmp_path / "figs")])
+    assert len(sp) == 1 and abs(sp[0]["speedup"] - 1.5) < 1e-9
+    assert (tmp_path / "figs" / "end_to_end.svg").exists() and (tmp_path / "figs" / "scaling.svg").exists()
+
+
+def test_summarize_ncu_tables(tmp_path):
+    raw = tmp_path / "raw.csv"
+    raw.write_text('"ID","Kernel Name","gpu__time_duration.sum","dram__bytes_read.sum",'
+                   '"sm__pipe_tensor_cycles_active.avg.pct_of_peak_sustained_active","launch__grid_size"\n'
+                   '"","","us","Mbyte","%",""\n'
+                   '"0","void lf::k<1, 2>(P)","761.3","1101.4","86.98","148"\n')
+    text = summarize_ncu.main([str(raw)])
+    assert "`lf::k<1, 2>`" in text and "86.98" in text and "761.3 us" in text
+    launches = tmp_path / "l.csv"
+    launches.write_text('==PROF== Connected\n"ID","Kernel Name","Metric Name","Metric Unit","Metric Value"\n'
+                        '"0","a(int)","gpu__time_duration.sum","ns","3000000"\n'
+                        '"1","b(int)","gpu__time_duration.sum","ns","1000000"\n'
+                        '"2","a(int)","gpu__time_duration.sum","ns","1000000"\n')
+    text = summarize_ncu.main([str(launches), "--launches"])
+    assert "Total 5.0 ms over 3 launches" in text and "| `a` | 2 | 4.000 | 80.0 % |" in text
