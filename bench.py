@@ -270,7 +270,8 @@ def main():
             "grad_sync": trainer.grad_sync,
             "lora_mode": args.lora_mode,
             "recompute": args.recompute,
-            "layers_without_recompute": trainer.stage._plan_keep(args.capacity),
+            "layers_without_recompute": trainer.stage.keep_summary(args.capacity)["keep_all_gemm_outputs"],
+            "activation_plan": trainer.stage.keep_summary(args.capacity),
             "l2": "inputs (frozen base weights) far larger than L2",
             "baseline": "vs_baseline = value / (n_gpus * 1278.85 tok/s/GPU), the reference's published "
                         "70B-mixed LoRAFusion throughput on 4xH100 per GPU",

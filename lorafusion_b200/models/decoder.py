@@ -118,6 +118,7 @@ class DecoderStage:
         self.max_inflight = max(1, max_inflight)
         self.reserve_bytes = reserve_bytes
         self._keep_plan: dict = {}
+        self.force_keep_modes: Optional[list] = None  # tests / experiments: per-layer keep mode
         self.head_chunk_tokens = head_chunk_tokens
         self.training = True
         self.adapters = list(adapters)
@@ -212,8 +213,10 @@ class DecoderStage:
         full = None
         if keep:
             full = dict(rstd1=rstd1, qkv=qkv, attn=attn, lse=lse, s_qkv=s_qkv, s_o=s_o,
-                        h_mid=h_mid, rstd2=rstd2, gu=gu, s_gu=s_gu, s_d=s_d)
-            if keep != "cheap":  # "cheap" drops what one elementwise kernel can rebuild
+                        h_mid=h_mid, rstd2=rstd2, s_gu=s_gu, s_d=s_d)
+            if keep != "nogu":  # "nogu" also drops the (largest) gate|up projection output
+                full["gu"] = gu
+            if keep is True:  # "cheap" / "nogu" drop what one elementwise kernel can rebuild
                 full.update(x1=x1, x2=x2, act=act)
         return h_mid, d, LayerSaved(h_in, full)
 
@@ -229,6 +232,12 @@ class DecoderStage:
             sv = dict(sv)
             sv["x1"] = ew.rmsnorm_fwd(saved.h_in, lw.ln1, cfg.rms_eps, want_rstd=False)[0]
             sv["x2"] = ew.rmsnorm_fwd(sv["h_mid"], lw.ln2, cfg.rms_eps, want_rstd=False)[0]
+            if "gu" not in sv:
+                # one GEMM rebuilds gate|up from x2 and the kept LoRA down-projection S'
+                sv["gu"], s_new = lora_linear_forward(sv["x2"], lw.gate_up, self._stack(l, "gate_up"), info,
+                                                      stream_id=self._sid(l, "gate_up"), training=tr, s=sv["s_gu"])
+                if isinstance(s_new, list):  # unfused baseline: its stored masks were re-drawn
+                    sv["s_gu"] = s_new
             sv["act"] = ew.swiglu_fwd(sv["gu"])
         d_act = lora_linear_backward(dh, sv["act"], sv["s_d"], lw.down, self._stack(l, "down"), info,
                                      stream_id=self._sid(l, "down"), training=tr)
@@ -257,6 +266,47 @@ class DecoderStage:
         c = self.cfg
         return tokens * (c.qkv_size + c.q_size + c.hidden_size + 2 * c.intermediate_size) * 2 \
             + c.num_heads * tokens * 4 + tokens * 4 * 256 * 2
+
+    def _plan_modes(self, tokens: int) -> list:
+        """Per-layer keep mode for the forward pass.  ``recompute=True`` -> all ``False``
+        (recompute the layer from its input), ``False`` -> all ``True`` (keep everything),
+        ``"auto"`` -> a memory plan over three levels, best value per byte first:
+
+        * ``"nogu"``  keep the GEMM / attention outputs except gate|up (the backward re-runs
+          that one GEMM plus two RMSNorms and SwiGLU): about half of the recomputation time
+          for a third of the bytes;
+        * ``"cheap"`` also keep gate|up (only elementwise kernels are re-run);
+        * ``False``   keep nothing but the layer input.
+
+        As many layers as fit become ``"nogu"``; what memory is left upgrades trailing layers
+        to ``"cheap"``."""
+        n = len(self.layers)
+        if self.force_keep_modes is not None:
+            return list(self.force_keep_modes)
+        if self.recompute is True:
+            return [False] * n
+        if self.recompute is False:
+            return [True] * n
+        key = ("modes", tokens)
+        if key not in self._keep_plan:
+            free, _ = torch.cuda.mem_get_info(self.device)
+            free += torch.cuda.memory_reserved(self.device) - torch.cuda.memory_allocated(self.device)
+            per_full = self.saved_bytes_per_layer(tokens)
+            per_gu = tokens * 2 * self.cfg.intermediate_size * 2
+            per_part = per_full - per_gu
+            h_in_all = n * tokens * self.cfg.hidden_size * 2
+            budget = max(0, free - self.reserve_bytes - 3 * per_full - h_in_all * self.max_inflight)
+            budget //= self.max_inflight
+            n_part = int(min(n, budget // per_part))
+            n_full = int(min(n_part, (budget - n_part * per_part) // per_gu))
+            self._keep_plan[key] = [False] * (n - n_part) + ["nogu"] * (n_part - n_full) + ["cheap"] * n_full
+        return self._keep_plan[key]
+
+    def keep_summary(self, tokens: int) -> dict:
+        modes = self._plan_modes(tokens)
+        return {"keep_all_gemm_outputs": sum(m in (True, "cheap") for m in modes),
+                "keep_all_but_gate_up": sum(m == "nogu" for m in modes),
+                "recompute_layer": sum(m is False for m in modes)}
 
     def _plan_keep(self, tokens: int) -> int:
         """How many (trailing) layers keep their activations instead of recomputing them.
@@ -288,11 +338,9 @@ class DecoderStage:
         else:
             delta, res = h_in, None
         saved = []
-        n_keep = self._plan_keep(batch.num_tokens)
-        first_keep = len(self.layers) - n_keep
+        modes = self._plan_modes(batch.num_tokens)
         for li in range(len(self.layers)):
-            keep = False if li < first_keep else ("cheap" if self.recompute == "auto" else True)
-            res, delta, sv = self._layer_forward(li, res, delta, batch, keep=keep)
+            res, delta, sv = self._layer_forward(li, res, delta, batch, keep=modes[li])
             saved.append(sv)
         if self.is_last:
             return (res, delta), saved

@@ -146,17 +146,21 @@ def _unfused_backward(dy, x, saved, wd, stack, info, need_dx):
 
 def lora_linear_forward(x: torch.Tensor, w: Weight, stack: Optional[LoRAStack],
                         info: Optional[MultiLoRABatchInfo], *, stream_id: int = 0,
-                        bias: Optional[torch.Tensor] = None, training: bool = True):
-    """Returns ``(y, s)``; ``s`` (``[M, R]`` bf16) is what the backward needs besides ``x``."""
+                        bias: Optional[torch.Tensor] = None, training: bool = True,
+                        s: Optional[torch.Tensor] = None):
+    """Returns ``(y, s)``; ``s`` (``[M, R]`` bf16) is what the backward needs besides ``x``.
+    A precomputed ``s`` (kept from an earlier forward of the same call site) skips the
+    down-projection."""
     unfused = _UNFUSED and stack is not None and info is not None
     wd = materialize_weight(w, None if unfused else x.shape[0])
     if unfused:
         return _unfused_forward(x, wd, stack, info, stream_id, bias, training)
     if stack is None or info is None:
         return lk.base_lora_fwd(x, wd, None, None, tile_adapter=None, bias=bias), None
-    drop = info.dropout_spec(stream_id, training)
-    s = lk.lora_down(x, stack.a, tile_adapter=info.tile_adapter, adapter_scale=info.adapter_scale,
-                     dropout=drop)
+    if s is None or isinstance(s, list):
+        drop = info.dropout_spec(stream_id, training)
+        s = lk.lora_down(x, stack.a, tile_adapter=info.tile_adapter, adapter_scale=info.adapter_scale,
+                         dropout=drop)
     y = lk.base_lora_fwd(x, wd, s, stack.b, tile_adapter=info.tile_adapter, bias=bias)
     return y, s
 

@@ -38,12 +38,14 @@ def test_engine_matches_autograd_oracle(model, quantize):
                                 max_mismatch_ratio=5e-3, msg=f"dB {key}")
 
 
-@pytest.mark.parametrize("mode", [False, "auto"])
+@pytest.mark.parametrize("mode", [False, "auto", "nogu"])
 def test_recompute_is_bitwise_equivalent(mode):
     """Full recomputation, keeping everything, and the memory-planned mix (which keeps GEMM /
     attention outputs and rebuilds the elementwise ones) must give identical gradients."""
     s1, batch = _setup(recompute=True)
-    s2, _ = _setup(recompute=mode)
+    s2, _ = _setup(recompute="auto" if mode == "nogu" else mode)
+    if mode == "nogu":  # first layer rebuilds gate|up from x2 and the kept S', second keeps it
+        s2.force_keep_modes = ["nogu", "cheap"]
     l1 = s1.forward_backward(batch)
     l2 = s2.forward_backward(batch)
     assert float(l1) == float(l2)
