@@ -31,6 +31,10 @@ import sys
 import threading
 import time
 
+# Grow allocator segments in place: with fixed-size segments a third of a B200 ends up as
+# cached-but-unusable fragments next to the multi-GB activation tensors of a 70B layer.
+os.environ.setdefault("PYTORCH_CUDA_ALLOC_CONF", "expandable_segments:True")
+
 H100_PER_GPU_TOKENS_PER_S = 5115.41 / 4  # reference LoRAFusion, 70B mixed, 4xH100 (published)
 
 
@@ -49,6 +53,9 @@ def parse_args():
     ap.add_argument("--recompute", default="auto", choices=["auto", "all", "none"],
                     help="activation recomputation: all layers, none, or as memory allows")
     ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--offload", default="auto", choices=["auto", "on", "off"],
+                    help="park gate|up activations in pinned host memory over PCIe; auto = time one step "
+                         "with and without during set-up and keep the faster plan")
     ap.add_argument("--grad-sync", default="auto", choices=["auto", "fused", "nccl"],
                     help="DP gradient path: fused reduce+Adam kernel over peer memory, or NCCL all-reduce")
     ap.add_argument("--lora-mode", default="fused", choices=["fused", "unfused"],
@@ -189,6 +196,8 @@ def main():
                                recompute={'auto': 'auto', 'all': True, 'none': False}[args.recompute], optim=OptimizerConfig(lr=1e-4),
                                dp_group=dist.group.WORLD if world > 1 else None, seed=1234, init_b_std=0.01,
                                grad_sync=args.grad_sync, use_multimem=args.multimem)
+    if "expandable_segments:True" in os.environ.get("PYTORCH_CUDA_ALLOC_CONF", ""):
+        trainer.stage.reserve_bytes = 16 << 30  # little fragmentation to provide for
     torch.cuda.synchronize()
     if rank == 0:
         print(f"[bench] model {cfg.name} built in {time.time() - t0:.1f}s, base weights "
@@ -245,6 +254,72 @@ def main():
         bytes_in = sum(h2d_bytes(b) for b in (dev[-1] if dev else trainer.to_device(step_specs[-1], host[-1], 0)))
         return ms, toks, clocks, launches, loss_val, bytes_in
 
+    def agree(flag: bool) -> bool:
+        """True only if every rank says True."""
+        t = torch.tensor([1.0 if flag else 0.0], device=device)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        return bool(t.item() > 0.5)
+
+    def timed_step(batches) -> float:
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        trainer.step_on_device(batches)
+        e1.record()
+        barrier()
+        t = torch.tensor([e0.elapsed_time(e1)], device=device)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- set-up (untimed): choose the activation plan by measurement ----
+    offload_note = "off"
+    if args.offload != "off" and args.recompute == "auto" and args.lora_mode == "fused":
+        host0 = trainer.stage_batches(step_specs[0], 0)
+        dev0 = trainer.to_device(step_specs[0], host0, 0)
+        trainer.step_on_device(dev0)
+        t_off = timed_step(dev0)
+        ok = agree(trainer.stage.prepare_offload(args.capacity))
+        if ok:
+            trainer.step_on_device(dev0)
+            t_on = timed_step(dev0)
+            n_off = trainer.stage.keep_summary(args.capacity)["gate_up_in_host_memory"]
+            waits = trainer.stage._offloader.backlog_waits
+            offload_note = f"on, {n_off} layers (set-up step {t_on:.0f} ms vs {t_off:.0f} ms without, {waits} backlog waits)"
+            if args.offload == "auto" and not t_on < 0.99 * t_off:
+                ok = False
+                offload_note = f"off (set-up step {t_on:.0f} ms with {n_off} layers parked vs {t_off:.0f} ms without, {waits} backlog waits)"
+        if not ok:
+            trainer.stage.disable_offload()
+            torch.cuda.empty_cache()
+        # The plan provides for transient memory with a fixed allowance; measure what a step
+        # really leaves unused and hand all but a safety margin back to the plan.
+        torch.cuda.synchronize()
+        torch.cuda.reset_peak_memory_stats()
+        trainer.step_on_device(dev0)
+        torch.cuda.synchronize()
+        total = torch.cuda.mem_get_info()[1]
+        slack = torch.tensor([float(total - torch.cuda.max_memory_reserved() - (8 << 30))], device=device)
+        if world > 1:
+            dist.all_reduce(slack, op=dist.ReduceOp.MIN)
+        slack = int(slack.item())
+        if slack > (1 << 30):
+            old = trainer.stage.reserve_bytes
+            trainer.stage.reserve_bytes = max(1 << 30, old - slack)
+            trainer.stage.clear_plan()
+            try:
+                trainer.step_on_device(dev0)
+                torch.cuda.synchronize()
+                good = True
+            except torch.cuda.OutOfMemoryError:
+                good = False
+            if not agree(good):
+                trainer.stage.reserve_bytes = old
+                trainer.stage.clear_plan()
+                torch.cuda.empty_cache()
+        del dev0, host0
+
     ms, toks, clocks, launches, loss_val, bytes_in = run_pass(e2e=False)
     value = toks / (ms / 1e3)
     result = {
@@ -272,11 +347,14 @@ def main():
             "recompute": args.recompute,
             "layers_without_recompute": trainer.stage.keep_summary(args.capacity)["keep_all_gemm_outputs"],
             "activation_plan": trainer.stage.keep_summary(args.capacity),
+            "activation_offload": offload_note,
             "l2": "inputs (frozen base weights) far larger than L2",
             "baseline": "vs_baseline = value / (n_gpus * 1278.85 tok/s/GPU), the reference's published "
                         "70B-mixed LoRAFusion throughput on 4xH100 per GPU",
             "tokens_per_step_per_gpu": tokens_per_step[-1],
             "final_loss": loss_val,
+            "peak_memory_gib": {"allocated": round(torch.cuda.max_memory_allocated() / 2**30, 1),
+                                "reserved": round(torch.cuda.max_memory_reserved() / 2**30, 1)},
         },
         "clocks": clocks,
         "gpu_launches": launches,

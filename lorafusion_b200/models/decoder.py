@@ -98,6 +98,11 @@ class LayerSaved:
     full: Optional[dict] = None
 
 
+def _pinned_bytes(nbytes: int) -> int:
+    """The pinned-memory allocator hands out power-of-two blocks."""
+    return 1 << max(0, int(nbytes - 1).bit_length())
+
+
 class DecoderStage:
     """Layers ``[layer_start, layer_end)`` of a decoder, on one GPU."""
 
@@ -119,6 +124,9 @@ class DecoderStage:
         self.reserve_bytes = reserve_bytes
         self._keep_plan: dict = {}
         self.force_keep_modes: Optional[list] = None  # tests / experiments: per-layer keep mode
+        self.offload_enabled = False      # park gate|up outputs in pinned host memory
+        self.offload_host_budget: Optional[int] = None  # bytes; None = share of MemAvailable
+        self._offloader = None
         self.head_chunk_tokens = head_chunk_tokens
         self.training = True
         self.adapters = list(adapters)
@@ -214,7 +222,9 @@ class DecoderStage:
         if keep:
             full = dict(rstd1=rstd1, qkv=qkv, attn=attn, lse=lse, s_qkv=s_qkv, s_o=s_o,
                         h_mid=h_mid, rstd2=rstd2, s_gu=s_gu, s_d=s_d)
-            if keep != "nogu":  # "nogu" also drops the (largest) gate|up projection output
+            if keep == "offload":  # gate|up goes to pinned host memory, overlapped with compute
+                full["gu_off"] = self._get_offloader(gu.shape[0]).store(li, gu)
+            elif keep != "nogu":  # "nogu" drops the (largest) gate|up projection output
                 full["gu"] = gu
             if keep is True:  # "cheap" / "nogu" drop what one elementwise kernel can rebuild
                 full.update(x1=x1, x2=x2, act=act)
@@ -297,14 +307,74 @@ class DecoderStage:
             h_in_all = n * tokens * self.cfg.hidden_size * 2
             budget = max(0, free - self.reserve_bytes - 3 * per_full - h_in_all * self.max_inflight)
             budget //= self.max_inflight
+            offload = self.offload_enabled and self.max_inflight == 1
+            if offload:
+                # ring of returning buffers + copies still on their way out
+                budget = max(0, budget - (3 + 4) * per_gu)
             n_part = int(min(n, budget // per_part))
             n_full = int(min(n_part, (budget - n_part * per_part) // per_gu))
-            self._keep_plan[key] = [False] * (n - n_part) + ["nogu"] * (n_part - n_full) + ["cheap"] * n_full
+            modes = [False] * (n - n_part) + ["nogu"] * (n_part - n_full) + ["cheap"] * n_full
+            if offload:
+                # two layers out of three: the forward produces gate|up faster than PCIe drains
+                # it, so a denser pattern would pile the copies up in device memory
+                from .offload import default_host_budget_bytes
+
+                host = self.offload_host_budget if self.offload_host_budget is not None \
+                    else default_host_budget_bytes()
+                slots = int(host // _pinned_bytes(per_gu))
+                j = 0
+                for li in range(n):
+                    if modes[li] == "nogu":
+                        if j % 3 != 2 and slots > 0:
+                            modes[li] = "offload"
+                            slots -= 1
+                        j += 1
+            self._keep_plan[key] = modes
         return self._keep_plan[key]
+
+    def set_offload(self, enabled: bool, host_budget_bytes: Optional[int] = None) -> None:
+        """Allow the memory plan to park gate|up outputs in pinned host memory (single
+        microbatch in flight only).  Clears the cached plan."""
+        self.offload_enabled = bool(enabled)
+        self.offload_host_budget = host_budget_bytes
+        self._keep_plan = {k: v for k, v in self._keep_plan.items() if k[0] != "modes"}
+
+    def prepare_offload(self, tokens: int, host_budget_bytes: Optional[int] = None) -> bool:
+        """Enable offloading for microbatches of up to ``tokens`` tokens and pin the host
+        memory now.  Returns False (offloading left disabled) when the plan has nothing to park
+        or the host refuses the pinned allocation."""
+        self.set_offload(True, host_budget_bytes)
+        keys = [li for li, m in enumerate(self._plan_modes(tokens)) if m == "offload"]
+        if keys:
+            try:
+                self._get_offloader(tokens).reserve_host(keys)
+                return True
+            except RuntimeError:
+                pass
+        self.disable_offload()
+        return False
+
+    def clear_plan(self) -> None:
+        self._keep_plan = {}
+
+    def disable_offload(self) -> None:
+        self._offloader = None
+        self.set_offload(False)
+
+    def _get_offloader(self, tokens: int):
+        from .offload import ActivationOffloader
+
+        numel = max(tokens, 1) * 2 * self.cfg.intermediate_size
+        if self._offloader is None or self._offloader.slot_numel < numel:
+            self._offloader = ActivationOffloader(self.device, numel)
+        return self._offloader
 
     def keep_summary(self, tokens: int) -> dict:
         modes = self._plan_modes(tokens)
+        if self._offloader is not None:
+            self._offloader.reap()
         return {"keep_all_gemm_outputs": sum(m in (True, "cheap") for m in modes),
+                "gate_up_in_host_memory": sum(m == "offload" for m in modes),
                 "keep_all_but_gate_up": sum(m == "nogu" for m in modes),
                 "recompute_layer": sum(m is False for m in modes)}
 
@@ -371,9 +441,28 @@ class DecoderStage:
         """Back-propagate ``dh`` (gradient w.r.t. this stage's output) through the layers;
         LoRA gradients accumulate in the arena.  Returns the gradient w.r.t. the stage input
         (``None`` on the first stage, whose input is the frozen embedding)."""
+        # gate|up outputs parked in host memory come back two layers ahead of their use
+        parked = [li for li in reversed(range(len(self.layers)))
+                  if saved[li].full is not None and "gu_off" in saved[li].full]
+        inflight: dict = {}
+
+        def fetch_ahead():
+            while parked and len(inflight) < 2:
+                nxt = parked.pop(0)
+                inflight[nxt] = self._offloader.prefetch(saved[nxt].full["gu_off"])
+
+        fetch_ahead()
         for li in reversed(range(len(self.layers))):
             need = not (self.is_first and li == 0)
+            slot = None
+            if li in inflight:
+                dev, ready, slot = inflight.pop(li)
+                fetch_ahead()
+                torch.cuda.current_stream(self.device).wait_event(ready)
+                saved[li].full = dict(saved[li].full, gu=dev)
             dh = self._layer_backward(li, saved[li], dh, batch, need_input_grad=need)
+            if slot is not None:
+                self._offloader.release(slot)
             saved[li] = None
         return dh
 

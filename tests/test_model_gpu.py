@@ -38,18 +38,26 @@ def test_engine_matches_autograd_oracle(model, quantize):
                                 max_mismatch_ratio=5e-3, msg=f"dB {key}")
 
 
-@pytest.mark.parametrize("mode", [False, "auto", "nogu"])
+@pytest.mark.parametrize("mode", [False, "auto", "nogu", "offload"])
 def test_recompute_is_bitwise_equivalent(mode):
     """Full recomputation, keeping everything, and the memory-planned mix (which keeps GEMM /
     attention outputs and rebuilds the elementwise ones) must give identical gradients."""
     s1, batch = _setup(recompute=True)
-    s2, _ = _setup(recompute="auto" if mode == "nogu" else mode)
+    s2, _ = _setup(recompute="auto" if mode in ("nogu", "offload") else mode)
     if mode == "nogu":  # first layer rebuilds gate|up from x2 and the kept S', second keeps it
         s2.force_keep_modes = ["nogu", "cheap"]
+    if mode == "offload":  # gate|up of both layers travels to pinned host memory and back
+        s2.force_keep_modes = ["offload", "offload"]
     l1 = s1.forward_backward(batch)
     l2 = s2.forward_backward(batch)
     assert float(l1) == float(l2)
     assert torch.equal(s1.arena.grad, s2.arena.grad)
+    if mode == "offload":
+        assert s2._offloader.bytes_out == 2 * batch.num_tokens * 2 * s2.cfg.intermediate_size * 2
+        # a second microbatch reuses the host slots and ring buffers
+        s1.arena.zero_grad(), s2.arena.zero_grad()
+        assert float(s1.forward_backward(batch)) == float(s2.forward_backward(batch))
+        assert torch.equal(s1.arena.grad, s2.arena.grad)
     if mode == "auto":
         assert s2._plan_keep(batch.num_tokens) == len(s2.layers)
 
