@@ -293,31 +293,6 @@ def main():
         if not ok:
             trainer.stage.disable_offload()
             torch.cuda.empty_cache()
-        # The plan provides for transient memory with a fixed allowance; measure what a step
-        # really leaves unused and hand all but a safety margin back to the plan.
-        torch.cuda.synchronize()
-        torch.cuda.reset_peak_memory_stats()
-        trainer.step_on_device(dev0)
-        torch.cuda.synchronize()
-        total = torch.cuda.mem_get_info()[1]
-        slack = torch.tensor([float(total - torch.cuda.max_memory_reserved() - (8 << 30))], device=device)
-        if world > 1:
-            dist.all_reduce(slack, op=dist.ReduceOp.MIN)
-        slack = int(slack.item())
-        if slack > (1 << 30):
-            old = trainer.stage.reserve_bytes
-            trainer.stage.reserve_bytes = max(1 << 30, old - slack)
-            trainer.stage.clear_plan()
-            try:
-                trainer.step_on_device(dev0)
-                torch.cuda.synchronize()
-                good = True
-            except torch.cuda.OutOfMemoryError:
-                good = False
-            if not agree(good):
-                trainer.stage.reserve_bytes = old
-                trainer.stage.clear_plan()
-                torch.cuda.empty_cache()
         del dev0, host0
 
     ms, toks, clocks, launches, loss_val, bytes_in = run_pass(e2e=False)

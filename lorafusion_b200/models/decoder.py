@@ -309,8 +309,9 @@ class DecoderStage:
             budget //= self.max_inflight
             offload = self.offload_enabled and self.max_inflight == 1
             if offload:
-                # ring of returning buffers + copies still on their way out
-                budget = max(0, budget - (3 + 4) * per_gu)
+                # copies still on their way out, and the ring of returning buffers unless it
+                # exists already (then it is no longer part of the free memory)
+                budget = max(0, budget - (4 + (3 if self._offloader is None else 0)) * per_gu)
             n_part = int(min(n, budget // per_part))
             n_full = int(min(n_part, (budget - n_part * per_part) // per_gu))
             modes = [False] * (n - n_part) + ["nogu"] * (n_part - n_full) + ["cheap"] * n_full
@@ -319,9 +320,9 @@ class DecoderStage:
                 # it, so a denser pattern would pile the copies up in device memory
                 from .offload import default_host_budget_bytes
 
-                host = self.offload_host_budget if self.offload_host_budget is not None \
-                    else default_host_budget_bytes()
-                slots = int(host // _pinned_bytes(per_gu))
+                if self.offload_host_budget is None:  # fixed at the first plan: pinning shrinks MemAvailable
+                    self.offload_host_budget = default_host_budget_bytes()
+                slots = int(self.offload_host_budget // _pinned_bytes(per_gu))
                 j = 0
                 for li in range(n):
                     if modes[li] == "nogu":
