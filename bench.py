@@ -198,6 +198,7 @@ def main():
                                grad_sync=args.grad_sync, use_multimem=args.multimem)
     if "expandable_segments:True" in os.environ.get("PYTORCH_CUDA_ALLOC_CONF", ""):
         trainer.stage.reserve_bytes = 16 << 30  # little fragmentation to provide for
+    trainer.stage.plan_activations(args.capacity)
     torch.cuda.synchronize()
     if rank == 0:
         print(f"[bench] model {cfg.name} built in {time.time() - t0:.1f}s, base weights "

@@ -123,6 +123,8 @@ class DecoderStage:
         self.max_inflight = max(1, max_inflight)
         self.reserve_bytes = reserve_bytes
         self._keep_plan: dict = {}
+        self._modes_plan: Optional[list] = None
+        self._modes_tokens = 0
         self.force_keep_modes: Optional[list] = None  # tests / experiments: per-layer keep mode
         self.offload_enabled = False      # park gate|up outputs in pinned host memory
         self.offload_host_budget: Optional[int] = None  # bytes; None = share of MemAvailable
@@ -297,8 +299,10 @@ class DecoderStage:
             return [False] * n
         if self.recompute is False:
             return [True] * n
-        key = ("modes", tokens)
-        if key not in self._keep_plan:
+        # One plan per stage, made for the largest microbatch seen (smaller ones just use less
+        # memory): the plan must not change between microbatches, or host buffers would be
+        # pinned in the middle of a step on some ranks and not on others.
+        if self._modes_plan is None or tokens > self._modes_tokens:
             free, _ = torch.cuda.mem_get_info(self.device)
             free += torch.cuda.memory_reserved(self.device) - torch.cuda.memory_allocated(self.device)
             per_full = self.saved_bytes_per_layer(tokens)
@@ -330,15 +334,22 @@ class DecoderStage:
                             modes[li] = "offload"
                             slots -= 1
                         j += 1
-            self._keep_plan[key] = modes
-        return self._keep_plan[key]
+            self._modes_plan, self._modes_tokens = modes, tokens
+        return self._modes_plan
+
+    def plan_activations(self, max_tokens: int) -> dict:
+        """Make the activation plan now, for microbatches of up to ``max_tokens`` tokens, while
+        no activations are alive (a plan made in the middle of a step sees less free memory)."""
+        self._modes_plan = None
+        self._plan_modes(max_tokens)
+        return self.keep_summary(max_tokens)
 
     def set_offload(self, enabled: bool, host_budget_bytes: Optional[int] = None) -> None:
         """Allow the memory plan to park gate|up outputs in pinned host memory (single
         microbatch in flight only).  Clears the cached plan."""
         self.offload_enabled = bool(enabled)
         self.offload_host_budget = host_budget_bytes
-        self._keep_plan = {k: v for k, v in self._keep_plan.items() if k[0] != "modes"}
+        self._modes_plan = None
 
     def prepare_offload(self, tokens: int, host_budget_bytes: Optional[int] = None) -> bool:
         """Enable offloading for microbatches of up to ``tokens`` tokens and pin the host
@@ -357,6 +368,7 @@ class DecoderStage:
 
     def clear_plan(self) -> None:
         self._keep_plan = {}
+        self._modes_plan = None
 
     def disable_offload(self) -> None:
         self._offloader = None

@@ -75,6 +75,8 @@ class ParallelTrainer:
             self.stage = TpDecoderStage(cfg, adapters, self.device, st.tp_group, max_tokens=engine.capacity, **kw)
         else:
             self.stage = DecoderStage(cfg, adapters, self.device, **kw)
+            if engine.recompute == "auto":
+                self.stage.plan_activations(engine.capacity)
         self._fused = None
         if grad_sync == "fused":
             from ..parallel.dp_sync import FusedGradSync
