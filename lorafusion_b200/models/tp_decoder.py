@@ -110,10 +110,8 @@ class TpDecoderStage(DecoderStage):
             n = full.arena.num_adapters
             for (l, proj), fv in full.arena.views.items():
                 lv = self.arena.views[(l, proj)]
-                for name in ("master", "work"):
+                for name in ("work",):  # padded layout; the dense fp32 master follows below
                     src, dst = getattr(full.arena, name), getattr(self.arena, name)
-                    if src is None or dst is None:
-                        continue
                     fa = src[fv.a_offset:fv.a_offset + n * fv.R * fv.K].view(n, fv.R, fv.K)
                     fb = src[fv.b_offset:fv.b_offset + n * fv.N * fv.R].view(n, fv.N, fv.R)
                     la = dst[lv.a_offset:lv.a_offset + n * lv.R * lv.K].view(n, lv.R, lv.K)
@@ -127,6 +125,7 @@ class TpDecoderStage(DecoderStage):
                         step = fv.K // tp
                         la.copy_(fa[:, :, r * step:(r + 1) * step])
                         lb.copy_(fb)
+            self.arena.sync_master_from_work()
         return self
 
     # ------------------------------------------------------------------ helpers
