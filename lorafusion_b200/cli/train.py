@@ -50,6 +50,25 @@ def main(argv=None) -> dict:
     if world > 1 and not dist.is_initialized():
         dist.init_process_group("nccl", device_id=device)
     setup_logging(rank)
+    health = None
+    if world > 1:
+        # heartbeats + failure notes in the rendezvous store: a rank that raised or left is
+        # noticed before the next launch instead of by a device-side wait running out
+        from ..parallel.health import HealthMonitor
+
+        health = HealthMonitor(dist.distributed_c10d._get_default_store(), rank, world, timeout=120.0).start()
+    try:
+        return _run(margs, targs, dargs, rank, world, device, health)
+    except Exception as e:  # noqa: BLE001
+        if health is not None:
+            health.report_failure(f"{type(e).__name__}: {e}")
+        raise
+    finally:
+        if health is not None:
+            health.stop()
+
+
+def _run(margs, targs, dargs, rank, world, device, health) -> dict:
 
     cfg = get_model_config(margs.model_name_or_path)
     if margs.num_layers_for_debugging:
@@ -86,6 +105,8 @@ def main(argv=None) -> dict:
     log_rank0(f"schedule: {json.dumps(provider.statistics())}")
 
     mbs = trainer.prepare(provider)
+    if health is not None:
+        health.check()
     n_warm = min(len(mbs) // 4, 2 * pp)
     torch.cuda.synchronize()
     if world > 1:
@@ -100,6 +121,8 @@ def main(argv=None) -> dict:
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
+    if health is not None:
+        health.check()
     torch.cuda.reset_peak_memory_stats()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
@@ -143,6 +166,8 @@ def main(argv=None) -> dict:
                          base_model_name=cfg.name)
     if world > 1:
         dist.barrier()
+        if health is not None:
+            health.stop()
         dist.destroy_process_group()
     return result
 

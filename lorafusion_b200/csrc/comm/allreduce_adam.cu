@@ -48,6 +48,7 @@ struct ArAdamParams {
   int epoch;
   int sync_mode;                     // 0 = no cross-rank flags, 1 = flags
   int use_multimem;
+  unsigned long long wait_ns;        // limit of every cross-rank flag wait
   unsigned int* done_counter;        // local, zero before launch, reset by the kernel
   float lr, beta1, beta2, eps, weight_decay, bias_c1, bias_c2, grad_scale;
   int* err;
@@ -95,7 +96,7 @@ allreduce_adam_kernel(const ArAdamParams p, int blocks_per_chunk) {
       st_release_sys(p.flags[threadIdx.x] + p.rank, p.epoch);
     }
     if (threadIdx.x < p.world) {
-      wait_flag_ge(p.flags[p.rank] + threadIdx.x, p.epoch, ctx);
+      wait_flag_ge(p.flags[p.rank] + threadIdx.x, p.epoch, ctx, p.wait_ns);
     }
     __syncthreads();
   }
@@ -186,7 +187,7 @@ allreduce_adam_kernel(const ArAdamParams p, int blocks_per_chunk) {
       if (threadIdx.x < p.world) {
         __threadfence_system();
         st_release_sys(p.flags[threadIdx.x] + kMaxRanks + p.rank, p.epoch);
-        wait_flag_ge(p.flags[p.rank] + kMaxRanks + threadIdx.x, p.epoch, ctx);
+        wait_flag_ge(p.flags[p.rank] + kMaxRanks + threadIdx.x, p.epoch, ctx, p.wait_ns);
       }
       if (threadIdx.x == 0) *p.done_counter = 0u;
     }
@@ -210,7 +211,8 @@ typedef struct LfArAdamArgs {
   void* done_counter;
   void* err;
   void* stream;
-  int num_chunks, rank, world, epoch, sync_mode, use_multimem, step, pad0;
+  int num_chunks, rank, world, epoch, sync_mode, use_multimem, step;
+  int wait_ms;  // limit of the cross-rank flag waits in milliseconds; 0 = the 10 s default
   float lr, beta1, beta2, eps, weight_decay, grad_scale;
 } LfArAdamArgs;
 
@@ -245,6 +247,7 @@ extern "C" int lf_allreduce_adam(const LfArAdamArgs* a) {
   p.bias_c2 = 1.f - powf(a->beta2, (float)a->step);
   p.grad_scale = a->grad_scale;
   p.err = (int*)a->err;
+  p.wait_ns = a->wait_ms > 0 ? (unsigned long long)a->wait_ms * 1000000ull : kPeerWaitNs;
   if (p.sync_mode && p.done_counter == nullptr) return -2;
   int bpc = (148 * 4 + a->num_chunks - 1) / a->num_chunks;
   if (bpc < 1) bpc = 1;

@@ -36,7 +36,7 @@ class LfArAdamArgs(C.Structure):
         ("err", C.c_void_p),
         ("stream", C.c_void_p),
         ("num_chunks", C.c_int), ("rank", C.c_int), ("world", C.c_int), ("epoch", C.c_int),
-        ("sync_mode", C.c_int), ("use_multimem", C.c_int), ("step", C.c_int), ("pad0", C.c_int),
+        ("sync_mode", C.c_int), ("use_multimem", C.c_int), ("step", C.c_int), ("wait_ms", C.c_int),
         ("lr", C.c_float), ("beta1", C.c_float), ("beta2", C.c_float), ("eps", C.c_float),
         ("weight_decay", C.c_float), ("grad_scale", C.c_float),
     ]
@@ -46,7 +46,7 @@ def launch_allreduce_adam(*, chunks: torch.Tensor, grad_ptrs, work_ptrs, grad_mc
                           master: torch.Tensor, m: torch.Tensor, v: torch.Tensor, flag_ptrs,
                           done_counter: Optional[torch.Tensor], rank: int, world: int, epoch: int,
                           sync: bool, use_multimem: bool, step: int, lr: float, beta1: float, beta2: float,
-                          eps: float, weight_decay: float, grad_scale: float, device) -> None:
+                          eps: float, weight_decay: float, grad_scale: float, device, wait_ms: int = 0) -> None:
     lib = nv.cuda_lib()
     if not getattr(lib, "_lf_ar_declared", False):
         lib.lf_allreduce_adam.argtypes = [C.POINTER(LfArAdamArgs)]
@@ -65,6 +65,7 @@ def launch_allreduce_adam(*, chunks: torch.Tensor, grad_ptrs, work_ptrs, grad_mc
     a.stream = nv.current_stream_ptr()
     a.num_chunks, a.rank, a.world, a.epoch = chunks.shape[0], rank, world, epoch
     a.sync_mode, a.use_multimem, a.step = int(sync), int(use_multimem), step
+    a.wait_ms = int(wait_ms)  # 0 = default limit (10 s) of the cross-rank flag waits
     a.lr, a.beta1, a.beta2, a.eps = lr, beta1, beta2, eps
     a.weight_decay, a.grad_scale = weight_decay, grad_scale
     nv.note_launch()

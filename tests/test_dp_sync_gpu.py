@@ -125,3 +125,41 @@ def test_two_real_ranks_over_peer_memory(tmp_path):
     outs = [p.communicate(timeout=300)[0] for p in procs]
     for r, (p, o) in enumerate(zip(procs, outs)):
         assert p.returncode == 0, f"rank {r} failed:\n{o[-3000:]}"
+
+
+def test_peer_that_never_signals_ends_in_an_error_status_not_a_hang():
+    """The fused sync kernel waits for every rank's "gradients ready" flag.  Here rank 1 does
+    not exist: its flag is never set, the (shortened) wait runs out, the kernel records the
+    failure and returns, the host reads the status, and the context stays usable."""
+    from lorafusion_b200.ops import _native
+    from lorafusion_b200.parallel.dp_sync import launch_allreduce_adam
+
+    a, ghost = _arena(), _arena(seed=1)
+    before = a.work.clone()
+    a.grad.normal_()
+    my_pad = torch.zeros(16, dtype=torch.int32, device="cuda")      # what peers would write to
+    ghost_pad = torch.zeros(16, dtype=torch.int32, device="cuda")   # what this rank writes to
+    done = torch.zeros(1, dtype=torch.int32, device="cuda")
+    hp = dict(lr=1e-2, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.0)
+    _native.check_device_errors()
+    t0 = torch.cuda.Event(enable_timing=True)
+    t1 = torch.cuda.Event(enable_timing=True)
+    t0.record()
+    launch_allreduce_adam(
+        chunks=a.chunk_table(0), grad_ptrs=[a.grad.data_ptr(), ghost.grad.data_ptr()],
+        work_ptrs=[a.work.data_ptr(), ghost.work.data_ptr()], grad_mc=0, work_mc=0, master=a.master, m=a.m,
+        v=a.v, flag_ptrs=[my_pad.data_ptr(), ghost_pad.data_ptr()], done_counter=done, rank=0, world=2, epoch=1,
+        sync=True, use_multimem=False, step=1, grad_scale=1.0, device="cuda", wait_ms=200, **hp)
+    t1.record()
+    with pytest.raises(RuntimeError, match="peer flag"):
+        _native.check_device_errors()
+    assert 150.0 < t0.elapsed_time(t1) < 5000.0           # gave up after the limit, did not spin on
+    assert int(ghost_pad[0]) == 1                          # it did announce itself to the peer
+    assert torch.equal(a.work, before)                     # and applied nothing
+    # the status word was cleared by the read; the same context runs the single-rank path fine
+    launch_allreduce_adam(
+        chunks=a.chunk_table(0), grad_ptrs=[a.grad.data_ptr()], work_ptrs=[a.work.data_ptr()], grad_mc=0,
+        work_mc=0, master=a.master, m=a.m, v=a.v, flag_ptrs=None, done_counter=None, rank=0, world=1, epoch=0,
+        sync=False, use_multimem=False, step=1, grad_scale=1.0, device="cuda", **hp)
+    _native.check_device_errors()
+    assert not torch.equal(a.work, before)
