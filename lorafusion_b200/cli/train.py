@@ -29,7 +29,7 @@ import torch
 import torch.distributed as dist
 
 from ..models.config import get_model_config
-from ..models.peft_io import save_adapter
+from ..models.peft_io import load_adapter, load_training_state, save_adapter, save_training_state
 from ..ops import _native
 from ..simulator import pipeline_sim as ps
 from ..solver import schedule as S
@@ -104,6 +104,16 @@ def _run(margs, targs, dargs, rank, world, device, health) -> dict:
         provider.schedule, provider.flat = sched, S.flatten_schedule(sched)
     log_rank0(f"schedule: {json.dumps(provider.statistics())}")
 
+    if targs.resume_from:
+        # adapters (PEFT layout) and optimizer state written by --save_adapters of an earlier run
+        if tp != 1:
+            raise ValueError("--resume_from needs tensor_parallel_size 1 (adapters are saved unsharded)")
+        for i, a in enumerate(adapters):
+            d = Path(targs.resume_from) / f"stage{trainer.state.pp_rank}" / a.name
+            load_adapter(trainer.stage.arena, i, d)
+            if (d / "training_state.pt").exists():
+                meta = load_training_state(trainer.stage.arena, i, d / "training_state.pt")
+                log_rank0(f"resumed {a.name}: optimizer step {meta['step']}, data cursor {meta['data_cursor']}")
     mbs = trainer.prepare(provider)
     if health is not None:
         health.check()
@@ -125,8 +135,12 @@ def _run(margs, targs, dargs, rank, world, device, health) -> dict:
         health.check()
     torch.cuda.reset_peak_memory_stats()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    from ..utils.benchmark import create_profiler_context
+
     e0.record()
-    stats = trainer.run(mbs)
+    with create_profiler_context(enabled=targs.profile and rank == 0,
+                                 output_dir=str(Path(targs.output_dir) / "profile"), scheduled=False):
+        stats = trainer.run(mbs)
     e1.record()
     torch.cuda.synchronize()
     _native.check_device_errors()
@@ -162,8 +176,10 @@ def _run(margs, targs, dargs, rank, world, device, health) -> dict:
         print(json.dumps(result))
     if targs.save_adapters and trainer.state.dp_rank == 0 and tp == 1:
         for i, a in enumerate(adapters):
-            save_adapter(trainer.stage.arena, i, Path(targs.output_dir) / f"stage{trainer.state.pp_rank}" / a.name,
-                         base_model_name=cfg.name)
+            d = Path(targs.output_dir) / f"stage{trainer.state.pp_rank}" / a.name
+            save_adapter(trainer.stage.arena, i, d, base_model_name=cfg.name)
+            save_training_state(trainer.stage.arena, i, d / "training_state.pt",
+                                data_cursor=trainer.manager.steps_taken.get(i, 0) * gbs_global[i])
     if world > 1:
         dist.barrier()
         if health is not None:

@@ -49,6 +49,13 @@ def get_pipeline_stage_layer_indices(num_layers: int, num_stages: int, stage_idx
     return list(range(s, e))
 
 
+# The reference marks a no-op microbatch by sending input ids filled with this value
+# (``lorafusion/pipeline_parallel/multi_lora_schedule.py``); here the schedule is known to every
+# stage, so ``PipelineMicrobatch.is_empty`` carries the information and nothing is sent.  The
+# constant is kept for schedule files that use it.
+EMPTY_BATCH_MAGIC_TOKEN = 7
+
+
 @dataclass
 class PipelineMicrobatch:
     """What one stage needs to know about a microbatch: its device batch (``None`` for an

@@ -114,13 +114,17 @@ def nvtx_range(name: str):
 
 
 def create_profiler_context(enabled: bool = True, output_dir: str = "./profiling-results", *, skip_first: int = 0,
-                            wait: int = 0, warmup: int = 1, active: int = 3):
-    """torch.profiler (CPU + CUDA) with a Chrome/TensorBoard trace handler, or a no-op."""
+                            wait: int = 0, warmup: int = 1, active: int = 3, scheduled: bool = True):
+    """torch.profiler (CPU + CUDA) with a Chrome/TensorBoard trace handler, or a no-op.
+    ``scheduled=False`` records everything inside the ``with`` block (no ``step()`` calls
+    needed) and writes the trace on exit."""
     if not enabled:
         return contextlib.nullcontext()
     from torch.profiler import ProfilerActivity, profile, schedule, tensorboard_trace_handler
 
     acts = [ProfilerActivity.CPU] + ([ProfilerActivity.CUDA] if torch.cuda.is_available() else [])
+    if not scheduled:
+        return profile(activities=acts, on_trace_ready=tensorboard_trace_handler(output_dir))
     return profile(activities=acts, schedule=schedule(skip_first=skip_first, wait=wait, warmup=warmup, active=active),
                    on_trace_ready=tensorboard_trace_handler(output_dir), record_shapes=True)
 
