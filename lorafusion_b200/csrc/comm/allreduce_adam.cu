@@ -131,8 +131,11 @@ allreduce_adam_kernel(const ArAdamParams p, int blocks_per_chunk) {
         }
       }
       float gv[4] = {g.x * p.grad_scale, g.y * p.grad_scale, g.z * p.grad_scale, g.w * p.grad_scale};
-      const long long col0 = (i4 << 2) % c.ld;
-      const long long row = (i4 << 2) / c.ld;
+      // 32-bit arithmetic: the arena builder rejects regions of 2^31 elements or more
+      const unsigned e32 = unsigned(i4) << 2;
+      const unsigned row32 = e32 / unsigned(c.ld);
+      const long long col0 = e32 - row32 * unsigned(c.ld);
+      const long long row = row32;
       if (col0 + 4 <= c.col0 || col0 >= c.col0 + c.cols) continue;  // padding: cleared only
       // optimizer state is dense over the trainable window: (row, col) -> state + row*cols + col-col0
       const long long s0 = c.state + row * c.cols + (col0 - c.col0);

@@ -146,6 +146,17 @@ struct AdamHyper {
   float grad_scale;        // multiplies the accumulated gradient before the update
 };
 
+__device__ __forceinline__ void adam_one(float g, float& w, float& mi, float& vi, const AdamHyper& h,
+                                         float inv_c1, float inv_sqrt_c2) {
+  mi = h.beta1 * mi + (1.f - h.beta1) * g;
+  vi = h.beta2 * vi + (1.f - h.beta2) * g * g;
+  w -= h.lr * h.weight_decay * w;
+  w -= h.lr * (mi * inv_c1) / (sqrtf(vi) * inv_sqrt_c2 + h.eps);
+}
+
+// One chunk is shared by `blocks_per_chunk` CTAs.  Regions whose offsets and sizes are all
+// multiples of four elements (every region the adapter arenas produce) go through 16-byte
+// accesses with 32-bit index arithmetic; anything else takes the scalar path.
 __global__ void __launch_bounds__(256)
 adam_chunks_kernel(const AdamChunk* __restrict__ chunks, int num_chunks, float* __restrict__ grad,
                    float* __restrict__ master, float* __restrict__ m, float* __restrict__ v,
@@ -157,6 +168,39 @@ adam_chunks_kernel(const AdamChunk* __restrict__ chunks, int num_chunks, float* 
   const float inv_c1 = 1.f / h.bias_c1;
   const float inv_sqrt_c2 = rsqrtf(h.bias_c2);
   const long long total = c.rows * c.ld;
+  const bool vec = (((c.offset | c.ld | c.col0 | c.cols | c.state) & 3) == 0) && total < (1ll << 31);
+  if (vec) {
+    float4* g4p = reinterpret_cast<float4*>(grad + c.offset);
+    const unsigned n4 = unsigned(total >> 2);
+    const unsigned ld = unsigned(c.ld), col0 = unsigned(c.col0), cols = unsigned(c.cols);
+    const unsigned stride = unsigned(blocks_per_chunk) * 256u;
+    for (unsigned i4 = unsigned(sub) * 256u + threadIdx.x; i4 < n4; i4 += stride) {
+      const float4 g = g4p[i4];
+      g4p[i4] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (cols == 0) continue;  // padding: cleared only
+      const unsigned e = i4 << 2;
+      const unsigned row = e / ld;
+      const unsigned col = e - row * ld;
+      if (col < col0 || col >= col0 + cols) continue;
+      const long long se = c.state + (long long)row * cols + (col - col0);
+      float4 w4 = *reinterpret_cast<const float4*>(master + se);
+      float4 m4 = *reinterpret_cast<const float4*>(m + se);
+      float4 v4 = *reinterpret_cast<const float4*>(v + se);
+      adam_one(g.x * h.grad_scale, w4.x, m4.x, v4.x, h, inv_c1, inv_sqrt_c2);
+      adam_one(g.y * h.grad_scale, w4.y, m4.y, v4.y, h, inv_c1, inv_sqrt_c2);
+      adam_one(g.z * h.grad_scale, w4.z, m4.z, v4.z, h, inv_c1, inv_sqrt_c2);
+      adam_one(g.w * h.grad_scale, w4.w, m4.w, v4.w, h, inv_c1, inv_sqrt_c2);
+      *reinterpret_cast<float4*>(master + se) = w4;
+      *reinterpret_cast<float4*>(m + se) = m4;
+      *reinterpret_cast<float4*>(v + se) = v4;
+      __nv_bfloat162 lo = __floats2bfloat162_rn(w4.x, w4.y), hi = __floats2bfloat162_rn(w4.z, w4.w);
+      uint2 packed;
+      packed.x = *reinterpret_cast<uint32_t*>(&lo);
+      packed.y = *reinterpret_cast<uint32_t*>(&hi);
+      *reinterpret_cast<uint2*>(work + c.offset + e) = packed;
+    }
+    return;
+  }
   for (long long i = sub * 256LL + threadIdx.x; i < total; i += blocks_per_chunk * 256LL) {
     const long long e = c.offset + i;
     const float g = grad[e] * h.grad_scale;
@@ -164,13 +208,10 @@ adam_chunks_kernel(const AdamChunk* __restrict__ chunks, int num_chunks, float* 
     const long long col = i % c.ld;
     if (col < c.col0 || col >= c.col0 + c.cols) continue;
     const long long se = c.state + (i / c.ld) * c.cols + (col - c.col0);
-    float w = master[se];
-    const float mi = h.beta1 * m[se] + (1.f - h.beta1) * g;
-    const float vi = h.beta2 * v[se] + (1.f - h.beta2) * g * g;
+    float w = master[se], mi = m[se], vi = v[se];
+    adam_one(g, w, mi, vi, h, inv_c1, inv_sqrt_c2);
     m[se] = mi;
     v[se] = vi;
-    w -= h.lr * h.weight_decay * w;
-    w -= h.lr * (mi * inv_c1) / (sqrtf(vi) * inv_sqrt_c2 + h.eps);
     master[se] = w;
     work[e] = __float2bfloat16(w);
   }

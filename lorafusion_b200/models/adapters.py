@@ -213,6 +213,8 @@ class LoRAArena:
                     else:
                         rows.append((b_base + n0 * v.R, size, v.R, 0, 0, 0))
                     n0 += size
+            if any(r[1] * r[2] >= 2 ** 31 for r in rows):
+                raise ValueError("an adapter region of 2^31 elements or more is not supported by the optimizer kernels")
             self._chunk_rows[adapter] = rows
             self.state_range[adapter] = (lo, state)
         self.state_numel = max(state, 4)

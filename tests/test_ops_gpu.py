@@ -105,16 +105,21 @@ def test_adam_chunks_matches_torch():
     opt = torch.optim.AdamW([ref], lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
     # two regions: a flat one and a 2-D one where only columns [8, 24) of 32 are trainable;
     # the optimizer state is dense: 1000 elements, then the 100 x 16 window row by row
-    chunks = torch.tensor([[0, 1, 1000, 0, 1000, 0], [1024, 100, 32, 8, 16, 1000]], dtype=torch.int64,
-                          device="cuda")
+    # (a third region with odd offsets and sizes takes the kernel's scalar path)
+    chunks = torch.tensor([[0, 1, 1000, 0, 1000, 0], [1024, 100, 32, 8, 16, 1000],
+                           [4301, 10, 30, 3, 10, 2600]], dtype=torch.int64, device="cuda")
     trainable = torch.zeros(n, dtype=torch.bool, device="cuda")
     trainable[:1000] = True
     blk = torch.zeros(100, 32, dtype=torch.bool, device="cuda")
     blk[:, 8:24] = True
     trainable[1024:1024 + 3200] = blk.view(-1)
+    blk3 = torch.zeros(10, 30, dtype=torch.bool, device="cuda")
+    blk3[:, 3:13] = True
+    trainable[4301:4601] = blk3.view(-1)
 
     def dense(t):
-        return torch.cat([t[:1000], t[1024:4224].view(100, 32)[:, 8:24].reshape(-1)])
+        return torch.cat([t[:1000], t[1024:4224].view(100, 32)[:, 8:24].reshape(-1),
+                          t[4301:4601].view(10, 30)[:, 3:13].reshape(-1)])
 
     master = dense(init).clone()
     m, v = torch.zeros_like(master), torch.zeros_like(master)
@@ -127,6 +132,7 @@ def test_adam_chunks_matches_torch():
         ew.adam_chunks(chunks, grad, master, m, v, work, lr=1e-2, beta1=0.9, beta2=0.95, eps=1e-8,
                        weight_decay=0.1, step=step, grad_scale=0.5)
         assert float(grad[:1000].abs().max()) == 0.0 and float(grad[1024:4224].abs().max()) == 0.0
+        assert float(grad[4301:4601].abs().max()) == 0.0 and float(grad[4224:4301].abs().min()) > 0.0
     assert_close(master, dense(ref.detach()), rtol=1e-4, atol=1e-5, msg="adam master")
     assert_close(work[trainable], ref.detach()[trainable].to(torch.bfloat16), msg="adam bf16 copy")
     assert torch.equal(work[~trainable], init.to(torch.bfloat16)[~trainable])
