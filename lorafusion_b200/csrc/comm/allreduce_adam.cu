@@ -33,8 +33,17 @@ struct ArAdamChunk {
   long long offset, rows, ld, col0, cols, state;
 };
 
+// {chunk, first element, element count} (multiples of 4): the part of a chunk one CTA handles.
+// The host cuts THIS RANK's slice of every chunk into equal pieces, so that the CTAs are
+// balanced although chunk sizes differ by two orders of magnitude.
+struct ArAdamWorkItem {
+  int chunk;
+  unsigned first, count;
+};
+
 struct ArAdamParams {
   const ArAdamChunk* chunks;
+  const ArAdamWorkItem* items;
   int num_chunks;
   int rank, world;
   float* grad[kMaxRanks];            // peer pointers to the fp32 gradient arenas
@@ -83,7 +92,7 @@ __device__ __forceinline__ float adam_update(float g, float& w, float& mi, float
 }
 
 __global__ void __launch_bounds__(256)
-allreduce_adam_kernel(const ArAdamParams p, int blocks_per_chunk) {
+allreduce_adam_kernel(const ArAdamParams p) {
   __shared__ int abort_smem;
   if (threadIdx.x == 0) abort_smem = 0;
   __syncthreads();
@@ -102,32 +111,37 @@ allreduce_adam_kernel(const ArAdamParams p, int blocks_per_chunk) {
   }
 
   if (!aborted(ctx)) {
-    const int chunk = blockIdx.x / blocks_per_chunk;
-    const int sub = blockIdx.x % blocks_per_chunk;
-    const ArAdamChunk c = p.chunks[chunk];
+    const ArAdamWorkItem item = p.items[blockIdx.x];
+    const ArAdamChunk c = p.chunks[item.chunk];
     const float inv_c1 = 1.f / p.bias_c1;
     const float inv_sqrt_c2 = rsqrtf(p.bias_c2);
-    // the chunk is cut in `world` slices of whole 4-element groups; this rank owns slice `rank`
+    // every chunk is cut in `world` slices of whole 4-element groups (ld and offsets are
+    // multiples of 4); the work items of this launch cover slice `rank` of every chunk
     const bool aligned4 = ((c.cols | c.col0 | c.state) & 3) == 0;
-    const long long total4 = (c.rows * c.ld) >> 2;   // ld and offsets are multiples of 4
-    const long long per = (total4 + p.world - 1) / p.world;
-    const long long lo4 = min(total4, per * p.rank), hi4 = min(total4, per * (p.rank + 1));
-    for (long long i4 = lo4 + sub * 256LL + threadIdx.x; i4 < hi4; i4 += blocks_per_chunk * 256LL) {
+    const long long lo4 = item.first >> 2, hi4 = (item.first + item.count) >> 2;
+    for (long long i4 = lo4 + threadIdx.x; i4 < hi4; i4 += 256) {
       const long long e = c.offset + (i4 << 2);
       float4 g;
       if (p.use_multimem) {
         g = multimem_ld_reduce_f32x4(p.grad_mc + e);
         multimem_st_f32x4(p.grad_mc + e, make_float4(0.f, 0.f, 0.f, 0.f));
       } else {
+        // all ranks' loads are issued before the first use: a peer load takes microseconds,
+        // and one after the other they would bound the kernel by latency
+        uint4 t[kMaxRanks];
+#pragma unroll
+        for (int r = 0; r < kMaxRanks; ++r)
+          if (r < p.world) t[r] = ld_global_v4(p.grad[r] + e);
         g = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int r = 0; r < p.world; ++r) {
-          float4* src = reinterpret_cast<float4*>(p.grad[r] + e);
-          const float4 t = *src;
-          g.x += t.x;
-          g.y += t.y;
-          g.z += t.z;
-          g.w += t.w;
-          *src = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int r = 0; r < kMaxRanks; ++r) {  // fixed rank order: bitwise identical on every rank
+          if (r < p.world) {
+            g.x += __uint_as_float(t[r].x);
+            g.y += __uint_as_float(t[r].y);
+            g.z += __uint_as_float(t[r].z);
+            g.w += __uint_as_float(t[r].w);
+            *reinterpret_cast<float4*>(p.grad[r] + e) = make_float4(0.f, 0.f, 0.f, 0.f);
+          }
         }
       }
       float gv[4] = {g.x * p.grad_scale, g.y * p.grad_scale, g.z * p.grad_scale, g.w * p.grad_scale};
@@ -203,6 +217,8 @@ using namespace lf;
 
 typedef struct LfArAdamArgs {
   const void* chunks;
+  const void* items;   // ArAdamWorkItem[num_items] on the device
+  long long num_items;
   void* grad[8];
   void* work[8];
   void* grad_mc;
@@ -220,10 +236,11 @@ typedef struct LfArAdamArgs {
 } LfArAdamArgs;
 
 extern "C" int lf_allreduce_adam(const LfArAdamArgs* a) {
-  if (a == nullptr || a->num_chunks <= 0) return 0;
+  if (a == nullptr || a->num_chunks <= 0 || a->num_items <= 0) return 0;
   if (a->world < 1 || a->world > kMaxRanks || a->rank < 0 || a->rank >= a->world) return -1;
   ArAdamParams p;
   p.chunks = (const ArAdamChunk*)a->chunks;
+  p.items = (const ArAdamWorkItem*)a->items;
   p.num_chunks = a->num_chunks;
   p.rank = a->rank;
   p.world = a->world;
@@ -252,11 +269,8 @@ extern "C" int lf_allreduce_adam(const LfArAdamArgs* a) {
   p.err = (int*)a->err;
   p.wait_ns = a->wait_ms > 0 ? (unsigned long long)a->wait_ms * 1000000ull : kPeerWaitNs;
   if (p.sync_mode && p.done_counter == nullptr) return -2;
-  int bpc = (148 * 4 + a->num_chunks - 1) / a->num_chunks;
-  if (bpc < 1) bpc = 1;
-  if (bpc > 32) bpc = 32;
   // Blocks only ever wait on flags written by other GPUs, never on sibling blocks, so the
   // grid may exceed what is resident at once.
-  allreduce_adam_kernel<<<a->num_chunks * bpc, 256, 0, (cudaStream_t)a->stream>>>(p, bpc);
+  allreduce_adam_kernel<<<(unsigned)a->num_items, 256, 0, (cudaStream_t)a->stream>>>(p);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }

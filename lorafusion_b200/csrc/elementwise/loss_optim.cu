@@ -154,27 +154,33 @@ __device__ __forceinline__ void adam_one(float g, float& w, float& mi, float& vi
   w -= h.lr * (mi * inv_c1) / (sqrtf(vi) * inv_sqrt_c2 + h.eps);
 }
 
-// One chunk is shared by `blocks_per_chunk` CTAs.  Regions whose offsets and sizes are all
-// multiples of four elements (every region the adapter arenas produce) go through 16-byte
-// accesses with 32-bit index arithmetic; anything else takes the scalar path.
+// One CTA per work item {chunk, first element, element count}: regions differ in size by two
+// orders of magnitude (a 16 x 8192 A block next to a 57344 x 64 B block), so the host cuts
+// them into equal pieces instead of giving every region the same number of CTAs.  Regions
+// whose offsets and sizes are all multiples of four elements (every region the adapter arenas
+// produce) go through 16-byte accesses with 32-bit index arithmetic; anything else takes the
+// scalar path.
+struct AdamWorkItem {
+  int chunk;
+  unsigned first, count;  // elements; multiples of 4 inside vectorisable regions
+};
+
 __global__ void __launch_bounds__(256)
-adam_chunks_kernel(const AdamChunk* __restrict__ chunks, int num_chunks, float* __restrict__ grad,
-                   float* __restrict__ master, float* __restrict__ m, float* __restrict__ v,
-                   __nv_bfloat16* __restrict__ work, AdamHyper h, int blocks_per_chunk) {
-  const int chunk = blockIdx.x / blocks_per_chunk;
-  const int sub = blockIdx.x % blocks_per_chunk;
-  if (chunk >= num_chunks) return;
-  const AdamChunk c = chunks[chunk];
+adam_chunks_kernel(const AdamChunk* __restrict__ chunks, const AdamWorkItem* __restrict__ items,
+                   float* __restrict__ grad, float* __restrict__ master, float* __restrict__ m,
+                   float* __restrict__ v, __nv_bfloat16* __restrict__ work, AdamHyper h) {
+  const AdamWorkItem item = items[blockIdx.x];
+  const AdamChunk c = chunks[item.chunk];
   const float inv_c1 = 1.f / h.bias_c1;
   const float inv_sqrt_c2 = rsqrtf(h.bias_c2);
   const long long total = c.rows * c.ld;
-  const bool vec = (((c.offset | c.ld | c.col0 | c.cols | c.state) & 3) == 0) && total < (1ll << 31);
+  const bool vec = (((c.offset | c.ld | c.col0 | c.cols | c.state) & 3) == 0) && total < (1ll << 31) &&
+                   ((item.first | item.count) & 3u) == 0;
   if (vec) {
     float4* g4p = reinterpret_cast<float4*>(grad + c.offset);
-    const unsigned n4 = unsigned(total >> 2);
     const unsigned ld = unsigned(c.ld), col0 = unsigned(c.col0), cols = unsigned(c.cols);
-    const unsigned stride = unsigned(blocks_per_chunk) * 256u;
-    for (unsigned i4 = unsigned(sub) * 256u + threadIdx.x; i4 < n4; i4 += stride) {
+    const unsigned end4 = (item.first + item.count) >> 2;
+    for (unsigned i4 = (item.first >> 2) + threadIdx.x; i4 < end4; i4 += 256u) {
       const float4 g = g4p[i4];
       g4p[i4] = make_float4(0.f, 0.f, 0.f, 0.f);
       if (cols == 0) continue;  // padding: cleared only
@@ -201,7 +207,7 @@ adam_chunks_kernel(const AdamChunk* __restrict__ chunks, int num_chunks, float* 
     }
     return;
   }
-  for (long long i = sub * 256LL + threadIdx.x; i < total; i += blocks_per_chunk * 256LL) {
+  for (long long i = (long long)item.first + threadIdx.x; i < (long long)item.first + item.count; i += 256) {
     const long long e = c.offset + i;
     const float g = grad[e] * h.grad_scale;
     grad[e] = 0.f;
@@ -232,11 +238,14 @@ int lf_cross_entropy(void* logits, const int* labels, float* loss, long long M, 
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
-// chunks: device array of AdamChunk {int64 offset, rows, ld, col0, cols, state}
-int lf_adam_chunks(const void* chunks, int num_chunks, float* grad, float* master, float* m,
-                   float* v, void* work, float lr, float beta1, float beta2, float eps,
+// chunks: device array of AdamChunk {int64 offset, rows, ld, col0, cols, state};
+// items: device array of AdamWorkItem {int32 chunk, uint32 first, uint32 count} covering every
+// element of every chunk exactly once (first and count multiples of 4 unless the chunk has odd
+// offsets or sizes).
+int lf_adam_chunks(const void* chunks, const void* items, int num_items, float* grad, float* master,
+                   float* m, float* v, void* work, float lr, float beta1, float beta2, float eps,
                    float weight_decay, int step, float grad_scale, void* stream) {
-  if (num_chunks <= 0) return 0;
+  if (num_items <= 0) return 0;
   AdamHyper h;
   h.lr = lr;
   h.beta1 = beta1;
@@ -246,11 +255,8 @@ int lf_adam_chunks(const void* chunks, int num_chunks, float* grad, float* maste
   h.bias_c1 = 1.f - powf(beta1, (float)step);
   h.bias_c2 = 1.f - powf(beta2, (float)step);
   h.grad_scale = grad_scale;
-  int bpc = (148 * 8 + num_chunks - 1) / num_chunks;
-  if (bpc < 1) bpc = 1;
-  if (bpc > 64) bpc = 64;
-  adam_chunks_kernel<<<num_chunks * bpc, 256, 0, (cudaStream_t)stream>>>(
-      (const AdamChunk*)chunks, num_chunks, grad, master, m, v, (__nv_bfloat16*)work, h, bpc);
+  adam_chunks_kernel<<<num_items, 256, 0, (cudaStream_t)stream>>>(
+      (const AdamChunk*)chunks, (const AdamWorkItem*)items, grad, master, m, v, (__nv_bfloat16*)work, h);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 

@@ -64,8 +64,8 @@ int lf_gemm(const LfGemmArgs* args);
 //     (own shard already in place); the kernel pushes the own shard to `ag_peer_dst[q]` and
 //     signals `ag_peer_flags[q][rank * tiles_per_shard + tile] = epoch`; it waits on its own
 //     `ag_flags`.  `ag2_*` optionally gathers the LoRA slab operand the same way.
-//   mode 2 (GEMM -> reduce-scatter): partial tiles go to `rs_peer_stage[owner]`
-//     ([world, M / world, N] bf16), the flag
+//   mode 2 (GEMM -> reduce-scatter): partial tiles go to this rank's own `rs_peer_stage[rank]`
+//     ([M, N] bf16; the owner of a row reads it from every source's stage), the flag
 //     `rs_peer_cnt[owner][(rank * tiles_per_shard + tile) * num_n_tiles + n_tile]` is set to
 //     `epoch`, and rows owned by this rank are reduced into `rs_out` (+ optional
 //     `rs_residual`) once the matching flags in `rs_cnt` carry `epoch` (`rs_target` is unused).

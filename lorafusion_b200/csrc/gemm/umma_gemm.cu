@@ -73,10 +73,11 @@ __constant__ float kNf4Values[16] = {
 //           computes; extra warps push this rank's shard to every peer with plain stores over
 //           NVLink and raise one flag per row tile; the TMA producer waits for the flag of a
 //           tile's source rank before loading it (own shard first).
-//  TP == 2  GEMM -> reduce-scatter: the epilogue stores each bf16 partial tile straight into
-//           the staging buffer of the rank that owns those token rows (peer stores), raises a
-//           per-(source, row tile, column tile) epoch flag there, and once its GEMM tiles are
-//           done every CTA sums the partials of the rows this rank owns (fp32) as they arrive.
+//  TP == 2  GEMM -> reduce-scatter: the epilogue stores each bf16 partial tile into this GPU's
+//           own staging buffer and raises a per-(source, row tile, column tile) epoch flag in
+//           the memory of the rank that owns those token rows; four extra warps, concurrent
+//           with the GEMM, pull the partials of the rows this rank owns from every source with
+//           coalesced peer loads as their flags arrive and sum them in fp32 (+ residual).
 struct TpParams {
   int rank, world, tiles_per_shard, epoch;
   const int* ag_flags;
@@ -147,7 +148,7 @@ constexpr int kNumCommWarps = 4;
 template <int BN, int NACC, bool A_MN, bool B_MN, bool B2_MN, int EPI, bool MASK_A, int TP = 0,
           bool NF4B = false>
 __global__ void __launch_bounds__((MASK_A || NF4B) ? (192 + 32 * kNumMaskWarps)
-                                                   : (TP == 1 ? 192 + 32 * kNumCommWarps : 192), 1)
+                                                   : (TP != 0 ? 192 + 32 * kNumCommWarps : 192), 1)
     umma_gemm_kernel(const GemmKParams p, const __grid_constant__ CUtensorMap tmA,
                      const __grid_constant__ CUtensorMap tmB,
                      const __grid_constant__ CUtensorMap tmA2,
@@ -435,9 +436,10 @@ __global__ void __launch_bounds__((MASK_A || NF4B) ? (192 + 32 * kNumMaskWarps)
           if (row < p.M) {
             __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.out) + (long long)row * p.ldo;
             if (TP == 2) {
-              const int ms = tp.tiles_per_shard * BM;
-              const int owner = row / ms;
-              out = tp.rs_peer_stage[owner] + ((long long)tp.rank * ms + (row - owner * ms)) * p.N;
+              // partial tiles stay in THIS GPU's stage [M, N]; the owner of the rows pulls them
+              // (row-per-thread stores are merged in the local L2; pushed over NVLink they
+              // would travel as 16-byte writes)
+              out = tp.rs_peer_stage[tp.rank] + (long long)row * p.N;
             }
 #pragma unroll
             for (int g = 0; g < 4; ++g) {
@@ -471,44 +473,68 @@ __global__ void __launch_bounds__((MASK_A || NF4B) ? (192 + 32 * kNumMaskWarps)
         }
       }
     }
-    if (TP == 2 && ok) {
-      // ---- reduce the partials of the rows this rank owns, as they arrive ----
-      const int et = threadIdx.x - 64;  // 0..127
-      const int ms = tp.tiles_per_shard * BM;
-      const int items = tp.tiles_per_shard * p.num_n_tiles;
-      constexpr int VEC_PER_ROW = BN / 8;
-      for (int item = blockIdx.x; ok && item < items; item += gridDim.x) {
-        const int lt = item / p.num_n_tiles, nt = item - lt * p.num_n_tiles;
-        if (et < tp.world) {
-          if (!wait_flag_ge(tp.rs_cnt + (et * tp.tiles_per_shard + lt) * p.num_n_tiles + nt, tp.epoch, ctx))
-            ok = false;
-        }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (aborted(ctx)) {
+  } else if (TP == 2) {
+    // ---- reduce the partials of the rows this rank owns, as they arrive ----
+    // Four dedicated warps, concurrent with the GEMM of the other warps: they poll the
+    // per-(source, row tile, column tile) flags and sum the bf16 partials in fp32 (+ residual).
+    // Every thread keeps the loads of two output vectors from all sources in flight.
+    const int et = threadIdx.x - 192;  // 0..127
+    const int ms = tp.tiles_per_shard * BM;
+    const int items = tp.tiles_per_shard * p.num_n_tiles;
+    constexpr int VEC_PER_ROW = BN / 8;
+    constexpr int NV = BM * VEC_PER_ROW;
+    bool ok = true;
+    for (int item = blockIdx.x; ok && item < items; item += gridDim.x) {
+      const int lt = item / p.num_n_tiles, nt = item - lt * p.num_n_tiles;
+      if (et < tp.world) {
+        if (!wait_flag_ge(tp.rs_cnt + (et * tp.tiles_per_shard + lt) * p.num_n_tiles + nt, tp.epoch, ctx))
           ok = false;
-          break;
-        }
-        for (int v = et; v < BM * VEC_PER_ROW; v += 128) {
+      }
+      asm volatile("bar.sync 2, 128;" ::: "memory");
+      if (aborted(ctx)) {
+        ok = false;
+        break;
+      }
+      // row of this item inside every source's stage [M, N]
+      const long long grow0 = (long long)tp.rank * ms;
+      for (int v0 = et; v0 < NV; v0 += 256) {
+        uint4 raw[2][8];
+        uint4 res[2];
+        long long out_off[2];
+        bool live[2];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const int v = v0 + u * 128;
           const int lr = lt * BM + v / VEC_PER_ROW;
           const int col = nt * BN + (v % VEC_PER_ROW) * 8;
-          if (col >= p.N) continue;
+          live[u] = v < NV && col < p.N;
+          out_off[u] = (long long)lr * tp.rs_ldo + col;
+#pragma unroll
+          for (int src = 0; src < 8; ++src)
+            if (live[u] && src < tp.world)
+              raw[u][src] = ld_global_v4(tp.rs_peer_stage[src] + (grow0 + lr) * p.N + col);
+          if (live[u] && tp.rs_residual != nullptr) res[u] = ld_global_v4(tp.rs_residual + out_off[u]);
+        }
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          if (!live[u]) continue;
           float acc[8];
 #pragma unroll
           for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-          for (int src = 0; src < tp.world; ++src) {
-            const uint4 raw = *reinterpret_cast<const uint4*>(
-                tp.rs_peer_stage[tp.rank] + ((long long)src * ms + lr) * p.N + col);
-            const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const float2 f = unpack_bf16x2(w[j]);
-              acc[2 * j] += f.x;
-              acc[2 * j + 1] += f.y;
+          for (int src = 0; src < 8; ++src) {
+            if (src < tp.world) {
+              const uint32_t w[4] = {raw[u][src].x, raw[u][src].y, raw[u][src].z, raw[u][src].w};
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const float2 f = unpack_bf16x2(w[j]);
+                acc[2 * j] += f.x;
+                acc[2 * j + 1] += f.y;
+              }
             }
           }
           if (tp.rs_residual != nullptr) {
-            const uint4 raw = *reinterpret_cast<const uint4*>(tp.rs_residual + (long long)lr * tp.rs_ldo + col);
-            const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+            const uint32_t w[4] = {res[u].x, res[u].y, res[u].z, res[u].w};
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               const float2 f = unpack_bf16x2(w[j]);
@@ -516,8 +542,8 @@ __global__ void __launch_bounds__((MASK_A || NF4B) ? (192 + 32 * kNumMaskWarps)
               acc[2 * j + 1] += f.y;
             }
           }
-          st_global_v4(tp.rs_out + (long long)lr * tp.rs_ldo + col, pack_bf16x2(acc[0], acc[1]),
-                       pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7]));
+          st_global_v4(tp.rs_out + out_off[u], pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]),
+                       pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7]));
         }
       }
     }
@@ -723,7 +749,7 @@ static int launch_variant(const GemmKParams& kp, const CUtensorMap& tA, const CU
     }
     configured = true;
   }
-  const int threads = (MASK_A || NF4B) ? (192 + 32 * kNumMaskWarps) : (TP == 1 ? 192 + 32 * kNumCommWarps : 192);
+  const int threads = (MASK_A || NF4B) ? (192 + 32 * kNumMaskWarps) : (TP != 0 ? 192 + 32 * kNumCommWarps : 192);
   kern<<<grid, threads, smem, stream>>>(kp, tA, tB, tA2, tB2, tp);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {

@@ -120,6 +120,7 @@ class LoRAArena:
                 self.grad[v.b_offset:v.b_offset + n_b].view(n, v.N, v.R))
         self.steps = [0] * n
         self._chunks: dict[int, torch.Tensor] = {}
+        self._work_items: dict[tuple, torch.Tensor] = {}
         self._init_weights(init_b_std, seed)
 
     # ------------------------------------------------------------------ layout helpers
@@ -229,6 +230,19 @@ class LoRAArena:
             self._chunks[adapter] = t
         return t
 
+    def work_items(self, adapter: int, rank: int = 0, world: int = 1) -> torch.Tensor:
+        """Device table of equal-sized pieces of ``adapter``'s regions for the optimizer
+        kernels (``ops.elementwise.build_adam_work_items``); slice ``rank`` of ``world`` for the
+        fused data-parallel kernel."""
+        from ..ops.elementwise import build_adam_work_items
+
+        key = (adapter, rank, world)
+        t = self._work_items.get(key)
+        if t is None:
+            t = build_adam_work_items(self._chunk_rows[adapter], rank=rank, world=world).to(self.device)
+            self._work_items[key] = t
+        return t
+
     def trainable_numel(self, adapter: int) -> int:
         tot = 0
         for v in self.views.values():
@@ -246,7 +260,7 @@ class LoRAArena:
         self.steps[adapter] += 1
         adam_chunks(self.chunk_table(adapter), self.grad, self.master, self.m, self.v, self.work,
                     lr=lr, beta1=beta1, beta2=beta2, eps=eps, weight_decay=weight_decay,
-                    step=self.steps[adapter], grad_scale=grad_scale)
+                    step=self.steps[adapter], grad_scale=grad_scale, items=self.work_items(adapter))
 
     def zero_grad(self) -> None:
         self.grad.zero_()

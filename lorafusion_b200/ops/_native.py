@@ -115,7 +115,7 @@ _SIGNATURES = {
     "lf_embedding": [_VP, _VP, _VP, _LL, _I, _I, _VP],
     "lf_add": [_VP, _VP, _VP, _LL, _VP],
     "lf_cross_entropy": [_VP, _VP, _VP, _LL, _I, _LL, _F, _VP],
-    "lf_adam_chunks": [_VP, _I, _VP, _VP, _VP, _VP, _VP, _F, _F, _F, _F, _F, _I, _F, _VP],
+    "lf_adam_chunks": [_VP, _VP, _I, _VP, _VP, _VP, _VP, _VP, _F, _F, _F, _F, _F, _I, _F, _VP],
     "lf_nf4_quantize": [_VP, _VP, _VP, _LL, _VP],
     "lf_nf4_dequantize": [_VP, _VP, _VP, _VP, _VP, _F, _VP, _LL, _VP],
     "lf_attn_fwd": [_VP, _LL, _LL, _I, _I, _I, _I, _I, _VP, _I, _VP, _LL, _VP, _F, _VP, _VP],

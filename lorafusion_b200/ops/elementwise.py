@@ -91,14 +91,45 @@ def cross_entropy_inplace(logits: torch.Tensor, labels: torch.Tensor, grad_scale
     return loss_out
 
 
+ADAM_WORK_UNIT = 32768  # elements per CTA (a multiple of 4)
+
+
+def build_adam_work_items(chunk_rows, *, rank: int = 0, world: int = 1, unit: int = ADAM_WORK_UNIT) -> torch.Tensor:
+    """Cut every region of a chunk table (rows ``offset, rows, ld, col0, cols, state``) into
+    pieces of at most ``unit`` elements: int32 ``[n, 3]`` rows ``(chunk index, first element,
+    element count)`` on the CPU.  With ``world > 1`` only slice ``rank`` of every region is
+    covered (slices are whole 4-element groups, the split the fused data-parallel kernel
+    uses).  Regions differ in size by two orders of magnitude; equal pieces keep the CTAs of the
+    optimizer kernels balanced."""
+    items = []
+    for ci, row in enumerate(chunk_rows):
+        total = int(row[1]) * int(row[2])
+        vec = all(int(v) % 4 == 0 for v in (row[0], row[2], row[3], row[4], row[5]))
+        if world > 1:
+            if not vec:
+                raise ValueError("data-parallel slicing needs regions made of whole 4-element groups")
+            total4 = total // 4
+            per = (total4 + world - 1) // world
+            lo, hi = 4 * min(total4, per * rank), 4 * min(total4, per * (rank + 1))
+        else:
+            lo, hi = 0, total
+        step = unit if vec else max(1, unit // 4)
+        for first in range(lo, hi, step):
+            items.append((ci, first, min(step, hi - first)))
+    return torch.tensor(items, dtype=torch.int32).view(-1, 3)
+
+
 def adam_chunks(chunks: torch.Tensor, grad: torch.Tensor, master: torch.Tensor, m: torch.Tensor,
                 v: torch.Tensor, work: torch.Tensor, *, lr: float, beta1: float, beta2: float,
-                eps: float, weight_decay: float, step: int, grad_scale: float = 1.0) -> None:
+                eps: float, weight_decay: float, step: int, grad_scale: float = 1.0,
+                items: Optional[torch.Tensor] = None) -> None:
     """AdamW over the regions listed in ``chunks`` (int64 ``[n, 6]``: offset, rows, ld, col0,
     cols, state).  ``grad`` and ``work`` are addressed by ``offset`` (padded layout), ``master`` /
     ``m`` / ``v`` by ``state`` (dense over the trainable window); consumes and clears the gradient."""
     if chunks.dim() != 2 or chunks.shape[1] != 6:
         raise ValueError("chunk table must be int64 [n, 6]")
-    nv.call("lf_adam_chunks", chunks.data_ptr(), chunks.shape[0], grad.data_ptr(),
+    if items is None:  # callers on a hot path pass a cached table (this reads the chunks back)
+        items = build_adam_work_items(chunks.cpu().tolist()).to(chunks.device)
+    nv.call("lf_adam_chunks", chunks.data_ptr(), items.data_ptr(), items.shape[0], grad.data_ptr(),
             master.data_ptr(), m.data_ptr(), v.data_ptr(), work.data_ptr(), lr, beta1, beta2, eps,
             weight_decay, step, grad_scale, nv.current_stream_ptr())

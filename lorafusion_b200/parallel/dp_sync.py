@@ -24,6 +24,8 @@ from .symmetric import SymmetricAllocator, SymmetricBuffer, allocate_symmetric, 
 class LfArAdamArgs(C.Structure):
     _fields_ = [
         ("chunks", C.c_void_p),
+        ("items", C.c_void_p),
+        ("num_items", C.c_int64),
         ("grad", C.c_void_p * 8),
         ("work", C.c_void_p * 8),
         ("grad_mc", C.c_void_p),
@@ -42,7 +44,7 @@ class LfArAdamArgs(C.Structure):
     ]
 
 
-def launch_allreduce_adam(*, chunks: torch.Tensor, grad_ptrs, work_ptrs, grad_mc: int, work_mc: int,
+def launch_allreduce_adam(*, chunks: torch.Tensor, items: Optional[torch.Tensor] = None, grad_ptrs, work_ptrs, grad_mc: int, work_mc: int,
                           master: torch.Tensor, m: torch.Tensor, v: torch.Tensor, flag_ptrs,
                           done_counter: Optional[torch.Tensor], rank: int, world: int, epoch: int,
                           sync: bool, use_multimem: bool, step: int, lr: float, beta1: float, beta2: float,
@@ -52,8 +54,13 @@ def launch_allreduce_adam(*, chunks: torch.Tensor, grad_ptrs, work_ptrs, grad_mc
         lib.lf_allreduce_adam.argtypes = [C.POINTER(LfArAdamArgs)]
         lib.lf_allreduce_adam.restype = C.c_int
         lib._lf_ar_declared = True
+    if items is None:  # tests; the trainer passes the arena's cached table
+        from ..ops.elementwise import build_adam_work_items
+
+        items = build_adam_work_items(chunks.cpu().tolist(), rank=rank, world=world).to(chunks.device)
     a = LfArAdamArgs()
     a.chunks = chunks.data_ptr()
+    a.items, a.num_items = items.data_ptr(), items.shape[0]
     for r in range(world):
         a.grad[r] = grad_ptrs[r]
         a.work[r] = work_ptrs[r]
@@ -100,7 +107,8 @@ class FusedGradSync:
         ar.steps[adapter] += 1
         self.epoch += 1
         launch_allreduce_adam(
-            chunks=ar.chunk_table(adapter), grad_ptrs=self.grad_h.peer_ptrs, work_ptrs=self.work_h.peer_ptrs,
+            chunks=ar.chunk_table(adapter), items=ar.work_items(adapter, self.rank, self.world),
+            grad_ptrs=self.grad_h.peer_ptrs, work_ptrs=self.work_h.peer_ptrs,
             grad_mc=self.grad_h.multicast_ptr, work_mc=self.work_h.multicast_ptr, master=ar.master, m=ar.m,
             v=ar.v, flag_ptrs=self.flags_h.peer_ptrs, done_counter=self.done, rank=self.rank, world=self.world,
             epoch=self.epoch, sync=self.world > 1, use_multimem=self.use_multimem, step=ar.steps[adapter],

@@ -12,8 +12,9 @@ of the 32B / 70B models.  Activations between them are sequence-parallel: every 
 * ``gather`` ``[T, K_max]``  -- destination of the all-gathered A operand (a rank writes its
   own shard in place, peers push theirs during the consuming kernel), ``gather2`` for the
   LoRA ``S'`` / ``dS`` operand, ``ag_flags`` one flag per (source rank, row tile);
-* ``rs_stage`` ``[tp, T / tp, N_max]`` -- where peers deposit partial output tiles for the rows
-  this rank owns, ``rs_cnt`` one epoch flag per (source rank, row tile, column tile).
+* ``rs_stage`` ``[T, N_max]`` -- where this rank keeps its partial output tiles of ALL rows; the
+  owner of a row pulls it from every rank's stage.  ``rs_cnt`` one epoch flag per (source rank,
+  row tile, column tile), raised in the owner's memory when the partial tile is complete.
 
 Flags carry a per-context epoch that grows with every call, so microbatches of different
 sizes can reuse the same flag words.
