@@ -550,21 +550,43 @@ __global__ void __launch_bounds__((MASK_A || NF4B) ? (192 + 32 * kNumMaskWarps)
   } else if (TP == 1 && !MASK_A) {
     // ------------- push this rank's token shard to every peer's gathered buffer -------------
     const int ct = threadIdx.x - 192;  // 0..127
-    const int ms = tp.tiles_per_shard * BM;
-    for (int lt = blockIdx.x; lt < tp.tiles_per_shard; lt += gridDim.x) {
-      const long long row0 = (long long)tp.rank * ms + lt * BM;
+    const int tps = tp.tiles_per_shard;
+    const int ms = tps * BM;
+    // A row tile is pushed by up to eight CTAs (row slices), so that every SM's copy warps take
+    // part even when the shard has fewer row tiles than the grid has CTAs.  The slices of a
+    // tile count themselves in this rank's own (otherwise unused) entry of its flag array as
+    // (epoch << 4 | arrivals); whoever completes the count raises the tile's flag at the peers.
+    int parts = 1;
+    while (parts < 8 && parts * 2 * tps <= int(gridDim.x)) parts *= 2;
+    const int rows_per = BM / parts;
+    int* my_cnt = const_cast<int*>(tp.ag_flags) + tp.rank * tps;
+    for (int u = blockIdx.x; u < tps * parts; u += gridDim.x) {
+      const int lt = u / parts, part = u - lt * parts;
+      const long long row0 = (long long)tp.rank * ms + lt * BM + part * rows_per;
       const int vec_per_row = tp.ag_cols / 8;
-      for (int v = ct; v < BM * vec_per_row; v += 32 * kNumCommWarps) {
-        const long long off = (row0 + v / vec_per_row) * tp.ag_ld + (v % vec_per_row) * 8;
-        const uint4 val = *reinterpret_cast<const uint4*>(tp.ag_src + off);
-        for (int d = 1; d < tp.world; ++d) {
-          const int q = (tp.rank + d) % tp.world;
-          *reinterpret_cast<uint4*>(tp.ag_peer_dst[q] + off) = val;
+      const int nvec = rows_per * vec_per_row;
+      for (int v0 = ct; v0 < nvec; v0 += 4 * 32 * kNumCommWarps) {
+        uint4 val[4];
+        long long off[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {  // four local loads in flight before the first peer store
+          const int v = v0 + i * 32 * kNumCommWarps;
+          off[i] = (row0 + v / vec_per_row) * tp.ag_ld + (v % vec_per_row) * 8;
+          if (v < nvec) val[i] = *reinterpret_cast<const uint4*>(tp.ag_src + off[i]);
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          if (v0 + i * 32 * kNumCommWarps < nvec) {
+            for (int d = 1; d < tp.world; ++d) {
+              const int q = (tp.rank + d) % tp.world;
+              *reinterpret_cast<uint4*>(tp.ag_peer_dst[q] + off[i]) = val[i];
+            }
+          }
         }
       }
       if (tp.ag2_src != nullptr) {
         const int vec2 = tp.ag2_cols / 8;
-        for (int v = ct; v < BM * vec2; v += 32 * kNumCommWarps) {
+        for (int v = ct; v < rows_per * vec2; v += 32 * kNumCommWarps) {
           const long long off = (row0 + v / vec2) * tp.ag2_ld + (v % vec2) * 8;
           const uint4 val = *reinterpret_cast<const uint4*>(tp.ag2_src + off);
           for (int d = 1; d < tp.world; ++d) {
@@ -575,8 +597,27 @@ __global__ void __launch_bounds__((MASK_A || NF4B) ? (192 + 32 * kNumMaskWarps)
       }
       __threadfence_system();
       asm volatile("bar.sync 2, 128;" ::: "memory");
-      if (ct < tp.world && ct != tp.rank) {
-        st_release_sys(tp.ag_peer_flags[ct] + tp.rank * tp.tiles_per_shard + lt, tp.epoch);
+      if (ct == 0) {
+        bool last = true;
+        if (parts > 1) {
+          int seen = *reinterpret_cast<volatile int*>(my_cnt + lt);
+          for (;;) {
+            const int want = ((seen >> 4) == tp.epoch) ? seen + 1 : ((tp.epoch << 4) | 1);
+            const int prev = atomicCAS(my_cnt + lt, seen, want);
+            if (prev == seen) {
+              last = (want & 15) == parts;
+              break;
+            }
+            seen = prev;
+          }
+        }
+        if (last) {
+          __threadfence_system();
+          for (int d = 1; d < tp.world; ++d) {
+            const int q = (tp.rank + d) % tp.world;
+            st_release_sys(tp.ag_peer_flags[q] + tp.rank * tps + lt, tp.epoch);
+          }
+        }
       }
     }
   } else if (NF4B) {
