@@ -110,3 +110,23 @@ def test_training_state_roundtrip(tmp_path):
     # adapter 1's state was not touched
     sl1 = slice(*arena.state_range[1])
     assert not torch.equal(other.m[sl1], arena.m[sl1])
+
+
+def test_adam_work_items_cover_every_element_exactly_once():
+    from lorafusion_b200.ops.elementwise import build_adam_work_items
+
+    arena, _ = _arena()
+    for adapter in range(2):
+        rows = arena._chunk_rows[adapter]
+        for world in (1, 3):
+            seen = [torch.zeros(r[1] * r[2], dtype=torch.int32) for r in rows]
+            for rank in range(world):
+                items = build_adam_work_items(rows, rank=rank, world=world, unit=1024)
+                assert items.dtype == torch.int32 and items.shape[1] == 3
+                for ci, first, count in items.tolist():
+                    assert 0 < count <= 1024 and first % 4 == 0 and count % 4 == 0
+                    seen[ci][first:first + count] += 1
+            assert all(int(s.min()) == 1 and int(s.max()) == 1 for s in seen if s.numel())
+    # regions with odd offsets keep working on the scalar path with smaller pieces
+    odd = build_adam_work_items([(4301, 10, 30, 3, 10, 2600)], unit=1024).tolist()
+    assert sum(c for _, _, c in odd) == 300 and all(c <= 256 for _, _, c in odd)
