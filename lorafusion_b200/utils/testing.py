@@ -56,7 +56,7 @@ def assert_close_two_rounds(actual: torch.Tensor, expected_fp32: torch.Tensor, *
                             scale_atol_by_rms: bool = False, msg: str = "") -> None:
     """Compare a low-precision kernel output with an fp32 oracle.
 
-    Round 1: ``|a - e| <= atol + rtol * |e|`` everywhere.  Round 2 (only if round 1 fails):
+    Strict pass: ``|a - e| <= atol + rtol * |e|`` everywhere.  Relaxed pass (only if that fails):
     fewer than ``max_mismatch_ratio`` of the elements may be off, and they must be within
     ``rounding_factor`` times the largest rounding error that casting the oracle to the
     kernel's output dtype produces.
@@ -78,4 +78,4 @@ def assert_close_two_rounds(actual: torch.Tensor, expected_fp32: torch.Tensor, *
     ok2, text2, _ = mismatch_report(actual, expected_fp32, rtol, atol2)
     if ok2 and ratio < max_mismatch_ratio:
         return
-    raise AssertionError(f"{msg}: round 1: {text}\nround 2 (atol {atol2:.4g}): {text2}")
+    raise AssertionError(f"{msg}: strict pass: {text}\nrelaxed pass (atol {atol2:.4g}): {text2}")
