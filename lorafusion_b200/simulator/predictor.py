@@ -127,6 +127,44 @@ def synthesize_profile(cfg: ModelConfig | str, hw: Optional[HardwareSpec] = None
         head_fwd_bwd_ms=head)
 
 
+def calibrate_profile(profile: LoRALLMProfileResult, *, layer_fwd_bwd_ms: dict, head_fwd_bwd_ms: dict,
+                      fwd_share: float = 0.32) -> LoRALLMProfileResult:
+    """Rescale a synthesised profile so that it passes through measured points.
+
+    ``layer_fwd_bwd_ms`` / ``head_fwd_bwd_ms`` map a token count to a measured time.  Every grid
+    point takes the measured/synthetic ratio of the nearest measured token count (in log space);
+    the forward time is set to ``fwd_share`` of forward+backward (the share seen in kernel
+    traces of this framework: the backward holds the dX GEMMs, the LoRA gradient GEMMs and the
+    2.5x heavier attention backward)."""
+    import copy
+
+    out = copy.deepcopy(profile)
+
+    def ratios(measured: dict, synth: Sequence[float]) -> list:
+        pts = sorted(measured)
+        res = []
+        for t in out.tokens:
+            near = min(pts, key=lambda m: abs(math.log(m) - math.log(t)))
+            res.append(measured[near] / profile._interp(synth, near))
+        return res
+
+    r_layer = ratios(layer_fwd_bwd_ms, profile.layer_fwd_bwd_ms)
+    r_head = ratios(head_fwd_bwd_ms, profile.head_fwd_bwd_ms)
+    out.layer_fwd_bwd_ms = [v * r for v, r in zip(profile.layer_fwd_bwd_ms, r_layer)]
+    out.layer_fwd_ms = [v * fwd_share for v in out.layer_fwd_bwd_ms]
+    out.head_fwd_bwd_ms = [v * r for v, r in zip(profile.head_fwd_bwd_ms, r_head)]
+    return out
+
+
+CONFIG_DIR = Path(__file__).resolve().parent / "configs"
+
+
+def load_b200_profile(model: str) -> LoRALLMProfileResult:
+    """Profile of ``model`` measured on B200 with this framework (``simulator/configs/*.yaml``,
+    the counterpart of the reference's ``lorafusion/simulator/configs/*.yaml`` for H100)."""
+    return LoRALLMProfileResult.load(CONFIG_DIR / f"{model}.yaml")
+
+
 # ----------------------------------------------------------------------------------------
 # collective cost model
 # ----------------------------------------------------------------------------------------

@@ -40,3 +40,23 @@ def test_70b_memory_and_parallelism_tradeoffs():
     assert nf4.estimate(dp8).tokens_per_s > 6 * r.tokens_per_s
     best = P.best_configurations(nf4, 8, top=3)
     assert best and all(b[2].fits for b in best) and best[0][0] >= best[-1][0]
+
+
+def test_b200_profiles_reproduce_measured_throughput():
+    """The shipped B200 profiles (calibrated on measured layer times) predict the measured
+    single-GPU and pipeline runs to within 15 %."""
+    p8 = P.LoRALLMPredictor(P.load_b200_profile("llama-3.1-8b"))
+    one = P.SimulationConfiguration(microbatch_tokens=16384, microbatches_per_step=3, recompute_layers=0,
+                                    num_adapters=1)
+    assert p8.estimate(one).tokens_per_s == pytest.approx(27731, rel=0.15)      # measured: cli.train, 1 GPU
+    pp4dp2 = P.SimulationConfiguration(dp=2, pp=4, microbatch_tokens=16384, microbatches_per_step=15,
+                                       recompute_layers=0)
+    assert p8.estimate(pp4dp2).tokens_per_s == pytest.approx(144030, rel=0.15)  # measured: 8 GPUs
+    prof = P.load_b200_profile("llama-3.1-70b")
+    assert prof.layer_fwd_bwd(4096) == pytest.approx(15.30) and prof.layer_fwd_bwd(8192) == pytest.approx(29.96)
+    # calibration keeps measured points exact and scales the rest of the grid
+    synth = P.synthesize_profile("qwen2.5-32b")
+    cal = P.calibrate_profile(synth, layer_fwd_bwd_ms={4096: 9.06}, head_fwd_bwd_ms={4096: 11.26})
+    assert cal.layer_fwd_bwd(4096) == pytest.approx(9.06) and cal.head_fwd_bwd(4096) == pytest.approx(11.26)
+    assert cal.layer_fwd_bwd(8192) / cal.layer_fwd_bwd(4096) == pytest.approx(
+        synth.layer_fwd_bwd(8192) / synth.layer_fwd_bwd(4096))
