@@ -39,6 +39,11 @@ class HardwareSpec:
     p2p_latency_us: float = 6.0
     memory_gb: float = 180.0
     gemm_efficiency: float = 0.85        # fraction of bf16_tflops the fused GEMMs reach
+    # A layer split over tp ranks does not run tp times faster: the per-rank GEMMs are narrower and
+    # carry the copy / reduce warps.  FLOP-weighted roofline fractions of the fused all-gather->GEMM
+    # and GEMM->reduce-scatter kernels measured on 2 and 4 GPUs, relative to the single-GPU GEMMs;
+    # 8 is extrapolated.
+    tp_efficiency: dict = field(default_factory=lambda: {1: 1.0, 2: 0.92, 4: 0.82, 8: 0.7})
 
     @classmethod
     def from_measured_peaks(cls, path: str | Path) -> "HardwareSpec":
@@ -235,8 +240,9 @@ class LoRALLMPredictor:
         t = c.microbatch_tokens
         n_layers = self._layers_of_stage(s, c.pp)
         n_re = n_layers if c.recompute_layers is None else min(n_layers, c.recompute_layers)
-        fwd = p.layer_fwd(t) / c.tp
-        fb = p.layer_fwd_bwd(t) / c.tp
+        eff = hw.tp_efficiency.get(c.tp, min(hw.tp_efficiency.values()))
+        fwd = p.layer_fwd(t) / c.tp / eff
+        fb = p.layer_fwd_bwd(t) / c.tp / eff
         tp_comm = 0.0
         if c.tp > 1:
             act = t * p.hidden_size * 2
