@@ -55,6 +55,7 @@ def main(argv=None) -> dict:
     ap.add_argument("--out", default="schedules")
     ap.add_argument("--name", default=None)
     ap.add_argument("--compare", action="store_true", help="simulate naive / sorted / mLoRA schedules too")
+    ap.add_argument("--gantt", default=None, help="write an SVG Gantt chart of the simulated 1F1B run of the schedule")
     args = ap.parse_args(argv)
 
     data = build_data(args)
@@ -78,6 +79,17 @@ def main(argv=None) -> dict:
     if args.compare:
         report["simulation"] = ps.compare_schedules(data, args.capacity, args.num_pipeline_stages,
                                                     time_limit=min(args.time_limit, 0.5))
+    if args.gantt:
+        from ..utils.plotting import PipelineGantt
+
+        tokens = [0 if m.is_empty_marker else m.padded_total_tokens for m in S.flatten_schedule(fixed)]
+        tl = ps.evaluate_schedule_pipeline_parallelism(tokens, args.num_pipeline_stages)
+        n_st = args.num_pipeline_stages
+        fwd = [[(float(tl.f_start[m, s]), float(tl.f_end[m, s])) for m in range(len(tokens))] for s in range(n_st)]
+        bwd = [[(float(tl.b_start[m, s]), float(tl.b_end[m, s])) for m in range(len(tokens))] for s in range(n_st)]
+        PipelineGantt(fwd, bwd, title=f"{name}: bubble ratio {tl.bubble_ratio:.3f}", width=1200).save(args.gantt)
+        report["gantt"] = str(args.gantt)
+        report["simulated_bubble_ratio"] = float(tl.bubble_ratio)
     print(json.dumps(report, indent=2))
     return report
 
