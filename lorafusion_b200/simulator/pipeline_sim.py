@@ -227,3 +227,99 @@ def compare_schedules(data, capacity: int, num_stages: int, *, time_limit: float
                      "adjusted_bubble_ratio": tl.adjusted_bubble_ratio(),
                      "tokens_per_time": real / tl.total_time if tl.total_time > 0 else 0.0}
     return out
+
+
+# ----------------------------------------------------------------------------------------
+# latency-minimising order of a set of microbatches
+# ----------------------------------------------------------------------------------------
+@dataclass
+class OrderSolution:
+    order: list            # permutation of the input indices
+    total_time: float
+    bubble_ratio: float
+    method: str            # "exact" or "local-search"
+    evaluated: int         # simulated orders
+
+
+def solve_schedule_order(microbatch_tokens: Sequence[int], num_stages: int, *,
+                         time_model: Optional[Callable] = None, precedence: Sequence[tuple] = (),
+                         exact_limit: int = 8, time_limit: float = 1.0, seed: int = 0) -> OrderSolution:
+    """Order the microbatches so that the simulated 1F1B run finishes earliest.
+
+    The reference states this as a MILP over forward / backward start and end times of every
+    (stage, microbatch) pair (``benchmarks_paper/imbalance_simulator/proposed_solver.py:15-245``,
+    solved with CBC).  Here the event-driven simulator is the objective: all orders are tried
+    when there are at most ``exact_limit`` microbatches, otherwise a local search (swaps and
+    re-insertions from several sorted starting points) runs until ``time_limit`` seconds.
+    ``precedence`` holds ``(i, j)`` pairs meaning microbatch ``i`` must come before ``j``
+    (microbatches of consecutive global batches of one adapter)."""
+    import itertools
+    import random
+    import time as _time
+
+    tokens = [int(t) for t in microbatch_tokens]
+    M = len(tokens)
+    model = time_model or default_time_model()
+    fwd = np.zeros((M, num_stages))
+    bwd = np.zeros((M, num_stages))
+    for m, t in enumerate(tokens):
+        for s in range(num_stages):
+            fwd[m, s], bwd[m, s] = model(t, s, num_stages) if t > 0 else (0.0, 0.0)
+    prec = [(int(i), int(j)) for i, j in precedence]
+    count = 0
+
+    def feasible(order) -> bool:
+        if not prec:
+            return True
+        pos = {m: k for k, m in enumerate(order)}
+        return all(pos[i] < pos[j] for i, j in prec)
+
+    def cost(order) -> float:
+        nonlocal count
+        count += 1
+        idx = list(order)
+        return simulate_1f1b(fwd[idx], bwd[idx]).total_time
+
+    if M == 0:
+        return OrderSolution([], 0.0, 0.0, "exact", 0)
+    if M <= exact_limit:
+        best, best_c = None, float("inf")
+        for perm in itertools.permutations(range(M)):
+            if feasible(perm):
+                c = cost(perm)
+                if c < best_c - 1e-12:
+                    best, best_c = list(perm), c
+        if best is None:
+            raise ValueError("the precedence constraints admit no order")
+        tl = simulate_1f1b(fwd[best], bwd[best])
+        return OrderSolution(best, tl.total_time, tl.bubble_ratio, "exact", count)
+
+    # local search
+    rng = random.Random(seed)
+    asc = sorted(range(M), key=lambda m: tokens[m])
+    desc = asc[::-1]
+    # small ones first to fill the pipeline quickly, large ones in the middle, small ones to drain
+    pyramid = asc[0::2] + asc[1::2][::-1]
+    starts = [list(range(M)), desc, asc, pyramid]
+    cands = [(cost(o), o) for o in starts if feasible(o)]
+    if not cands:
+        raise ValueError("no feasible starting order; relax the precedence constraints")
+    best_c, best = min(cands, key=lambda x: x[0])
+    best = list(best)
+    deadline = _time.monotonic() + time_limit
+    while _time.monotonic() < deadline:
+        i, j = rng.randrange(M), rng.randrange(M)
+        if i == j:
+            continue
+        trial = list(best)
+        if rng.random() < 0.5:
+            trial[i], trial[j] = trial[j], trial[i]
+        else:
+            trial.insert(j, trial.pop(i))
+        if not feasible(trial):
+            continue
+        c = cost(trial)
+        if c < best_c - 1e-12:
+            best, best_c = trial, c
+    tl = simulate_1f1b(fwd[best], bwd[best])
+    return OrderSolution(best, tl.total_time, tl.bubble_ratio, "local-search", count)

@@ -175,3 +175,32 @@ def test_manager_inflight_order_and_steps():
     assert mgr.pop_oldest_batch_info() is i1
     assert mgr.maybe_reduce_grad_and_optimizer_step() == [0] and stepped[-1] == (0, 2)
     assert mgr.adapter_sample_counts == {0: 0, 1: 0} and i1.microbatch_idx == 1
+
+
+def test_latency_minimising_order_search():
+    """Exact search on small instances is a lower bound for every other order; the local search
+    on larger ones never loses to the sorted or the given order; precedence pairs are kept."""
+    import itertools
+    import random
+
+    from lorafusion_b200.simulator.pipeline_sim import (evaluate_schedule_pipeline_parallelism,
+                                                        solve_schedule_order)
+
+    rng = random.Random(3)
+    toks = [rng.choice([1024, 2048, 4096, 8192, 12000]) for _ in range(6)]
+    sol = solve_schedule_order(toks, 3)
+    assert sol.method == "exact" and sorted(sol.order) == list(range(6))
+    brute = min(evaluate_schedule_pipeline_parallelism([toks[i] for i in p], 3).total_time
+                for p in itertools.permutations(range(6)))
+    assert sol.total_time == pytest.approx(brute)
+    # precedence: 5 before 0 and 0 before 3
+    solp = solve_schedule_order(toks, 3, precedence=[(5, 0), (0, 3)])
+    assert solp.order.index(5) < solp.order.index(0) < solp.order.index(3)
+    assert solp.total_time >= sol.total_time - 1e-9
+    big = [rng.choice([1024, 2048, 4096, 8192, 16384]) for _ in range(30)]
+    solb = solve_schedule_order(big, 4, time_limit=0.3)
+    assert solb.method == "local-search" and sorted(solb.order) == list(range(30))
+    for ref in (big, sorted(big), sorted(big, reverse=True)):
+        assert solb.total_time <= evaluate_schedule_pipeline_parallelism(ref, 4).total_time + 1e-9
+    with pytest.raises(ValueError):
+        solve_schedule_order(toks, 3, precedence=[(0, 1), (1, 0)])
