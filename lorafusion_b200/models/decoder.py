@@ -371,8 +371,13 @@ class DecoderStage:
         self._modes_plan = None
 
     def disable_offload(self) -> None:
+        """Drop the offloader and give its pinned host buffers back to the operating system
+        (the pinned-memory allocator would otherwise keep them cached)."""
         self._offloader = None
         self.set_offload(False)
+        release = getattr(torch._C, "_host_emptyCache", None)
+        if release is not None:
+            release()
 
     def _get_offloader(self, tokens: int):
         from .offload import ActivationOffloader
