@@ -377,7 +377,10 @@ class DecoderStage:
         self.set_offload(False)
         release = getattr(torch._C, "_host_emptyCache", None)
         if release is not None:
-            release()
+            try:
+                release()
+            except RuntimeError:
+                pass  # only an optimisation: the buffers stay cached
 
     def _get_offloader(self, tokens: int):
         from .offload import ActivationOffloader
