@@ -159,3 +159,38 @@ def test_global_batches_of_an_adapter_never_interleave():
                     counts.setdefault(a, []).append(g)
             for a, gs in counts.items():
                 assert gs == sorted(gs), (seed, stages, a)
+
+
+def test_random_instances_always_yield_valid_schedules():
+    """Property test over random job mixes: whatever the number of adapters, global batch sizes,
+    lengths, capacity and pipeline depth, the pipeline group -> pack -> merge -> verify (+ no-op
+    insertion) ends in a schedule that covers every sample once, respects the capacity and the
+    bubble lemma, and never interleaves global batches of one adapter."""
+    from hypothesis import HealthCheck, given, settings
+    from hypothesis import strategies as st
+
+    @settings(max_examples=30, deadline=None, suppress_health_check=[HealthCheck.too_slow])
+    @given(st.integers(1, 5), st.integers(1, 3), st.integers(1, 4), st.integers(0, 10 ** 6),
+           st.sampled_from([2048, 4096, 8192]))
+    def check(num_adapters, batches, stages, seed, capacity):
+        rng = random.Random(seed)
+        data = []
+        for a in range(num_adapters):
+            gbs = rng.randint(1, 6)
+            data.append([[rng.randint(16, capacity - 128) for _ in range(gbs)] for _ in range(batches)])
+        groups = S.group_adapters(data, capacity, num_stages=stages)
+        assert sorted(a for g in groups for a in g) == list(range(num_adapters))
+        packed = S.packing_data_to_microbatches_micro_milp(data, groups, capacity, stages, use_exact=False,
+                                                           num_workers=1)
+        merged = S.apply_merge_pass_for_adapter_group_step_infos(packed, stages)
+        ok, msgs, fixed = S.verify_correctness_of_schedule(data, merged, stages, add_bubble=True)
+        assert ok, msgs
+        ok2, msgs2 = S.verify_correctness_of_schedule(data, fixed, stages)[:2]
+        assert ok2, msgs2
+        flat = S.flatten_schedule(fixed)
+        assert S.bubble_lemma_violations(flat, stages) == []
+        assert all(m.padded_total_tokens <= capacity for m in flat)
+        total = sum(ln for a in data for b in a for ln in b)
+        assert sum(m.total_tokens for m in flat) == total
+
+    check()
