@@ -63,7 +63,9 @@ int lf_gemm(const LfGemmArgs* args);
 //   mode 1 (all-gather -> GEMM): `ag_src` is this rank's gathered A buffer [M, ag_cols]
 //     (own shard already in place); the kernel pushes the own shard to `ag_peer_dst[q]` and
 //     signals `ag_peer_flags[q][rank * tiles_per_shard + tile] = epoch`; it waits on its own
-//     `ag_flags`.  `ag2_*` optionally gathers the LoRA slab operand the same way.
+//     `ag_flags`.  `ag2_*` optionally gathers the LoRA slab operand the same way.  `rs_target`
+//     (> 0) is the offset in ints, inside the `ag_flags` buffer, of tiles_per_shard local
+//     arrival counters that let several CTAs share the push of one row tile; 0 = one CTA per tile.
 //   mode 2 (GEMM -> reduce-scatter): partial tiles go to this rank's own `rs_peer_stage[rank]`
 //     ([M, N] bf16; the owner of a row reads it from every source's stage), the flag
 //     `rs_peer_cnt[owner][(rank * tiles_per_shard + tile) * num_n_tiles + n_tile]` is set to

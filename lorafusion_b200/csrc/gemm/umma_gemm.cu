@@ -554,12 +554,15 @@ __global__ void __launch_bounds__((MASK_A || NF4B) ? (192 + 32 * kNumMaskWarps)
     const int ms = tps * BM;
     // A row tile is pushed by up to eight CTAs (row slices), so that every SM's copy warps take
     // part even when the shard has fewer row tiles than the grid has CTAs.  The slices of a
-    // tile count themselves in this rank's own (otherwise unused) entry of its flag array as
-    // (epoch << 4 | arrivals); whoever completes the count raises the tile's flag at the peers.
+    // tile count themselves as (epoch << 4 | arrivals) in a counter region that follows the
+    // flags in the same local buffer (`rs_target` = its offset in ints in this mode; the
+    // counters must never share words with flags: a stale count would read as a huge epoch);
+    // whoever completes the count raises the tile's flag at the peers.
     int parts = 1;
-    while (parts < 8 && parts * 2 * tps <= int(gridDim.x)) parts *= 2;
+    if (tp.rs_target > 0)
+      while (parts < 8 && parts * 2 * tps <= int(gridDim.x)) parts *= 2;
     const int rows_per = BM / parts;
-    int* my_cnt = const_cast<int*>(tp.ag_flags) + tp.rank * tps;
+    int* my_cnt = const_cast<int*>(tp.ag_flags) + tp.rs_target;
     for (int u = blockIdx.x; u < tps * parts; u += gridDim.x) {
       const int lt = u / parts, part = u - lt * parts;
       const long long row0 = (long long)tp.rank * ms + lt * BM + part * rows_per;

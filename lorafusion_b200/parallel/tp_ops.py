@@ -76,7 +76,9 @@ class TpContext:
         self.gather2: SymmetricBuffer = alloc(max_tokens * max_rank_width, torch.bfloat16)
         self.rs_stage: SymmetricBuffer = alloc(max_tokens * max_features, torch.bfloat16)
         n_flags = self.world * (max_tokens // TILE)
-        self.ag_flags: SymmetricBuffer = alloc(n_flags, torch.int32)
+        # flags [n_flags] followed by this rank's slice-arrival counters [max_tokens / 128]
+        self.n_flags = n_flags
+        self.ag_flags: SymmetricBuffer = alloc(n_flags + max_tokens // TILE, torch.int32)
         # one flag per (source rank, row tile, 256-column tile) of a reduce-scatter
         self.rs_cnt: SymmetricBuffer = alloc(n_flags * ((max_features + 255) // 256), torch.int32)
         self.ag_flags.tensor.zero_()
@@ -157,6 +159,7 @@ def ag_gemm(ctx: TpContext, tokens: int, k: int, w: torch.Tensor, *, w_mn: bool 
     tp = ctx._base_args(tokens)
     tp.mode, tp.epoch = 1, ctx.epoch
     tp.ag_flags = ctx.ag_flags.tensor.data_ptr()
+    tp.rs_target = ctx.n_flags  # offset (ints) of the arrival counters behind the flags
     tp.ag_src, tp.ag_ld, tp.ag_cols = a.data_ptr(), k, k
     for r in range(ctx.world):
         tp.ag_peer_flags[r] = ctx.ag_flags.peer_ptrs[r]

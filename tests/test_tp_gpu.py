@@ -24,14 +24,16 @@ from lorafusion_b200.ops import _native
 from lorafusion_b200.utils.testing import assert_close_two_rounds
 torch.backends.cuda.matmul.allow_tf32 = False
 
-T, K, N, R = 1024, 768, 1280, 64
-ctx = TpContext(dist.group.WORLD, dev, max_tokens=T, max_features=2048)
-ms = T // world
+T_MAX, K, N, R = 1024, 768, 1280, 64
+ctx = TpContext(dist.group.WORLD, dev, max_tokens=T_MAX, max_features=2048)
 def rnd(*shape, scale=1.0, seed=0):
     g = torch.Generator(device=dev).manual_seed(seed)
     return (torch.randn(*shape, generator=g, device=dev) * scale).to(torch.bfloat16)
 
-for it in range(3):
+# microbatches of different sizes reuse the same flag and counter words: the tile indexing
+# changes with the token count, only the epochs keep calls apart
+for it, T in enumerate([1024, 512, 1024]):
+    ms = T // world
     # ---------------- all-gather -> GEMM (+ LoRA slab), NT and NN weight layouts ----------------
     x_shard = rnd(ms, K, seed=10 * it + rank)
     s_shard = rnd(ms, R, scale=0.1, seed=100 + 10 * it + rank)
