@@ -85,3 +85,50 @@ def test_rank_that_dies_between_steps_is_noticed_by_heartbeat_timeout(tmp_path):
     for p in procs:
         p.join(timeout=30)
     assert rank == 0 and msg.startswith("detected [1]"), msg
+
+
+_STORE_CHILD = r"""
+import time, torch.distributed as dist
+from lorafusion_b200.parallel.health import HealthMonitor, PeerFailure
+dist.init_process_group("gloo")
+rank, world = dist.get_rank(), dist.get_world_size()
+h = HealthMonitor(dist.distributed_c10d._get_default_store(), rank, world, interval=0.1, timeout=2.0).start()
+time.sleep(0.4)
+h.check()
+dist.barrier()
+if rank == 1:
+    h.report_failure("boom")
+dist.barrier()
+if rank == 0:
+    try:
+        h.check()
+        raise SystemExit("rank 0 did not see the failure note")
+    except PeerFailure as e:
+        assert e.ranks == [1] and "boom" in str(e)
+dist.barrier()
+h.stop()
+dist.destroy_process_group()
+print("ok", rank)
+"""
+
+
+def test_health_monitor_on_the_rendezvous_store_of_a_process_group(tmp_path):
+    """Same checks through the store ``init_process_group`` creates (what ``cli.train`` uses)."""
+    import socket
+    import subprocess
+    import sys
+
+    script = tmp_path / "child.py"
+    script.write_text(_STORE_CHILD)
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    procs = []
+    for r in range(2):
+        env = dict(os.environ, RANK=str(r), WORLD_SIZE="2", MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port),
+                   PYTHONPATH=os.pathsep.join([os.getcwd(), os.environ.get("PYTHONPATH", "")]))
+        procs.append(subprocess.Popen([sys.executable, str(script)], env=env, stdout=subprocess.PIPE,
+                                      stderr=subprocess.STDOUT, text=True))
+    outs = [p.communicate(timeout=120)[0] for p in procs]
+    for r, (p, o) in enumerate(zip(procs, outs)):
+        assert p.returncode == 0, f"rank {r} failed:\n{o[-2000:]}"
