@@ -87,7 +87,7 @@ def _run(margs, targs, dargs, rank, world, device, health) -> dict:
     optim = OptimizerConfig(targs.learning_rate, targs.adam_beta1, targs.adam_beta2, targs.adam_epsilon,
                             targs.weight_decay)
     t0 = time.time()
-    trainer = ParallelTrainer(cfg, adapters, [g * dp for g in gbs_local], device, engine, optim)
+    trainer = ParallelTrainer(cfg, adapters, [g * dp for g in gbs_local], device, engine, optim, health=health)
     log_rank0(f"model {cfg.name} ({engine.layout}) built in {time.time() - t0:.1f}s; "
               f"{torch.cuda.memory_allocated() / 2**30:.1f} GiB allocated")
 

@@ -6,9 +6,14 @@ error status (``ops/_native.check_device_errors``), but a rank that is already g
 noticed BEFORE the next launch rather than by a 10-second device timeout.  Each rank therefore
 
 * publishes a heartbeat counter from a background thread (``hb/<rank>``),
+* publishes its progress from the training loop itself (``prog/<rank>``, one tick per pipeline
+  slot or step -- a main thread stuck in a collective keeps its heartbeat thread alive, so
+  liveness alone cannot show a stall),
 * publishes a note when its step raised (``failed/<rank>`` = message), and
-* calls :meth:`HealthMonitor.check` between steps, which raises :class:`PeerFailure` if a peer
-  left a failure note or its heartbeat has not advanced for ``timeout`` seconds.
+* calls :meth:`HealthMonitor.check` between steps AND between the microbatch slots of a
+  schedule (``PipelineRuntime``), which raises :class:`PeerFailure` if a peer left a failure
+  note, its heartbeat has not advanced for ``timeout`` seconds, or (with
+  ``progress_timeout``) its progress counter has stood still for that long.
 
 A rank only ever leaves between steps, with none of its kernels or collectives in flight.  The
 reference has no failure handling (an out-of-memory run is found by grepping the log,
@@ -32,11 +37,15 @@ class PeerFailure(RuntimeError):
 
 class HealthMonitor:
     def __init__(self, store, rank: int, world: int, *, interval: float = 0.5, timeout: float = 5.0,
-                 prefix: str = "lf_health", clock: Callable[[], float] = time.monotonic):
+                 prefix: str = "lf_health", clock: Callable[[], float] = time.monotonic,
+                 progress_timeout: Optional[float] = None):
         self.store, self.rank, self.world = store, rank, world
         self.interval, self.timeout, self.prefix = interval, timeout, prefix
+        self.progress_timeout = progress_timeout
         self.clock = clock
         self._beat = 0
+        self._progress = 0
+        self._last_progress: dict[int, tuple[int, float]] = {}
         self._stop = threading.Event()
         self._thread: Optional[threading.Thread] = None
         self._last_seen: dict[int, tuple[int, float]] = {}
@@ -49,6 +58,11 @@ class HealthMonitor:
     def beat(self) -> None:
         self._beat += 1
         self.store.set(self._key("hb", self.rank), str(self._beat))
+
+    def progress(self) -> None:
+        """Called from the training loop: publish that this rank's main thread moved on."""
+        self._progress += 1
+        self.store.set(self._key("prog", self.rank), str(self._progress))
 
     def start(self) -> "HealthMonitor":
         self.beat()
@@ -110,6 +124,15 @@ class HealthMonitor:
                 self._last_seen[r] = (count, now)
             elif now - seen[1] > self.timeout:
                 bad[r] = f"no heartbeat for {now - seen[1]:.1f}s"
+                continue
+            if self.progress_timeout is not None:
+                pg = self._get(self._key("prog", r))
+                if pg is not None:
+                    seen = self._last_progress.get(r)
+                    if seen is None or seen[0] != int(pg):
+                        self._last_progress[r] = (int(pg), now)
+                    elif now - seen[1] > self.progress_timeout:
+                        bad[r] = f"alive but no progress for {now - seen[1]:.1f}s"
         return bad
 
     def check(self) -> None:

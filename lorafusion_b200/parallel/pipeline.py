@@ -4,10 +4,18 @@ Replaces the reference's copies of Megatron's schedules
 (``lorafusion/pipeline_parallel/multi_lora_schedule.py:130-726``) and Megatron's p2p layer:
 
 * **No shape handshake and no empty-batch marker tensors.**  The microbatch schedule is
-  produced offline, so every stage knows each microbatch's padded token count in advance;
-  receive buffers are allocated directly and empty (no-op) microbatches -- inserted by the
-  solver to satisfy the bubble lemma -- are skipped by all stages without communication (the
-  reference sends a ``(1, 1, 7)`` marker tensor, ``multi_lora_schedule.py:36,575-579``).
+  produced offline, so every stage knows each microbatch's padded token count in advance and
+  receive buffers are allocated directly.  Empty (no-op) microbatches -- inserted by the
+  solver to satisfy the bubble lemma -- keep their SLOT in the 1F1B order on every stage: a
+  no-op forward and a no-op backward advance the schedule position exactly like a real
+  microbatch, but compute nothing and send nothing (the reference sends a ``(1, 1, 7)``
+  marker tensor through the pipeline, ``multi_lora_schedule.py:36,560-592``).  Dropping the
+  slots instead would pull the first microbatch of an adapter's next global batch forward,
+  ahead of the optimizer step of the previous one.
+* **The bubble lemma is asserted at run time**: before executing, :meth:`PipelineRuntime.run`
+  checks that every microbatch of global batch ``g + 1`` of an adapter sits at least
+  ``pp`` slots after the last microbatch of its batch ``g``, and raises
+  :class:`BubbleLemmaError` otherwise (``lorafusion/solver/proposed_solver.py:617-635``).
 * **Overlapped p2p.**  Forward activations and backward gradients travel on two separate
   process groups (independent communicators and streams), receives for the next microbatch
   are posted before the current one is computed, and sends are waited on lazily.
@@ -59,11 +67,46 @@ EMPTY_BATCH_MAGIC_TOKEN = 7
 @dataclass
 class PipelineMicrobatch:
     """What one stage needs to know about a microbatch: its device batch (``None`` for an
-    empty no-op) and the padded token count that fixes the activation shape."""
+    empty no-op) and the padded token count that fixes the activation shape.
+    ``adapter_batches`` maps adapter -> global batch index for the lemma check; when it is
+    ``None`` it is read from ``batch.info.micro_batch_info.data_samples`` if that exists."""
 
     batch: Any
     num_tokens: int
     is_empty: bool = False
+    adapter_batches: Optional[dict] = None
+
+    def lemma_samples(self) -> dict:
+        """``{(adapter, global batch, 0): 1}`` in the form the solver's lemma check reads."""
+        if self.is_empty:
+            return {}
+        if self.adapter_batches is not None:
+            return {(a, g, 0): 1 for a, g in self.adapter_batches.items()}
+        info = getattr(self.batch, "info", None)
+        mbi = getattr(info, "micro_batch_info", None)
+        return dict(getattr(mbi, "data_samples", None) or {})
+
+
+class BubbleLemmaError(RuntimeError):
+    """The microbatch order would let a global batch enter the pipeline before the optimizer
+    step of the adapter's previous global batch has been taken on every stage."""
+
+
+def check_bubble_lemma(microbatches: Sequence["PipelineMicrobatch"], num_pipeline_stages: int) -> None:
+    """Raise :class:`BubbleLemmaError` if the order (no-op slots included) violates the lemma."""
+    if num_pipeline_stages <= 1:
+        return
+    from types import SimpleNamespace
+
+    from ..solver.schedule import bubble_lemma_violations
+
+    flat = [SimpleNamespace(data_samples=m.lemma_samples()) for m in microbatches]
+    bad = bubble_lemma_violations(flat, num_pipeline_stages)
+    if bad:
+        raise BubbleLemmaError(
+            f"bubble lemma violated at microbatch slots {bad[:8]} for {num_pipeline_stages} pipeline stages: "
+            "a global batch would start before the previous optimizer step of its adapter; insert no-op "
+            "microbatches (verify_correctness_of_schedule(add_bubble=True))")
 
 
 @dataclass
@@ -131,11 +174,19 @@ class _P2P:
 
 class PipelineRuntime:
     def __init__(self, stage, state: ParallelState, *, hidden_size: int, dtype=torch.bfloat16, device="cuda",
-                 manager=None, fwd_group=None, bwd_group=None, use_timers: bool = False):
+                 manager=None, fwd_group=None, bwd_group=None, use_timers: bool = False,
+                 health=None, health_every: int = 1):
+        """``health`` (a :class:`~lorafusion_b200.parallel.health.HealthMonitor`) is consulted
+        on the host before every ``health_every``-th forward or backward slot, so that a peer
+        that raised or left is noticed before the next launch instead of by a device-side
+        wait running out; each consulted slot also publishes this rank's progress."""
         self.stage, self.state, self.manager = stage, state, manager
         self.device = torch.device(device)
         self.p2p = _P2P(state, fwd_group, bwd_group, hidden_size, dtype, self.device)
         self.use_timers = use_timers
+        self.health, self.health_every = health, max(1, int(health_every))
+        self._slot_counter = 0
+        self.executed_ops: list = []  # ("F" | "B", slot index, is_empty) of the last run
 
     # ------------------------------------------------------------------ timing helper
     def _tick(self) -> float:
@@ -175,37 +226,74 @@ class PipelineRuntime:
             stats.stepped += self.manager.maybe_reduce_grad_and_optimizer_step()
 
     # ------------------------------------------------------------------ schedules
+    def _check_health(self) -> None:
+        if self.health is None:
+            return
+        self._slot_counter += 1
+        if self._slot_counter % self.health_every == 0:
+            self.health.progress()
+            self.health.check()
+
     def run(self, microbatches: Sequence[PipelineMicrobatch]) -> PipelineStats:
-        """Execute one list of microbatches with 1F1B (or plainly when there is one stage)."""
+        """Execute one list of microbatches with 1F1B (or plainly when there is one stage).
+        Empty microbatches occupy a forward and a backward slot but do no work."""
         stats = PipelineStats()
         t_start = self._tick()
-        work = [m for m in microbatches if not m.is_empty]
+        work = list(microbatches)
         pp = self.state.layout.pp
+        if self.manager is not None:  # per-adapter optimizer steps happen inside the schedule
+            check_bubble_lemma(work, pp)
         M = len(work)
         warm = min(pp - self.state.pp_rank - 1, M)
         steady = M - warm
         in_flight: list = []
-        nf = nb = 0  # next forward / backward microbatch index
+        self.executed_ops = []
 
-        recv_f = self.p2p.post_recv_forward(work[0].num_tokens) if M else None
-        for _ in range(warm):
-            entry = self._forward(work[nf], recv_f, stats)
+        def next_real(idx: int) -> Optional[int]:
+            """Index of the first non-empty microbatch at or after ``idx``."""
+            while idx < M and work[idx].is_empty:
+                idx += 1
+            return idx if idx < M else None
+
+        # One forward receive is pre-posted at any time: that of the next non-empty microbatch.
+        posted_f = next_real(0)
+        recv_f = self.p2p.post_recv_forward(work[posted_f].num_tokens) if posted_f is not None else None
+
+        def forward_slot(i: int) -> None:
+            nonlocal posted_f, recv_f
+            self._check_health()
+            self.executed_ops.append(("F", i, work[i].is_empty))
+            if work[i].is_empty:
+                in_flight.append(None)
+                return
+            assert posted_f == i
+            handle = recv_f
+            entry = self._forward(work[i], handle, stats)
             in_flight.append(entry)
-            nf += 1
-            recv_f = self.p2p.post_recv_forward(work[nf].num_tokens) if nf < M else None
-        recv_b = None
-        for i in range(steady):
-            entry = self._forward(work[nf], recv_f, stats)
-            in_flight.append(entry)
-            nf += 1
-            recv_b = self.p2p.post_recv_backward(work[nb].num_tokens)
-            recv_f = self.p2p.post_recv_forward(work[nf].num_tokens) if nf < M else None
-            self._backward(work[nb], in_flight.pop(0), recv_b, stats)
-            nb += 1
+            posted_f = next_real(i + 1)
+            recv_f = self.p2p.post_recv_forward(work[posted_f].num_tokens) if posted_f is not None else None
+
+        def backward_slot(i: int) -> None:
+            self._check_health()
+            self.executed_ops.append(("B", i, work[i].is_empty))
+            entry = in_flight.pop(0)
+            if work[i].is_empty:
+                return
+            recv_b = self.p2p.post_recv_backward(work[i].num_tokens)
+            self._backward(work[i], entry, recv_b, stats)
             self.p2p.reap()
+
+        nf = nb = 0  # next forward / backward slot
         for _ in range(warm):
-            recv_b = self.p2p.post_recv_backward(work[nb].num_tokens)
-            self._backward(work[nb], in_flight.pop(0), recv_b, stats)
+            forward_slot(nf)
+            nf += 1
+        for _ in range(steady):
+            forward_slot(nf)
+            nf += 1
+            backward_slot(nb)
+            nb += 1
+        for _ in range(warm):
+            backward_slot(nb)
             nb += 1
         self.p2p.drain()
         if self.manager is not None:

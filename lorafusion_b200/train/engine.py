@@ -37,7 +37,9 @@ class EngineConfig:
 
 class ParallelTrainer:
     def __init__(self, cfg: ModelConfig, adapters: Sequence[AdapterSpec], global_batch_sizes: Sequence[int],
-                 device, engine: EngineConfig, optim: Optional[OptimizerConfig] = None):
+                 device, engine: EngineConfig, optim: Optional[OptimizerConfig] = None, health=None):
+        """``health``: optional :class:`~lorafusion_b200.parallel.health.HealthMonitor`; the
+        pipeline runtime consults it between microbatch slots."""
         self.cfg, self.adapters, self.engine = cfg, list(adapters), engine
         self.device = torch.device(device)
         self.optim = optim or OptimizerConfig()
@@ -87,7 +89,7 @@ class ParallelTrainer:
         self.manager.register_step_fn(self._step_adapter)
         self.runtime = PipelineRuntime(self.stage, st, hidden_size=cfg.hidden_size, device=self.device,
                                        manager=self.manager, fwd_group=self.fwd_group, bwd_group=self.bwd_group,
-                                       use_timers=engine.use_timers)
+                                       use_timers=engine.use_timers, health=health)
 
     # ------------------------------------------------------------------ optimizer step of one adapter
     def _step_adapter(self, adapter: int, num_microbatches: int) -> None:
