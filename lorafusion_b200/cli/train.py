@@ -29,10 +29,10 @@ import torch
 import torch.distributed as dist
 
 from ..models.config import get_model_config
-from ..models.peft_io import load_adapter, load_training_state, save_adapter, save_training_state
 from ..ops import _native
 from ..simulator import pipeline_sim as ps
 from ..solver import schedule as S
+from ..train.checkpoint import CheckpointLayout, load_checkpoint, save_checkpoint
 from ..train.args import parse_args_into_dataclasses, parse_list
 from ..train.engine import EngineConfig, ParallelTrainer
 from ..train.provider import MockMultiLoRADataProvider
@@ -91,29 +91,33 @@ def _run(margs, targs, dargs, rank, world, device, health) -> dict:
     log_rank0(f"model {cfg.name} ({engine.layout}) built in {time.time() - t0:.1f}s; "
               f"{torch.cuda.memory_allocated() / 2**30:.1f} GiB allocated")
 
+    ckpt_layout = CheckpointLayout.from_parallel_state(trainer.state, fused_dp=trainer.grad_sync == "fused")
+    start_batches, index_offset = None, 0
+    if targs.resume_from:
+        # adapters (PEFT layout) and optimizer state written by --save_adapters of an earlier run,
+        # under any dp x pp x tp layout; the data of every adapter continues where it stopped
+        metas = load_checkpoint(trainer.stage.arena, targs.resume_from, ckpt_layout)
+        start_batches = [0] * len(adapters)
+        for i, (a, meta) in enumerate(zip(adapters, metas)):
+            if meta is not None:
+                start_batches[i] = int(meta["data_cursor"]) // gbs_global[i]
+                index_offset = max(index_offset, int(meta["extra"].get("microbatches", 0)))
+                log_rank0(f"resumed {a.name}: optimizer step {meta['step']}, data cursor {meta['data_cursor']}")
+
     names = parse_list(dargs.adapter_to_dataset, str)
     names = (names * len(adapters))[:len(adapters)]
     provider = MockMultiLoRADataProvider.from_named_distributions(
-        adapters, names, gbs_local, num_samples=max(dargs.num_samples, max(gbs_local) * (targs.max_steps + 1)),
+        adapters, names, gbs_local, num_samples=max(dargs.num_samples, max(gbs_local) * (targs.max_steps + 1 + max(start_batches or [0]))),
         seed=dargs.dataset_seed, max_len=min(dargs.max_seq_len, engine.capacity), capacity=engine.capacity,
         num_pipeline_stages=pp, vocab_size=cfg.vocab_size, schedule_path=dargs.multi_lora_dataset_schedule_path,
-        num_global_batches=targs.max_steps, dp_rank=trainer.state.dp_rank, total_multiple=128 * tp)
+        num_global_batches=targs.max_steps, dp_rank=trainer.state.dp_rank, total_multiple=128 * tp,
+        start_global_batches=start_batches, index_offset=index_offset)
     if targs.benchmark_baseline_mlora_schedule:
         sched = ps.generate_mlora_schedule(provider.data, engine.capacity)
         _, _, sched = S.verify_correctness_of_schedule(provider.data, sched, pp, add_bubble=True)
         provider.schedule, provider.flat = sched, S.flatten_schedule(sched)
     log_rank0(f"schedule: {json.dumps(provider.statistics())}")
 
-    if targs.resume_from:
-        # adapters (PEFT layout) and optimizer state written by --save_adapters of an earlier run
-        if tp != 1:
-            raise ValueError("--resume_from needs tensor_parallel_size 1 (adapters are saved unsharded)")
-        for i, a in enumerate(adapters):
-            d = Path(targs.resume_from) / f"stage{trainer.state.pp_rank}" / a.name
-            load_adapter(trainer.stage.arena, i, d)
-            if (d / "training_state.pt").exists():
-                meta = load_training_state(trainer.stage.arena, i, d / "training_state.pt")
-                log_rank0(f"resumed {a.name}: optimizer step {meta['step']}, data cursor {meta['data_cursor']}")
     mbs = trainer.prepare(provider)
     if health is not None:
         health.check()
@@ -174,12 +178,11 @@ def _run(margs, targs, dargs, rank, world, device, health) -> dict:
                 w.writeheader()
             w.writerow(result)
         print(json.dumps(result))
-    if targs.save_adapters and trainer.state.dp_rank == 0 and tp == 1:
-        for i, a in enumerate(adapters):
-            d = Path(targs.output_dir) / f"stage{trainer.state.pp_rank}" / a.name
-            save_adapter(trainer.stage.arena, i, d, base_model_name=cfg.name)
-            save_training_state(trainer.stage.arena, i, d / "training_state.pt",
-                                data_cursor=trainer.manager.steps_taken.get(i, 0) * gbs_global[i])
+    if targs.save_adapters:
+        save_checkpoint(trainer.stage.arena, targs.output_dir, ckpt_layout, base_model_name=cfg.name,
+                        data_cursors=[((start_batches or [0] * len(adapters))[i] + trainer.manager.steps_taken.get(i, 0))
+                                      * gbs_global[i] for i in range(len(adapters))],
+                        extra={"microbatches": index_offset + len(mbs)})
     if world > 1:
         dist.barrier()
         if health is not None:

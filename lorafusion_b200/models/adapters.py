@@ -282,16 +282,25 @@ class LoRAArena:
             off += v.numel()
 
     # ------------------------------------------------------------------ per-adapter tensors
-    def export_adapter(self, adapter: int) -> dict[str, torch.Tensor]:
-        """``{"layers.{l}.{sub}.lora_A": [r, K], "...lora_B": [N_sub, r]}`` (fp32 master if
-        present, else the bf16 working copy)."""
+    def _source(self, source: str) -> Optional[torch.Tensor]:
+        if source not in ("master", "m", "v", "work"):
+            raise ValueError(f"unknown adapter tensor source {source!r}")
+        return None if source == "work" else getattr(self, source)
+
+    def export_adapter(self, adapter: int, source: Optional[str] = None) -> dict[str, torch.Tensor]:
+        """``{"layers.{l}.{sub}.lora_A": [r, K], "...lora_B": [N_sub, r]}``.  ``source`` picks
+        what is read: ``"master"`` (fp32 weights), ``"m"`` / ``"v"`` (Adam moments, same shapes),
+        ``"work"`` (the bf16 copy the kernels read); default = master if present, else work."""
+        if source is None:
+            source = "master" if self.master is not None else "work"
+        dense = self._source(source)
         out = {}
         for (l, _), v in self.views.items():
             for name, n0, size, c0, r in self.sub_slices(v, adapter):
-                if self.master is not None:
+                if dense is not None:
                     sa, sb = self.state_offsets[(v.layer, v.proj, adapter, name)]
-                    a = self.master[sa:sa + r * v.K].view(r, v.K)
-                    b = self.master[sb:sb + size * r].view(size, r)
+                    a = dense[sa:sa + r * v.K].view(r, v.K)
+                    b = dense[sb:sb + size * r].view(size, r)
                 else:
                     a = v.stack.a[adapter, c0:c0 + r]
                     b = v.stack.b[adapter, n0:n0 + size, c0:c0 + r]
@@ -299,15 +308,64 @@ class LoRAArena:
                 out[f"layers.{l}.{name}.lora_B"] = b.clone()
         return out
 
-    def import_adapter(self, adapter: int, tensors: dict[str, torch.Tensor]) -> None:
+    def import_adapter(self, adapter: int, tensors: dict[str, torch.Tensor], target: str = "weights") -> None:
+        """``target="weights"`` writes the bf16 working copy and the fp32 master; ``"m"`` /
+        ``"v"`` write an Adam moment (same keys and shapes)."""
+        if target not in ("weights", "m", "v"):
+            raise ValueError(f"unknown import target {target!r}")
         for (l, _), v in self.views.items():
             for name, n0, size, c0, r in self.sub_slices(v, adapter):
                 ka, kb = f"layers.{l}.{name}.lora_A", f"layers.{l}.{name}.lora_B"
                 if ka not in tensors or kb not in tensors:
                     raise KeyError(f"missing {ka} / {kb}")
-                v.stack.a[adapter, c0:c0 + r].copy_(tensors[ka])
-                v.stack.b[adapter, n0:n0 + size, c0:c0 + r].copy_(tensors[kb])
-                if self.master is not None:
+                if target == "weights":
+                    v.stack.a[adapter, c0:c0 + r].copy_(tensors[ka])
+                    v.stack.b[adapter, n0:n0 + size, c0:c0 + r].copy_(tensors[kb])
+                dense = self.master if target == "weights" else getattr(self, target)
+                if dense is not None:
                     sa, sb = self.state_offsets[(v.layer, v.proj, adapter, name)]
-                    self.master[sa:sa + r * v.K].view(r, v.K).copy_(tensors[ka])
-                    self.master[sb:sb + size * r].view(size, r).copy_(tensors[kb])
+                    dense[sa:sa + r * v.K].view(r, v.K).copy_(tensors[ka])
+                    dense[sb:sb + size * r].view(size, r).copy_(tensors[kb])
+
+    # ------------------------------------------------------------------ sharded optimizer state
+    def owned_state_mask(self, adapter: int, rank: int, world: int) -> torch.Tensor:
+        """Which elements of ``adapter``'s dense optimizer-state range data-parallel rank
+        ``rank`` owns under the fused gradient sync (bool ``[hi - lo]``).  That kernel updates
+        ``master`` / ``m`` / ``v`` only on the owner of each slice of each region (the same split
+        as :func:`lorafusion_b200.ops.elementwise.dp_slice`); everywhere else they keep their
+        old values, so a checkpoint must be stitched from the owners."""
+        from ..ops.elementwise import dp_slice
+
+        lo_s, hi_s = self.state_range[adapter]
+        mask = torch.zeros(hi_s - lo_s, dtype=torch.bool, device=self.device)
+        for _, rows, ld, col0, cols, state in self._chunk_rows[adapter]:
+            if cols == 0:
+                continue
+            lo, hi = dp_slice(rows * ld, rank, world)
+            if hi <= lo:
+                continue
+            r0, r1 = lo // ld, (hi - 1) // ld
+            base = state - lo_s
+            for row in {r0, r1}:  # first and last row may be covered in part
+                c_lo, c_hi = max(col0, lo - row * ld), min(col0 + cols, hi - row * ld)
+                if c_hi > c_lo:
+                    mask[base + row * cols + (c_lo - col0):base + row * cols + (c_hi - col0)] = True
+            if r1 - r0 >= 2:
+                mask[base + (r0 + 1) * cols:base + r1 * cols] = True
+        return mask
+
+    def gather_owned_state(self, group, rank: int, world: int) -> None:
+        """Collective over the data-parallel ``group``: make ``master`` / ``m`` / ``v`` complete
+        on every rank by taking each element from its owner (non-owned elements are zeroed and
+        the group sums).  Needed before saving a checkpoint under the fused gradient sync."""
+        import torch.distributed as dist
+
+        if world <= 1 or self.master is None:
+            return
+        for adapter in range(self.num_adapters):
+            lo, hi = self.state_range[adapter]
+            mask = self.owned_state_mask(adapter, rank, world)
+            for t in (self.master, self.m, self.v):
+                seg = t[lo:hi]
+                seg.masked_fill_(~mask, 0.0)
+                dist.all_reduce(seg, group=group)

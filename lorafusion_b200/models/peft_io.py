@@ -56,19 +56,33 @@ def adapter_config_dict(spec: AdapterSpec, base_model_name: str = "") -> dict:
     }
 
 
-def save_adapter(arena: LoRAArena, adapter: int, out_dir: str | Path, *, base_model_name: str = "",
-                 dtype: torch.dtype = torch.bfloat16) -> Path:
-    """Write adapter ``adapter`` as a PEFT checkpoint directory."""
+def internal_key(layer: int, module: str, which: str) -> str:
+    """Key of one LoRA factor in :meth:`LoRAArena.export_adapter` dictionaries."""
+    return f"layers.{layer}.{module}.lora_{which}"
+
+
+def write_adapter_tensors(tensors: dict, spec: AdapterSpec, out_dir: str | Path, *, base_model_name: str = "",
+                          dtype: torch.dtype = torch.bfloat16) -> Path:
+    """Write a dictionary in :meth:`LoRAArena.export_adapter` form (full, unsharded tensors of
+    any set of layers) as a PEFT checkpoint directory."""
     out = Path(out_dir)
     out.mkdir(parents=True, exist_ok=True)
-    spec = arena.adapters[adapter]
-    tensors = {}
-    for key, t in arena.export_adapter(adapter).items():
+    peft = {}
+    for key, t in tensors.items():
         _, layer, module, which = key.split(".")
-        tensors[_peft_key(int(layer), module, "A" if which == "lora_A" else "B")] = t.to(dtype).cpu().contiguous()
-    save_file(tensors, str(out / "adapter_model.safetensors"), metadata={"format": "pt"})
+        peft[_peft_key(int(layer), module, "A" if which == "lora_A" else "B")] = t.to(dtype).cpu().contiguous()
+    save_file(peft, str(out / "adapter_model.safetensors"), metadata={"format": "pt"})
     (out / "adapter_config.json").write_text(json.dumps(adapter_config_dict(spec, base_model_name), indent=2))
     return out
+
+
+def save_adapter(arena: LoRAArena, adapter: int, out_dir: str | Path, *, base_model_name: str = "",
+                 dtype: torch.dtype = torch.bfloat16) -> Path:
+    """Write adapter ``adapter`` as a PEFT checkpoint directory.  Single-rank form: under data,
+    tensor or pipeline parallelism use :func:`lorafusion_b200.train.checkpoint.save_checkpoint`,
+    which first makes the tensors complete."""
+    return write_adapter_tensors(arena.export_adapter(adapter), arena.adapters[adapter], out_dir,
+                                 base_model_name=base_model_name, dtype=dtype)
 
 
 def load_adapter_config(in_dir: str | Path, name: Optional[str] = None) -> AdapterSpec:
@@ -77,17 +91,17 @@ def load_adapter_config(in_dir: str | Path, name: Optional[str] = None) -> Adapt
                        dropout=float(cfg.get("lora_dropout", 0.0)), target_modules=tuple(cfg["target_modules"]))
 
 
-def load_adapter(arena: LoRAArena, adapter: int, in_dir: str | Path) -> None:
-    """Load a PEFT checkpoint into slot ``adapter`` of the arena (rank and targets must match
-    the slot's :class:`AdapterSpec`)."""
+def read_adapter_tensors(in_dir: str | Path, layers, have: AdapterSpec, device="cpu") -> dict:
+    """Read the LoRA factors of ``layers`` from a PEFT checkpoint directory into a dictionary in
+    :meth:`LoRAArena.export_adapter` form (fp32, full tensors).  Rank and target modules must
+    match ``have``."""
     spec = load_adapter_config(in_dir)
-    have = arena.adapters[adapter]
     if spec.r != have.r or set(spec.target_modules) != set(have.target_modules):
         raise ValueError(f"checkpoint (r={spec.r}, targets={sorted(spec.target_modules)}) does not match "
-                         f"adapter slot {adapter} (r={have.r}, targets={sorted(have.target_modules)})")
+                         f"the adapter slot (r={have.r}, targets={sorted(have.target_modules)})")
     raw = load_file(str(Path(in_dir) / "adapter_model.safetensors"))
     tensors = {}
-    for l in arena.layers:
+    for l in layers:
         for module in have.target_modules:
             for which in ("A", "B"):
                 k = _peft_key(l, module, which)
@@ -96,33 +110,63 @@ def load_adapter(arena: LoRAArena, adapter: int, in_dir: str | Path) -> None:
                 src = raw.get(k, raw.get(alt))
                 if src is None:
                     raise KeyError(f"{k} missing from checkpoint")
-                tensors[f"layers.{l}.{module}.lora_{which}"] = src.to(arena.device, torch.float32)
-    arena.import_adapter(adapter, tensors)
+                tensors[internal_key(l, module, which)] = src.to(device, torch.float32)
+    return tensors
+
+
+def load_adapter(arena: LoRAArena, adapter: int, in_dir: str | Path) -> None:
+    """Load a PEFT checkpoint into slot ``adapter`` of the arena (rank and targets must match
+    the slot's :class:`AdapterSpec`; only the arena's layers are read, so a pipeline stage
+    loads its part of a whole-model checkpoint)."""
+    arena.import_adapter(adapter, read_adapter_tensors(in_dir, arena.layers, arena.adapters[adapter], arena.device))
+
+
+def write_training_state(state: dict, path: str | Path, *, step: int, data_cursor: int = 0,
+                         extra: Optional[dict] = None) -> None:
+    """``state = {"master" | "m" | "v": {key: full fp32 tensor}}`` with keys as in
+    :meth:`LoRAArena.export_adapter`: a layout-independent file, so a run may resume under
+    another dp x pp x tp layout than the one that saved it."""
+    payload = {"version": 2, "step": int(step), "data_cursor": int(data_cursor), "extra": extra or {},
+               "state": {name: {k: t.detach().cpu().clone() for k, t in tensors.items()}
+                         for name, tensors in state.items()}}
+    Path(path).parent.mkdir(parents=True, exist_ok=True)
+    torch.save(payload, str(path))
+
+
+def read_training_state(path: str | Path) -> dict:
+    return torch.load(str(path), map_location="cpu", weights_only=False)
 
 
 def save_training_state(arena: LoRAArena, adapter: int, path: str | Path, *, data_cursor: int = 0,
                         extra: Optional[dict] = None) -> None:
-    """fp32 master / Adam moments of one adapter (its dense optimizer-state range), step
-    count and data cursor."""
-    lo, hi = arena.state_range[adapter]
-    state = {"step": arena.steps[adapter], "data_cursor": data_cursor, "extra": extra or {},
-             "numel": hi - lo,
-             "master": arena.master[lo:hi].cpu().clone(),
-             "m": arena.m[lo:hi].cpu().clone(),
-             "v": arena.v[lo:hi].cpu().clone()}
-    Path(path).parent.mkdir(parents=True, exist_ok=True)
-    torch.save(state, str(path))
+    """fp32 master / Adam moments of one adapter, keyed by layer and module, plus step count and
+    data cursor.  Single-rank form (see :func:`save_adapter`)."""
+    write_training_state({name: arena.export_adapter(adapter, name) for name in ("master", "m", "v")}, path,
+                         step=arena.steps[adapter], data_cursor=data_cursor, extra=extra)
+
+
+def apply_training_state(arena: LoRAArena, adapter: int, payload: dict, transform=None) -> dict:
+    """Put a payload of :func:`read_training_state` into the arena.  ``transform(tensors) ->
+    tensors`` cuts full tensors down to this rank's shard (tensor parallelism); tensors of
+    layers the arena does not hold are ignored."""
+    if int(payload.get("version", 1)) < 2:  # flat dense ranges of an unsharded single-rank arena
+        lo, hi = arena.state_range[adapter]
+        if int(payload["numel"]) != hi - lo:
+            raise ValueError(f"checkpoint holds {payload['numel']} optimizer elements, adapter {adapter} has {hi - lo}")
+        arena.master[lo:hi].copy_(payload["master"])
+        arena.m[lo:hi].copy_(payload["m"])
+        arena.v[lo:hi].copy_(payload["v"])
+        arena.import_adapter(adapter, arena.export_adapter(adapter, "master"))
+    else:
+        for name, target in (("master", "weights"), ("m", "m"), ("v", "v")):
+            tensors = {k: t.to(arena.device) for k, t in payload["state"][name].items()
+                       if int(k.split(".")[1]) in set(arena.layers)}
+            if transform is not None:
+                tensors = transform(tensors)
+            arena.import_adapter(adapter, tensors, target=target)  # "weights" also refreshes the bf16 copy
+    arena.steps[adapter] = int(payload["step"])
+    return {"step": payload["step"], "data_cursor": payload["data_cursor"], "extra": payload["extra"]}
 
 
 def load_training_state(arena: LoRAArena, adapter: int, path: str | Path) -> dict:
-    state = torch.load(str(path), map_location="cpu", weights_only=False)
-    lo, hi = arena.state_range[adapter]
-    if int(state["numel"]) != hi - lo:
-        raise ValueError(f"checkpoint holds {state['numel']} optimizer elements, adapter {adapter} has {hi - lo}")
-    arena.master[lo:hi].copy_(state["master"])
-    arena.m[lo:hi].copy_(state["m"])
-    arena.v[lo:hi].copy_(state["v"])
-    # the bf16 working copy follows the restored master weights
-    arena.import_adapter(adapter, arena.export_adapter(adapter))
-    arena.steps[adapter] = int(state["step"])
-    return {"step": state["step"], "data_cursor": state["data_cursor"], "extra": state["extra"]}
+    return apply_training_state(arena, adapter, read_training_state(path))

@@ -94,6 +94,15 @@ def cross_entropy_inplace(logits: torch.Tensor, labels: torch.Tensor, grad_scale
 ADAM_WORK_UNIT = 32768  # elements per CTA (a multiple of 4)
 
 
+def dp_slice(total: int, rank: int, world: int) -> tuple[int, int]:
+    """Element range ``[lo, hi)`` of a region of ``total`` elements that data-parallel rank
+    ``rank`` of ``world`` reduces, updates and owns the optimizer state of: regions are cut in
+    ``world`` slices of whole 4-element groups."""
+    total4 = total // 4
+    per = (total4 + world - 1) // world
+    return 4 * min(total4, per * rank), 4 * min(total4, per * (rank + 1))
+
+
 def build_adam_work_items(chunk_rows, *, rank: int = 0, world: int = 1, unit: int = ADAM_WORK_UNIT) -> torch.Tensor:
     """Cut every region of a chunk table (rows ``offset, rows, ld, col0, cols, state``) into
     pieces of at most ``unit`` elements: int32 ``[n, 3]`` rows ``(chunk index, first element,
@@ -108,9 +117,7 @@ def build_adam_work_items(chunk_rows, *, rank: int = 0, world: int = 1, unit: in
         if world > 1:
             if not vec:
                 raise ValueError("data-parallel slicing needs regions made of whole 4-element groups")
-            total4 = total // 4
-            per = (total4 + world - 1) // world
-            lo, hi = 4 * min(total4, per * rank), 4 * min(total4, per * (rank + 1))
+            lo, hi = dp_slice(total, rank, world)
         else:
             lo, hi = 0, total
         step = unit if vec else max(1, unit // 4)

@@ -41,13 +41,20 @@ class MockMultiLoRADataProvider:
                  global_batch_sizes: Sequence[int], *, capacity: int, num_pipeline_stages: int, vocab_size: int,
                  schedule_path: Optional[str | Path] = None, num_global_batches: Optional[int] = None,
                  solver_time_limit: float = 1.0, use_exact: bool = True, dp_rank: int = 0, seed: int = 0,
-                 num_workers: int = 4, total_multiple: int = 128):
+                 num_workers: int = 4, total_multiple: int = 128,
+                 start_global_batches: Optional[Sequence[int]] = None, index_offset: int = 0):
+        """``start_global_batches[i]`` = global batches of adapter ``i`` already consumed by an
+        earlier run (resume): they are skipped.  ``index_offset`` = microbatches that run
+        executed; it keeps the per-microbatch seeds (token ids, dropout) going where they stopped."""
         self.total_multiple = total_multiple
+        self.index_offset = int(index_offset)
         self.adapters, self.datasets = list(adapters), list(datasets)
         self.global_batch_sizes = [int(g) for g in global_batch_sizes]
         self.capacity, self.num_pipeline_stages, self.vocab_size = capacity, num_pipeline_stages, vocab_size
         self.dp_rank, self.seed = dp_rank, seed
         self.data = [ds.global_batches(g) for ds, g in zip(self.datasets, self.global_batch_sizes)]
+        if start_global_batches is not None:
+            self.data = [d[int(s0):] for d, s0 in zip(self.data, start_global_batches)]
         if num_global_batches is not None:
             self.data = [d[:num_global_batches] for d in self.data]
         if schedule_path is not None:
@@ -89,7 +96,7 @@ class MockMultiLoRADataProvider:
 
     def microbatches(self, start: int = 0, stop: Optional[int] = None) -> list:
         stop = len(self.flat) if stop is None else min(stop, len(self.flat))
-        return [ScheduledMicrobatch(spec_from_micro_batch_info(m, self.total_multiple), m, i)
+        return [ScheduledMicrobatch(spec_from_micro_batch_info(m, self.total_multiple), m, i + self.index_offset)
                 for i, m in enumerate(self.flat)
                 if start <= i < stop]
 

@@ -68,6 +68,60 @@ def test_emulated_ranks_match_allreduce_plus_adamw(world):
     assert_close(stitched[touched], ref.master[touched], rtol=1e-5, atol=1e-6, msg="sharded master weights")
 
 
+@pytest.mark.parametrize("world", [2, 4])
+def test_checkpoint_after_fused_steps_equals_allreduce_plus_adamw(world, tmp_path):
+    """Three fused steps on emulated ranks; the optimizer state is stitched from its owners the
+    way ``gather_owned_state`` does with an all-reduce (masked sum), saved from rank 0 and loaded
+    into a fresh single-rank arena: weights, master and both moments equal the reference that ran
+    sum-of-gradients + the plain Adam kernel."""
+    from lorafusion_b200.parallel.dp_sync import launch_allreduce_adam
+    from lorafusion_b200.train import checkpoint as ck
+
+    arenas = [_arena() for _ in range(world)]
+    ref = _arena()
+    hp = dict(lr=1e-2, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.05)
+    for step in range(1, 4):
+        g = torch.Generator(device="cuda").manual_seed(10 + step)
+        total = torch.zeros_like(ref.grad)
+        for a in arenas:
+            a.grad.copy_(torch.randn(a.numel, generator=g, device="cuda"))
+            total += a.grad
+        for adapter in range(2):
+            ref.grad.copy_(total)
+            ref.adam_step(adapter, grad_scale=1.0 / world, **hp)
+            for off, rows, ld, _, _, _ in ref.chunk_table(adapter).cpu().tolist():
+                total[off:off + rows * ld] = 0
+            for r, a in enumerate(arenas):
+                launch_allreduce_adam(
+                    chunks=a.chunk_table(adapter), grad_ptrs=[x.grad.data_ptr() for x in arenas],
+                    work_ptrs=[x.work.data_ptr() for x in arenas], grad_mc=0, work_mc=0, master=a.master, m=a.m,
+                    v=a.v, flag_ptrs=None, done_counter=None, rank=r, world=world, epoch=0, sync=False,
+                    use_multimem=False, step=step, grad_scale=1.0 / world, device="cuda", **hp)
+                a.steps[adapter] = step
+    # rank 0 alone holds stale state for the slices it does not own
+    lo, hi = arenas[0].state_range[0]
+    assert not torch.equal(arenas[0].m[lo:hi], ref.m[lo:hi])
+    for adapter in range(2):
+        lo, hi = ref.state_range[adapter]
+        for name in ("master", "m", "v"):
+            acc = torch.zeros(hi - lo, device="cuda")
+            for r, a in enumerate(arenas):
+                acc += getattr(a, name)[lo:hi].masked_fill(~a.owned_state_mask(adapter, r, world), 0.0)
+            getattr(arenas[0], name)[lo:hi].copy_(acc)
+    ck.save_checkpoint(arenas[0], tmp_path, base_model_name="tiny")
+    fresh = _arena(seed=5)
+    metas = ck.load_checkpoint(fresh, tmp_path)
+    assert [m["step"] for m in metas] == [3, 3]
+    for adapter in range(2):
+        for name in ("master", "m", "v"):
+            got, want = fresh.export_adapter(adapter, name), ref.export_adapter(adapter, name)
+            for k in want:
+                assert_close(got[k], want[k], rtol=1e-6, atol=1e-7, msg=f"{name} {k}")
+        got, want = fresh.export_adapter(adapter, "work"), ref.export_adapter(adapter, "work")
+        for k in want:
+            assert_close(got[k], want[k], msg=f"work {k}")
+
+
 _CHILD = r"""
 import os, sys, torch, torch.distributed as dist
 os.environ["NCCL_NVLS_ENABLE"] = "0"
