@@ -13,6 +13,7 @@
 // (The reference calls FlashAttention-2's backward through autograd.)
 #include <stdio.h>
 
+#include "../common/launch.h"
 #include "../common/tensormap.h"
 #include "attn_common.cuh"
 
@@ -466,13 +467,10 @@ extern "C" int lf_attn_bwd(const void* qkv, const void* out, const void* d_out, 
   if (rc != 0) return -20 + rc;
   rc = make_tmap_2d_b16(&tmDO, d_out, (uint64_t)M, (uint64_t)Hq * ATT_D, (uint64_t)ldo, 128, 64, true);
   if (rc != 0) return -30 + rc;
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(attn_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BWD_SMEM) != cudaSuccess ||
-        cudaFuncSetAttribute(attn_dkdv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BWD_SMEM) != cudaSuccess)
-      return -10;
-    configured = true;
-  }
+  static PerDeviceOnce dq_configured, dkdv_configured;
+  if (ensure_max_dynamic_smem(dq_configured, attn_dq_kernel, BWD_SMEM) != cudaSuccess ||
+      ensure_max_dynamic_smem(dkdv_configured, attn_dkdv_kernel, BWD_SMEM) != cudaSuccess)
+    return -10;
   {
     const long long warps = M * Hq;
     const int block = 256;
@@ -511,19 +509,21 @@ static __device__ __align__(256) float g_noalloc_delta[LF_ATTN_NOALLOC_MAX_DELTA
 
 namespace {
 constexpr int kMaxDevices = 64;
-float* g_noalloc_delta_addr[kMaxDevices] = {nullptr};
+std::atomic<float*> g_noalloc_delta_addr[kMaxDevices];  // zero-initialised (static storage)
 
 // In host code `g_noalloc_delta` is only a handle for the symbol, not a device address;
 // the real address has to be asked for once per device, with that device current.
 int noalloc_delta_address(float** out) {
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return -1;
-  if (g_noalloc_delta_addr[dev] == nullptr) {
+  float* addr = g_noalloc_delta_addr[dev].load(std::memory_order_acquire);
+  if (addr == nullptr) {  // two host threads may both look it up: they get the same answer
     void* p = nullptr;
     if (cudaGetSymbolAddress(&p, g_noalloc_delta) != cudaSuccess || p == nullptr) return -1;
-    g_noalloc_delta_addr[dev] = static_cast<float*>(p);
+    addr = static_cast<float*>(p);
+    g_noalloc_delta_addr[dev].store(addr, std::memory_order_release);
   }
-  *out = g_noalloc_delta_addr[dev];
+  *out = addr;
   return 0;
 }
 }  // namespace
@@ -546,43 +546,7 @@ extern "C" int lf_attn_bwd_noalloc(const void* qkv, const void* out, const void*
     fprintf(stderr, "lf_attn_bwd_noalloc: could not resolve the scratch symbol on this device\n");
     return LF_ATTN_NOALLOC_SETUP_FAILED;
   }
-  cudaStream_t st = (cudaStream_t)stream;
-  CUtensorMap tmQKV, tmDO;
-  int rc = make_tmap_2d_b16(&tmQKV, qkv, (uint64_t)M, (uint64_t)ld_qkv, (uint64_t)ld_qkv, 128, 64, true);
-  if (rc != 0) return -20 + rc;
-  rc = make_tmap_2d_b16(&tmDO, d_out, (uint64_t)M, (uint64_t)Hq * ATT_D, (uint64_t)ldo, 128, 64, true);
-  if (rc != 0) return -30 + rc;
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(attn_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BWD_SMEM) != cudaSuccess ||
-        cudaFuncSetAttribute(attn_dkdv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BWD_SMEM) != cudaSuccess)
-      return -10;
-    configured = true;
-  }
-  {
-    const long long warps = M * Hq;
-    const int block = 256;
-    const long long grid = (warps * 32 + block - 1) / block;
-    attn_delta_kernel<<<(unsigned)grid, block, 0, st>>>((const __nv_bfloat16*)out,
-                                                         (const __nv_bfloat16*)d_out, delta, M, Hq, ldo);
-  }
-  AttnBwdParams p;
-  p.tiles = (const int4*)tiles;
-  p.num_tiles = num_tiles;
-  p.Hq = Hq;
-  p.Hkv = Hkv;
-  p.q_col0 = q_col0;
-  p.k_col0 = k_col0;
-  p.v_col0 = v_col0;
-  p.dqkv = (__nv_bfloat16*)dqkv;
-  p.ld_qkv = ld_qkv;
-  p.lse = lse;
-  p.delta = delta;
-  p.M_total = M;
-  p.scale = scale;
-  p.scale_log2e = scale * 1.4426950408889634f;
-  p.err = err;
-  attn_dq_kernel<<<dim3(num_tiles, Hq), BWD_THREADS, BWD_SMEM, st>>>(p, tmQKV, tmDO);
-  attn_dkdv_kernel<<<dim3(num_tiles, Hkv), BWD_THREADS, BWD_SMEM, st>>>(p, tmQKV, tmDO);
-  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+  // Same launches as lf_attn_bwd, with the built-in array in place of the caller's scratch.
+  return lf_attn_bwd(qkv, out, d_out, dqkv, M, ld_qkv, q_col0, k_col0, v_col0, Hq, Hkv, tiles, num_tiles, ldo,
+                     lse, delta, scale, err, stream);
 }

@@ -14,6 +14,7 @@
 // map; O is written token-major [M, Hq * 128]; the log-sum-exp is kept for the backward.
 #include <stdio.h>
 
+#include "../common/launch.h"
 #include "../common/tensormap.h"
 #include "attn_common.cuh"
 
@@ -290,13 +291,8 @@ extern "C" int lf_attn_fwd(const void* qkv, long long M, long long ld_qkv, int q
   CUtensorMap tm;
   int rc = make_tmap_2d_b16(&tm, qkv, (uint64_t)M, (uint64_t)ld_qkv, (uint64_t)ld_qkv, 128, 64, true);
   if (rc != 0) return -20 + rc;
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             FWD_SMEM) != cudaSuccess)
-      return -10;
-    configured = true;
-  }
+  static PerDeviceOnce configured;
+  if (ensure_max_dynamic_smem(configured, attn_fwd_kernel, FWD_SMEM) != cudaSuccess) return -10;
   AttnFwdParams p;
   p.tiles = (const int4*)tiles;
   p.num_tiles = num_tiles;

@@ -18,7 +18,9 @@
 //     rejected with LF_ATTN_NOALLOC_TOO_LARGE and nothing is launched.
 //   * Every GPU that loads the library carries those 4 MiB until the process exits.
 //   * The first call on each device looks up the device address of the array (with that
-//     device current).  Make that first call outside of any stream capture.
+//     device current).  Make that first call outside of any stream capture.  Two host
+//     threads that make their first calls at the same time both do the look-up and get the
+//     same address; the ordering of their launches is still the callers' business (below).
 //   * All calls on a device share the one array.  It is fully rewritten by each call, so
 //     nothing has to be cleared, but two calls whose kernels overlap on the GPU (different
 //     streams without ordering between them) race on it: serialise them.

@@ -117,6 +117,26 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
   }
 }
 
+// Named barrier over `NTHREADS` threads that also ANDs a predicate: every participant gets
+// the same answer.  Used where a group of warps must agree on "go on" / "abort" before a later
+// named barrier: a thread that saw the abort flag a few polls earlier than its neighbours
+// would otherwise leave while they wait for its arrival.
+template <int ID, int NTHREADS>
+__device__ __forceinline__ bool named_bar_and(bool pred) {
+  uint32_t out;
+  asm volatile(
+      "{\n"
+      ".reg .pred pin, pout;\n"
+      "setp.ne.u32 pin, %1, 0;\n"
+      "bar.red.and.pred pout, %2, %3, pin;\n"
+      "selp.u32 %0, 1, 0, pout;\n"
+      "}\n"
+      : "=r"(out)
+      : "r"(uint32_t(pred)), "n"(ID), "n"(NTHREADS)
+      : "memory");
+  return out != 0;
+}
+
 // ----------------------------------------------------------------------------------
 // cross-CTA / cross-GPU flag waits (system scope, acquire)
 // ----------------------------------------------------------------------------------

@@ -20,6 +20,7 @@
 // of tile i+1.
 #include <stdio.h>
 
+#include "../common/launch.h"
 #include "../common/philox.cuh"
 #include "../common/ptx.cuh"
 #include "../common/tensormap.h"
@@ -354,7 +355,12 @@ __global__ void __launch_bounds__((MASK_A || NF4B) ? (192 + 32 * kNumMaskWarps)
       const bool has_slab = nkb2 > 0;
       const int buf = tile_iter % NBUF;
       const uint32_t bph = (tile_iter / NBUF) & 1;
-      if (!mbar_wait(&tfull[buf], bph, ctx, ERR_WAIT_TMEM_FULL)) {
+      bool got = mbar_wait(&tfull[buf], bph, ctx, ERR_WAIT_TMEM_FULL);
+      // The reduce-scatter epilogue ends in a named barrier of its 128 threads: they must all
+      // take the same branch here, or one that saw an abort earlier would leave the others
+      // waiting for its arrival.
+      if (TP == 2) got = named_bar_and<1, 128>(got);
+      if (!got) {
         ok = false;
         break;
       }
@@ -490,11 +496,9 @@ __global__ void __launch_bounds__((MASK_A || NF4B) ? (192 + 32 * kNumMaskWarps)
         if (!wait_flag_ge(tp.rs_cnt + (et * tp.tiles_per_shard + lt) * p.num_n_tiles + nt, tp.epoch, ctx))
           ok = false;
       }
-      asm volatile("bar.sync 2, 128;" ::: "memory");
-      if (aborted(ctx)) {
-        ok = false;
-        break;
-      }
+      // one agreed answer for the 128 reduce threads (see named_bar_and)
+      ok = named_bar_and<2, 128>(ok && !aborted(ctx));
+      if (!ok) break;
       // row of this item inside every source's stage [M, N]
       const long long grow0 = (long long)tp.rank * ms;
       for (int v0 = et; v0 < NV; v0 += 256) {
@@ -784,14 +788,13 @@ static int launch_variant(const GemmKParams& kp, const CUtensorMap& tA, const CU
                           cudaStream_t stream, const TpParams& tp = TpParams()) {
   auto kern = umma_gemm_kernel<BN, NACC, A_MN, B_MN, B2_MN, EPI, MASK_A, TP, NF4B>;
   constexpr int smem = SmemPlan<BN, NF4B>::TOTAL;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  static PerDeviceOnce configured;  // one per template instantiation
+  {
+    cudaError_t e = ensure_max_dynamic_smem(configured, kern, smem);
     if (e != cudaSuccess) {
       fprintf(stderr, "lf_gemm: cudaFuncSetAttribute failed: %s\n", cudaGetErrorString(e));
       return -10;
     }
-    configured = true;
   }
   const int threads = (MASK_A || NF4B) ? (192 + 32 * kNumMaskWarps) : (TP != 0 ? 192 + 32 * kNumCommWarps : 192);
   kern<<<grid, threads, smem, stream>>>(kp, tA, tB, tA2, tB2, tp);

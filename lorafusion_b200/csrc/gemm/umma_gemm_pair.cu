@@ -23,6 +23,7 @@
 // empty" lives in the leader and collects 256 arrivals.  All waits are bounded.
 #include <stdio.h>
 
+#include "../common/launch.h"
 #include "../common/philox.cuh"
 #include "../common/ptx.cuh"
 #include "../common/tensormap.h"
@@ -342,13 +343,10 @@ template <bool B_MN, int NACC, int EPI>
 static int launch(const Params& p, const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tA2,
                   const CUtensorMap& tB2, int pairs, cudaStream_t st) {
   auto kern = umma_gemm_pair_kernel<B_MN, NACC, EPI>;
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL) != cudaSuccess) {
-      fprintf(stderr, "lf_gemm_pair: cudaFuncSetAttribute failed\n");
-      return -10;
-    }
-    configured = true;
+  static lf::PerDeviceOnce configured;  // one per template instantiation
+  if (lf::ensure_max_dynamic_smem(configured, kern, SMEM_TOTAL) != cudaSuccess) {
+    fprintf(stderr, "lf_gemm_pair: cudaFuncSetAttribute failed\n");
+    return -10;
   }
   kern<<<2 * pairs, 192, SMEM_TOTAL, st>>>(p, tA, tB, tA2, tB2);
   cudaError_t e = cudaGetLastError();

@@ -162,17 +162,15 @@ for quantize, recompute in ((False, False), (False, True)):
         # tensors on save and cut again on load
         from lorafusion_b200.train import checkpoint as ck
         lay = ck.CheckpointLayout(tp_group=dist.group.WORLD, tp_rank=rank, tp_size=world)
-        for a in range(n):
-            tp.arena.adam_step(a, lr=1e-2)
-            full.arena.adam_step(a, lr=1e-2)
+        gm = torch.Generator(device=dev).manual_seed(21)   # same values on every rank
+        tp.arena.m.copy_(torch.randn(tp.arena.m.shape, generator=gm, device=dev))
         out_dir = os.environ["CKPT_DIR"]
         ck.save_checkpoint(tp.arena, out_dir, lay, base_model_name="tiny")
         single = DecoderStage(cfg, adapters, dev, init_b_std=0.0, seed=11, recompute=False)
         ck.load_checkpoint(single.arena, out_dir)
-        for a in range(n):
+        for a in range(n):   # the shards were put together in rank order: equal to the unpartitioned weights
             got, want = single.arena.export_adapter(a, "master"), full.arena.export_adapter(a, "master")
-            for k in want:   # same update from (nearly) the same gradients
-                assert_close_two_rounds(got[k], want[k], atol=2e-3, rtol=5e-2, msg=f"checkpointed {k}")
+            assert got.keys() == want.keys() and all(torch.equal(got[k], want[k]) for k in want)
         before = {a: tp.arena.export_adapter(a, "m") for a in range(n)}
         work_before = tp.arena.work.clone()
         tp.arena.work.zero_(); tp.arena.m.zero_(); tp.arena.master.zero_()

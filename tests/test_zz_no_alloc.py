@@ -5,7 +5,8 @@ point of the call (fixed memory partitions, callbacks of another runtime, frozen
 allocators): its temporary buffer is a fixed array inside the library.  The test drives the
 raw symbol with ctypes exactly as such a caller would -- passing only buffers that already
 exist -- and checks, on two calls in a row (the second one reuses the array with the first
-call's contents still in it), that it returns the same gradients as ``lf_attn_bwd``.
+call's contents still in it), that it returns the same gradients as ``lf_attn_bwd``, and that
+the amount of free device memory is the same after the call as before it.
 It also checks that an oversized problem is refused instead of overrunning the array.
 """
 
@@ -59,12 +60,19 @@ def test_noalloc_matches_regular_entry_point_twice():
         M = qkv.shape[0]
         dqkv = torch.empty_like(qkv)  # the caller's own, pre-existing output buffer
         k0, v0 = Hq * 128, (Hq + Hkv) * 128
+        err_ptr, stream_ptr = nv.err_word("cuda").data_ptr(), nv.current_stream_ptr()
         torch.cuda.synchronize()
+        free_before, _ = torch.cuda.mem_get_info()
         rc = fn(qkv.data_ptr(), out.data_ptr(), d_out.data_ptr(), dqkv.data_ptr(), M, qkv.stride(0), 0, k0, v0,
                 Hq, Hkv, tiles.tiles.data_ptr(), tiles.num_tiles, out.stride(0), lse.data_ptr(), scale,
-                nv.err_word("cuda").data_ptr(), nv.current_stream_ptr())
+                err_ptr, stream_ptr)
         assert rc == 0, f"call {call} returned {rc}"
         torch.cuda.synchronize()
+        free_after, _ = torch.cuda.mem_get_info()
+        # the driver reports free memory of the whole device: nothing was taken by the call
+        # (the first call may only have loaded the kernels' module, which happens before it
+        # in this process because the regular entry point ran the same kernels above)
+        assert free_after == free_before, f"call {call}: free device memory changed by {free_before - free_after} bytes"
         assert_close(dqkv, expected, msg=f"no-alloc attention backward, call {call}")
 
 
