@@ -11,12 +11,15 @@ One *step* = every rank runs forward + backward of ``--microbatches`` packed mic
 data-parallel group, and every adapter takes an AdamW step.  Weak scaling: per-GPU work is
 fixed as N grows.  Throughput counts real (unpadded) tokens summed over all GPUs.
 
-Two measurements are reported:
-* ``value``  -- device-timed (CUDA events, max over ranks) with the step's batches already
-  resident on the GPU;
-* ``e2e``    -- the same K steps through ``MultiLoRATrainer.train_step``: token arrays start
-  in pinned host memory and are copied host-to-device every step, and the loss is read back
-  to the host every step.
+Two measurements come out of ONE pass over the K timed steps (CUDA events, max over ranks):
+* ``e2e``    -- the whole pass: every step copies its token arrays from pinned host memory to
+  the device, computes, and reads the loss back to the host;
+* ``value``  -- the compute part alone (forward, backward, gradient reduction, optimizer), summed
+  over the steps.
+
+Every step's microbatches are packed by the solver from one pool of samples for the whole
+data-parallel group and dealt so that all ranks get the same number of nearly full microbatches
+and about the same attention work (``train.data.pack_balanced_dp_step``).
 
 ``--impl reference`` reports why the reference itself cannot be run here.
 """
@@ -52,7 +55,7 @@ def parse_args():
     ap.add_argument("--no-quantize", action="store_true")
     ap.add_argument("--recompute", default="auto", choices=["auto", "all", "none"],
                     help="activation recomputation: all layers, none, or as memory allows")
-    ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--skip-e2e", action="store_true", help="accepted for compatibility; both numbers come from one pass")
     ap.add_argument("--offload", default="auto", choices=["auto", "on", "off"],
                     help="park gate|up activations in pinned host memory over PCIe; auto = time one step "
                          "with and without during set-up and keep the faster plan")
@@ -61,6 +64,7 @@ def parse_args():
     ap.add_argument("--lora-mode", default="fused", choices=["fused", "unfused"],
                     help="unfused = same-GPU baseline: separate base GEMM + cuBLAS LoRA GEMMs + stored mask")
     ap.add_argument("--multimem", action="store_true", help="use NVLS multimem loads/stores in the fused sync")
+    ap.add_argument("--seed", type=int, default=1234, help="seed of the synthetic sample lengths")
     return ap.parse_args()
 
 
@@ -129,34 +133,26 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def make_step_specs(rng_seed: int, capacity: int, n_microbatches: int):
-    """Microbatches of one step: samples are drawn round-robin from the four adapters' length
-    distributions (lognormal medians 256/512/1024/2048, sigma 0.5-0.8, clipped to [32, 8192])
-    until a microbatch's padded token count would exceed the capacity."""
+def make_all_step_specs(seed: int, capacity: int, per_rank: int, world: int, n_steps: int):
+    """``specs[step][rank]`` = the microbatches of every rank for every step.  Samples are drawn
+    round-robin from the four adapters' length distributions (lognormal medians
+    256/512/1024/2048, sigma 0.5-0.8, clipped to [32, 8192]) into a pool a little larger than
+    the step needs; the solver packs it, and what it leaves over opens the next step's pool."""
     import numpy as np
 
-    from lorafusion_b200.train.data import LengthDistribution, MicroBatchSpec
+    from lorafusion_b200.train.data import LengthDistribution, pack_balanced_dp_step
 
     dists = [LengthDistribution(256, 0.5, 32, 8192), LengthDistribution(512, 0.6, 32, 8192),
              LengthDistribution(1024, 0.7, 32, 8192), LengthDistribution(2048, 0.8, 32, 8192)]
-    rng = np.random.default_rng(rng_seed)
-    specs = []
-    for _ in range(n_microbatches):
-        per = {a: [] for a in range(4)}
-
-        def padded(p):
-            return sum(((sum(v) + 127) // 128) * 128 for v in p.values() if v)
-
-        a, misses = 0, 0
-        while misses < 8:
-            n = int(dists[a].sample(1, int(rng.integers(1 << 31)))[0])
-            per[a].append(n)
-            if padded(per) > capacity:
-                per[a].pop()
-                misses += 1
+    rng = np.random.default_rng(seed)
+    out, pool, a = [], [], 0
+    for _ in range(n_steps):
+        while sum(n for _, n in pool) < world * per_rank * capacity * 1.08:
+            pool.append((a, int(dists[a].sample(1, int(rng.integers(1 << 31)))[0])))
             a = (a + 1) % 4
-        specs.append(MicroBatchSpec([(k, v) for k, v in per.items() if v]))
-    return specs
+        dealt, pool = pack_balanced_dp_step(pool, world, per_rank, capacity)
+        out.append(dealt)
+    return out
 
 
 def main():
@@ -197,7 +193,7 @@ def main():
                                dp_group=dist.group.WORLD if world > 1 else None, seed=1234, init_b_std=0.01,
                                grad_sync=args.grad_sync, use_multimem=args.multimem)
     if "expandable_segments:True" in os.environ.get("PYTORCH_CUDA_ALLOC_CONF", ""):
-        trainer.stage.reserve_bytes = 16 << 30  # little fragmentation to provide for
+        trainer.stage.reserve_bytes = 8 << 30  # little fragmentation to provide for
     trainer.stage.plan_activations(args.capacity)
     torch.cuda.synchronize()
     if rank == 0:
@@ -206,54 +202,26 @@ def main():
               f"{torch.cuda.memory_allocated() / 2**30:.1f} GiB", file=sys.stderr)
 
     n_total = args.warmup + args.steps
-    step_specs = [make_step_specs(1000 * rank + s, args.capacity, args.microbatches) for s in range(n_total)]
+    # Rank 0 packs every step for the whole group (the branch and bound stops on a time limit,
+    # so two ranks could find different packings) and hands every rank its share.
+    box = [make_all_step_specs(args.seed, args.capacity, args.microbatches, world, n_total + 1)
+           if rank == 0 else None]
+    if world > 1:
+        dist.broadcast_object_list(box, src=0)
+    all_specs = box[0]
+    step_specs = [all_specs[s][rank] for s in range(n_total)]
+    probe_specs = all_specs[n_total][rank]
     tokens_per_step = [sum(sp.total_tokens for sp in specs) for specs in step_specs]
+    sq = [sum(n * n for sp in st_[r] for _, lens in sp.segments for n in lens) for st_ in all_specs[:n_total]
+          for r in range(world)]
+    balance = {"attention_cost_max_over_mean": round(max(
+        max(sq[s * world:(s + 1) * world]) * world / max(sum(sq[s * world:(s + 1) * world]), 1)
+        for s in range(n_total)), 3)}
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
-
-    def run_pass(e2e: bool):
-        """Returns (elapsed ms for the timed steps (max over ranks), tokens, clocks, launches)."""
-        host = [trainer.stage_batches(specs, s) for s, specs in enumerate(step_specs)]
-        dev = None
-        if not e2e:
-            dev = [trainer.to_device(specs, h, s) for s, (specs, h) in enumerate(zip(step_specs, host))]
-        last_loss = None
-        for s in range(args.warmup):
-            if e2e:
-                last_loss = trainer.train_step(step_specs[s], s, host=host[s])
-            else:
-                trainer.step_on_device(dev[s])
-        barrier()
-        sampler = ClockSampler(local_rank)
-        sampler.start()
-        launches0 = _native.launch_count()
-        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        ev0.record()
-        for s in range(args.warmup, n_total):
-            if e2e:
-                last_loss = trainer.train_step(step_specs[s], s, host=host[s])
-            else:
-                last_loss = trainer.step_on_device(dev[s])
-        ev1.record()
-        barrier()
-        clocks = sampler.stop()
-        ms = ev0.elapsed_time(ev1)
-        launches = _native.launch_count() - launches0
-        toks = sum(tokens_per_step[args.warmup:])
-        stats = torch.tensor([ms, float(toks)], dtype=torch.float64, device=device)
-        if world > 1:
-            mx = stats.clone()
-            dist.all_reduce(mx, op=dist.ReduceOp.MAX)
-            sm = stats.clone()
-            dist.all_reduce(sm, op=dist.ReduceOp.SUM)
-            ms, toks = float(mx[0]), float(sm[1])
-        _native.check_device_errors()
-        loss_val = float(last_loss) if last_loss is not None else float("nan")
-        bytes_in = sum(h2d_bytes(b) for b in (dev[-1] if dev else trainer.to_device(step_specs[-1], host[-1], 0)))
-        return ms, toks, clocks, launches, loss_val, bytes_in
 
     def agree(flag: bool) -> bool:
         """True only if every rank says True."""
@@ -275,28 +243,80 @@ def main():
         return float(t.item())
 
     # ---- set-up (untimed): choose the activation plan by measurement ----
-    offload_note = "off"
+    # One warm step and one timed step without offloading; then, if the host link measured
+    # under the load of all ranks can take at least a few layers per forward pass, one timed
+    # step with that many layers' gate|up parked in host memory.  The faster plan stays.
+    offload_note, like_for_like = "off", None
+    host0 = trainer.stage_batches(probe_specs, n_total)
+    dev0 = trainer.to_device(probe_specs, host0, n_total)
+    probe_tokens = sum(sp.total_tokens for sp in probe_specs)
+    trainer.step_on_device(dev0)
+    t_off = timed_step(dev0)
+    like_for_like = {"policy": "no host offload (what every N runs when the shared host link is too slow)",
+                     "ms_per_step": round(t_off, 1), "tokens_per_s_per_gpu": round(probe_tokens / (t_off / 1e3), 1),
+                     "steps": 1}
     if args.offload != "off" and args.recompute == "auto" and args.lora_mode == "fused":
-        host0 = trainer.stage_batches(step_specs[0], 0)
-        dev0 = trainer.to_device(step_specs[0], host0, 0)
-        trainer.step_on_device(dev0)
-        t_off = timed_step(dev0)
-        ok = agree(trainer.stage.prepare_offload(args.capacity))
-        if ok:
-            trainer.step_on_device(dev0)
+        from lorafusion_b200.models.offload import measure_pcie_bandwidth
+
+        d2h, h2d = measure_pcie_bandwidth(device, dist.group.WORLD if world > 1 else None)
+        per_gu = args.capacity * 2 * cfg.intermediate_size * 2
+        fwd_s = (t_off / 1e3) / args.microbatches / 3.0   # a forward pass is about a third of fwd + bwd
+        n_link = int(0.9 * min(d2h, h2d) * fwd_s / per_gu)
+        offload_note = f"off (host link {d2h / 1e9:.1f} / {h2d / 1e9:.1f} GB/s out / in takes {n_link} layers per forward pass)"
+        if (n_link >= 6 or args.offload == "on") and agree(trainer.stage.prepare_offload(args.capacity, max_layers=n_link)):
             t_on = timed_step(dev0)
             n_off = trainer.stage.keep_summary(args.capacity)["gate_up_in_host_memory"]
             waits = trainer.stage._offloader.backlog_waits
-            offload_note = f"on, {n_off} layers (set-up step {t_on:.0f} ms vs {t_off:.0f} ms without, {waits} backlog waits)"
-            if args.offload == "auto" and not t_on < 0.99 * t_off:
-                ok = False
-                offload_note = f"off (set-up step {t_on:.0f} ms with {n_off} layers parked vs {t_off:.0f} ms without, {waits} backlog waits)"
-        if not ok:
+            detail = (f"{n_off} layers, host link {d2h / 1e9:.1f} / {h2d / 1e9:.1f} GB/s out / in under the load of "
+                      f"all ranks, set-up step {t_on:.0f} ms vs {t_off:.0f} ms without, {waits} backlog waits")
+            if args.offload == "on" or t_on < 0.995 * t_off:
+                offload_note = "on, " + detail
+            else:
+                offload_note = "off (tried " + detail + ")"
+                trainer.stage.disable_offload()
+                torch.cuda.empty_cache()
+        elif trainer.stage.offload_enabled:
             trainer.stage.disable_offload()
-            torch.cuda.empty_cache()
-        del dev0, host0
+    del dev0, host0
 
-    ms, toks, clocks, launches, loss_val, bytes_in = run_pass(e2e=False)
+    # ---- the timed pass: warm-up steps, then K steps end to end ----
+    host = [trainer.stage_batches(specs, s) for s, specs in enumerate(step_specs)]
+    last_loss = float("nan")
+    for s in range(args.warmup):
+        last_loss = trainer.train_step(step_specs[s], s, host=host[s])
+    barrier()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    launches0 = _native.launch_count()
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(2)] for _ in range(args.steps)]
+    ev_begin, ev_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    bytes_in = 0
+    ev_begin.record()
+    for k, s in enumerate(range(args.warmup, n_total)):
+        batches = trainer.to_device(step_specs[s], host[s], s)     # host -> device, from pinned memory
+        ev[k][0].record()
+        loss_dev = trainer.step_on_device(batches)
+        ev[k][1].record()
+        last_loss = float(loss_dev.item())                          # device -> host, 4 bytes
+        if k == 0:
+            bytes_in = sum(h2d_bytes(b) for b in batches)
+        del batches
+    ev_end.record()
+    barrier()
+    clocks = sampler.stop()
+    launches = _native.launch_count() - launches0
+    ms_e2e = ev_begin.elapsed_time(ev_end)
+    ms = sum(a.elapsed_time(b) for a, b in ev)
+    toks = float(sum(tokens_per_step[args.warmup:]))
+    stats = torch.tensor([ms, ms_e2e, toks], dtype=torch.float64, device=device)
+    if world > 1:
+        mx = stats.clone()
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        sm = stats.clone()
+        dist.all_reduce(sm, op=dist.ReduceOp.SUM)
+        ms, ms_e2e, toks = float(mx[0]), float(mx[1]), float(sm[2])
+    _native.check_device_errors()
+    loss_val = last_loss
     value = toks / (ms / 1e3)
     result = {
         "metric": "training tokens/s, multi-LoRA Llama-3.1-70B, 1/2/4/8 B200, max over ranks",
@@ -328,6 +348,10 @@ def main():
             "baseline": "vs_baseline = value / (n_gpus * 1278.85 tok/s/GPU), the reference's published "
                         "70B-mixed LoRAFusion throughput on 4xH100 per GPU",
             "tokens_per_step_per_gpu": tokens_per_step[-1],
+            "batches": "solver-packed per step for the whole dp group, dealt by sum(len^2) "
+                       "(train.data.pack_balanced_dp_step)",
+            "balance": balance,
+            "same_policy_at_every_n": like_for_like,
             "final_loss": loss_val,
             "peak_memory_gib": {"allocated": round(torch.cuda.max_memory_allocated() / 2**30, 1),
                                 "reserved": round(torch.cuda.max_memory_reserved() / 2**30, 1)},
@@ -335,17 +359,16 @@ def main():
         "clocks": clocks,
         "gpu_launches": launches,
     }
-    if not args.skip_e2e:
-        ms2, toks2, clocks2, launches2, loss2, bytes_in2 = run_pass(e2e=True)
-        result["e2e"] = {
-            "value": toks2 / (ms2 / 1e3),
-            "unit": "tokens/s",
-            "h2d_bytes_per_step": bytes_in2,
-            "d2h_bytes_per_step": 4,
-            "ms_per_step": ms2 / args.steps,
-            "clocks": clocks2,
-            "final_loss": loss2,
-        }
+    result["e2e"] = {
+        "value": toks / (ms_e2e / 1e3),
+        "unit": "tokens/s",
+        "h2d_bytes_per_step": bytes_in,
+        "d2h_bytes_per_step": 4,
+        "ms_per_step": ms_e2e / args.steps,
+        "note": "same K steps as value: one event pair around the whole pass (host-to-device copy of every "
+                "step's token arrays from pinned memory, compute, loss read back to the host every step); "
+                "value sums the compute intervals inside it",
+    }
     if rank == 0:
         print(json.dumps(result))
     if world > 1:

@@ -110,7 +110,7 @@ class DecoderStage:
                  layer_start: int = 0, layer_end: Optional[int] = None, quantize: bool = False,
                  double_quant: bool = True, init_std: float = 0.02, init_b_std: float = 0.0,
                  seed: int = 0, recompute=True, with_optimizer_state: bool = True,
-                 head_chunk_tokens: int = 2048, max_inflight: int = 1, reserve_bytes: int = 24 << 30,
+                 head_chunk_tokens: int = 2048, max_inflight: int = 1, reserve_bytes: int = 12 << 30,
                  shared_alloc=None):
         self.cfg = cfg
         self.device = torch.device(device)
@@ -128,6 +128,7 @@ class DecoderStage:
         self.force_keep_modes: Optional[list] = None  # tests / experiments: per-layer keep mode
         self.offload_enabled = False      # park gate|up outputs in pinned host memory
         self.offload_host_budget: Optional[int] = None  # bytes; None = share of MemAvailable
+        self.offload_max_layers: Optional[int] = None   # what the PCIe link drains during one forward
         self._offloader = None
         self.head_chunk_tokens = head_chunk_tokens
         self.training = True
@@ -279,19 +280,39 @@ class DecoderStage:
         return tokens * (c.qkv_size + c.q_size + c.hidden_size + 2 * c.intermediate_size) * 2 \
             + c.num_heads * tokens * 4 + tokens * 4 * 256 * 2
 
+    def working_set_bytes(self, tokens: int) -> int:
+        """Transient device memory next to the kept activations, at its peak: the backward of
+        a layer that re-runs gate|up (that output, the SwiGLU result, and both their gradients
+        are alive around the SwiGLU backward), a handful of hidden-sized tensors, the q|k|v
+        gradient, one chunk of logits of the loss head, and the bf16 scratch the NF4 weights are
+        expanded into (allocated at the first use of each weight shape)."""
+        c = self.cfg
+        per_gu = tokens * 2 * c.intermediate_size * 2
+        hidden = tokens * c.hidden_size * 2
+        head = 2 * min(tokens, self.head_chunk_tokens) * c.vocab_size * 2 if self.is_last else 0
+        scratch = 0
+        if self.quantize:
+            scratch = 2 * (c.qkv_size * c.hidden_size + c.hidden_size * c.q_size
+                           + 3 * c.intermediate_size * c.hidden_size)
+        return 3 * per_gu + 10 * hidden + 3 * tokens * c.qkv_size * 2 + head + scratch
+
     def _plan_modes(self, tokens: int) -> list:
         """Per-layer keep mode for the forward pass.  ``recompute=True`` -> all ``False``
         (recompute the layer from its input), ``False`` -> all ``True`` (keep everything),
-        ``"auto"`` -> a memory plan over three levels, best value per byte first:
+        ``"auto"`` -> a memory plan over these levels, best value per byte first:
 
-        * ``"nogu"``  keep the GEMM / attention outputs except gate|up (the backward re-runs
+        * ``"nogu"``    keep the GEMM / attention outputs except gate|up (the backward re-runs
           that one GEMM plus two RMSNorms and SwiGLU): about half of the recomputation time
           for a third of the bytes;
-        * ``"cheap"`` also keep gate|up (only elementwise kernels are re-run);
-        * ``False``   keep nothing but the layer input.
+        * ``"cheap"``   also keep gate|up on the device (only elementwise kernels are re-run);
+        * ``"offload"`` like ``"cheap"``, with gate|up parked in pinned host memory;
+        * ``False``     keep nothing but the layer input.
 
-        As many layers as fit become ``"nogu"``; what memory is left upgrades trailing layers
-        to ``"cheap"``."""
+        As many layers as fit become ``"nogu"``.  The memory that is left keeps gate|up of the
+        LAST layers on the device (their backward comes first, so nothing has to travel).  With
+        offloading, gate|up of up to ``offload_max_layers`` of the remaining layers -- what the
+        PCIe link drains during one forward pass, spread evenly so that the copies never pile
+        up -- goes to host memory; only the rest re-runs the gate|up GEMM."""
         n = len(self.layers)
         if self.force_keep_modes is not None:
             return list(self.force_keep_modes)
@@ -309,31 +330,31 @@ class DecoderStage:
             per_gu = tokens * 2 * self.cfg.intermediate_size * 2
             per_part = per_full - per_gu
             h_in_all = n * tokens * self.cfg.hidden_size * 2
-            budget = max(0, free - self.reserve_bytes - 3 * per_full - h_in_all * self.max_inflight)
+            budget = max(0, free - self.reserve_bytes - self.working_set_bytes(tokens) - h_in_all * self.max_inflight)
             budget //= self.max_inflight
             offload = self.offload_enabled and self.max_inflight == 1
             if offload:
                 # copies still on their way out, and the ring of returning buffers unless it
                 # exists already (then it is no longer part of the free memory)
-                budget = max(0, budget - (4 + (3 if self._offloader is None else 0)) * per_gu)
+                from .offload import ActivationOffloader as _AO
+
+                budget = max(0, budget - (_AO.MAX_BACKLOG + (_AO.RING if self._offloader is None else 0)) * per_gu)
             n_part = int(min(n, budget // per_part))
             n_full = int(min(n_part, (budget - n_part * per_part) // per_gu))
             modes = [False] * (n - n_part) + ["nogu"] * (n_part - n_full) + ["cheap"] * n_full
             if offload:
-                # two layers out of three: the forward produces gate|up faster than PCIe drains
-                # it, so a denser pattern would pile the copies up in device memory
                 from .offload import default_host_budget_bytes
 
                 if self.offload_host_budget is None:  # fixed at the first plan: pinning shrinks MemAvailable
                     self.offload_host_budget = default_host_budget_bytes()
+                cand = [li for li in range(n) if modes[li] == "nogu"]
                 slots = int(self.offload_host_budget // _pinned_bytes(per_gu))
-                j = 0
-                for li in range(n):
-                    if modes[li] == "nogu":
-                        if j % 3 != 2 and slots > 0:
-                            modes[li] = "offload"
-                            slots -= 1
-                        j += 1
+                # without a measured link rate: two layers out of three (a forward pass
+                # produces gate|up about 1.5x faster than one PCIe 5 link drains it)
+                cap = self.offload_max_layers if self.offload_max_layers is not None else (2 * n + 2) // 3
+                take = max(0, min(len(cand), slots, cap))
+                for j in range(take):  # evenly spread over the candidates
+                    modes[cand[(j * len(cand)) // take]] = "offload"
             self._modes_plan, self._modes_tokens = modes, tokens
         return self._modes_plan
 
@@ -344,18 +365,23 @@ class DecoderStage:
         self._plan_modes(max_tokens)
         return self.keep_summary(max_tokens)
 
-    def set_offload(self, enabled: bool, host_budget_bytes: Optional[int] = None) -> None:
+    def set_offload(self, enabled: bool, host_budget_bytes: Optional[int] = None,
+                    max_layers: Optional[int] = None) -> None:
         """Allow the memory plan to park gate|up outputs in pinned host memory (single
         microbatch in flight only).  Clears the cached plan."""
         self.offload_enabled = bool(enabled)
         self.offload_host_budget = host_budget_bytes
+        self.offload_max_layers = max_layers
         self._modes_plan = None
 
-    def prepare_offload(self, tokens: int, host_budget_bytes: Optional[int] = None) -> bool:
+    def prepare_offload(self, tokens: int, host_budget_bytes: Optional[int] = None,
+                        max_layers: Optional[int] = None) -> bool:
         """Enable offloading for microbatches of up to ``tokens`` tokens and pin the host
-        memory now.  Returns False (offloading left disabled) when the plan has nothing to park
-        or the host refuses the pinned allocation."""
-        self.set_offload(True, host_budget_bytes)
+        memory now.  ``max_layers`` = how many layers' gate|up the device-to-host link can take
+        during one forward pass (measured link rate x forward time / bytes per layer).  Returns
+        False (offloading left disabled) when the plan has nothing to park or the host refuses
+        the pinned allocation."""
+        self.set_offload(True, host_budget_bytes, max_layers)
         keys = [li for li, m in enumerate(self._plan_modes(tokens)) if m == "offload"]
         if keys:
             try:

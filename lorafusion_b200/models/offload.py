@@ -53,8 +53,55 @@ class OffloadedTensor:
     done: torch.cuda.Event  # device->host copy finished
 
 
+def measure_pcie_bandwidth(device, group=None, nbytes: int = 1 << 30, repeats: int = 3) -> tuple[float, float]:
+    """``(device->host, host->device)`` bytes per second of this GPU's host link with both
+    directions busy at once -- and, when ``group`` is given, with every rank of the group doing
+    the same at the same time; the slowest rank's figures are returned on all of them.  GPUs of
+    one node share the host's memory bandwidth and often PCIe switches, so the rate a rank gets
+    alone says little about what it gets next to seven others."""
+    import torch.distributed as dist
+
+    device = torch.device(device)
+    dev_a = torch.empty(nbytes, dtype=torch.uint8, device=device)
+    dev_b = torch.empty(nbytes, dtype=torch.uint8, device=device)
+    host_a = torch.empty(nbytes, dtype=torch.uint8, pin_memory=True)
+    host_b = torch.empty(nbytes, dtype=torch.uint8, pin_memory=True)
+    s_out, s_in = torch.cuda.Stream(device), torch.cuda.Stream(device)
+
+    def one_round(n):
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+        with torch.cuda.stream(s_out):
+            ev[0].record(s_out)
+            for _ in range(n):
+                host_a.copy_(dev_a, non_blocking=True)
+            ev[1].record(s_out)
+        with torch.cuda.stream(s_in):
+            ev[2].record(s_in)
+            for _ in range(n):
+                dev_b.copy_(host_b, non_blocking=True)
+            ev[3].record(s_in)
+        torch.cuda.synchronize(device)
+        return ev[0].elapsed_time(ev[1]) / 1e3, ev[2].elapsed_time(ev[3]) / 1e3
+
+    one_round(1)  # first touch of the pinned pages
+    multi = group is not None and dist.is_initialized() and dist.get_world_size(group) > 1
+    if multi:
+        dist.barrier(group)
+    t_out, t_in = one_round(repeats)
+    rates = torch.tensor([repeats * nbytes / max(t_out, 1e-9), repeats * nbytes / max(t_in, 1e-9)],
+                         dtype=torch.float64, device=device)
+    if multi:
+        dist.all_reduce(rates, op=dist.ReduceOp.MIN, group=group)
+    del dev_a, dev_b, host_a, host_b
+    return float(rates[0]), float(rates[1])
+
+
 class ActivationOffloader:
-    def __init__(self, device, slot_numel: int, dtype=torch.bfloat16, ring: int = 3, max_backlog: int = 4):
+    RING = 3          # device buffers that returning copies land in
+    MAX_BACKLOG = 3   # tensors held on the device while their outgoing copy is in flight
+
+    def __init__(self, device, slot_numel: int, dtype=torch.bfloat16, ring: int = RING,
+                 max_backlog: int = MAX_BACKLOG):
         self.device = torch.device(device)
         self.slot_numel, self.dtype = int(slot_numel), dtype
         self.d2h = torch.cuda.Stream(self.device)

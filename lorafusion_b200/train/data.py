@@ -203,3 +203,58 @@ def pack_greedy(lengths_by_adapter: dict[int, list[int]], capacity: int) -> list
         if not placed:
             bins.append({a: [n]})
     return [MicroBatchSpec([(a, lens) for a, lens in sorted(b.items())]) for b in bins]
+
+
+def pack_balanced_dp_step(samples: Sequence[tuple], world: int, per_rank: int, capacity: int, *,
+                          time_limit: float = 0.1, slack: float = 0.04) -> tuple[list, list]:
+    """Microbatches of one data-parallel step: every rank gets ``per_rank`` nearly full
+    microbatches and about the same attention work.
+
+    ``samples`` = ``[(adapter, length)]``, the pool to draw from (it should hold a little more
+    than ``world * per_rank * capacity`` tokens).  Two stages:
+
+    1. Samples are dealt to ranks longest first, each to the rank with the smallest
+       ``sum(length^2)`` so far -- the causal-attention cost, the only part of a step that is
+       not linear in tokens -- among the ranks whose token budget (``per_rank * capacity``
+       plus ``slack``) still has room.  What fits nowhere is a leftover.
+    2. Each rank's samples are bin-packed into microbatches of at most ``capacity`` padded
+       tokens by the solver (fewest bins, then smallest leftover bin:
+       ``solver.schedule.solve_micro_milp_lexicographic``; with some thirty samples per rank
+       the branch and bound is exact).  The ``per_rank`` fullest bins are used, the samples
+       of any further bin are leftovers.
+
+    Returns ``(specs[rank][i], leftovers)``; leftovers go first into the next step's pool.
+    Independent random draws per rank, the alternative, make every step as slow as the rank
+    that happened to draw the longest sequences."""
+    from ..solver.schedule import solve_micro_milp_lexicographic
+
+    budget = int(per_rank * capacity * (1.0 + slack))
+    tokens, cost = [0] * world, [0] * world
+    sets: list = [[] for _ in range(world)]
+    leftovers = []
+    for i in sorted(range(len(samples)), key=lambda i: -samples[i][1]):
+        n = samples[i][1]
+        cands = [r for r in range(world) if tokens[r] + n <= budget]
+        if not cands:
+            leftovers.append(samples[i])
+            continue
+        r = min(cands, key=lambda r: (cost[r], tokens[r]))
+        sets[r].append(i)
+        tokens[r] += n
+        cost[r] += n * n
+    dealt = []
+    for r in range(world):
+        keyed = [(i, samples[i][0], samples[i][1]) for i in sets[r]]
+        bins, _ = solve_micro_milp_lexicographic(keyed, capacity, TILE, time_limit)
+        if len(bins) < per_rank:
+            raise ValueError(f"the pool fills only {len(bins)} microbatches on rank {r}, {per_rank} are needed")
+        bins.sort(key=lambda b: -sum(samples[i][1] for i in b))
+        leftovers += [samples[i] for b in bins[per_rank:] for i in b]
+        specs = []
+        for b in bins[:per_rank]:
+            per: dict = {}
+            for i in sorted(b):
+                per.setdefault(samples[i][0], []).append(samples[i][1])
+            specs.append(MicroBatchSpec(sorted(per.items())))
+        dealt.append(specs)
+    return dealt, leftovers
