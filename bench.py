@@ -64,6 +64,8 @@ def parse_args():
     ap.add_argument("--lora-mode", default="fused", choices=["fused", "unfused"],
                     help="unfused = same-GPU baseline: separate base GEMM + cuBLAS LoRA GEMMs + stored mask")
     ap.add_argument("--multimem", action="store_true", help="use NVLS multimem loads/stores in the fused sync")
+    ap.add_argument("--fsdp", action="store_true",
+                    help="baseline: base weights sharded over the GPUs and all-gathered per layer (ZeRO-3 style)")
     ap.add_argument("--seed", type=int, default=1234, help="seed of the synthetic sample lengths")
     return ap.parse_args()
 
@@ -191,7 +193,7 @@ def main():
     trainer = MultiLoRATrainer(cfg, adapters, device, quantize=not args.no_quantize,
                                recompute={'auto': 'auto', 'all': True, 'none': False}[args.recompute], optim=OptimizerConfig(lr=1e-4),
                                dp_group=dist.group.WORLD if world > 1 else None, seed=1234, init_b_std=0.01,
-                               grad_sync=args.grad_sync, use_multimem=args.multimem)
+                               grad_sync=args.grad_sync, use_multimem=args.multimem, use_fsdp=args.fsdp)
     if "expandable_segments:True" in os.environ.get("PYTORCH_CUDA_ALLOC_CONF", ""):
         trainer.stage.reserve_bytes = 8 << 30  # little fragmentation to provide for
     trainer.stage.plan_activations(args.capacity)
@@ -336,7 +338,7 @@ def main():
             "model": cfg.name + ("-nf4" if not args.no_quantize else "-bf16"),
             "global_batch": f"{args.microbatches} x {args.capacity}-token microbatches per GPU per step",
             "seq_len": "lognormal medians 256/512/1024/2048, sigma 0.5-0.8, clip [32,8192], packed",
-            "parallelism": f"dp{world}",
+            "parallelism": f"dp{world}" + (" + base sharded ZeRO-3 style (baseline)" if args.fsdp else ""),
             "adapters": "4 x LoRA r16 alpha32 dropout %.2f on q,k,v,o,gate,up,down" % args.dropout,
             "grad_sync": trainer.grad_sync,
             "lora_mode": args.lora_mode,

@@ -5,7 +5,12 @@
 For every ``K x N`` shape and token count it times, forward and forward+backward:
 ``Torch Linear`` (cuBLAS, no adapter), ``Torch LoRA`` (unfused: cuBLAS GEMMs + elementwise
 ops + torch dropout), ``FusedLoRA`` (one adapter) and ``FusedMultiLoRA-4x`` (four adapters
-sharing the microbatch).  Rows are written in the reference's CSV layout
+sharing the microbatch) -- and, with ``--reference-triton``, the reference's own Triton kernels
+compiled for this GPU and composed as the reference composes them
+(``cli/reference_kernels.py``; checked against fp32 math before they are timed).  Each arm
+runs inside an NVTX range of the reference's names (``RawLinear``, ``RawLoRA``, ``FusedLoRA``,
+``FusedMultiLoRA``, ``benchmarks_paper/bench_lora_kernels.py:323,398,466,610``) so that an
+Nsight capture can be filtered by arm.  Rows are written in the reference's CSV layout
 (``Shape, Torch LoRA, Torch Linear, FlashLoRA`` seconds with rows
 ``"[MxKxNxr] FWD|FWD+BWD"``, ``benchmarks_paper/bench_lora_kernels.py:899-936``) plus the
 multi-adapter column.  ``--profile-only fused_fwd`` runs just one variant a few times, which
@@ -22,7 +27,7 @@ import torch
 from ..ops import lora_kernels as lk
 from ..ops.batch_info import prepare_multi_lora_batch_info, single_adapter_batch_info
 from ..ops.lora import LoRAStack, lora_linear_backward, lora_linear_forward
-from ..utils.benchmark import benchmark, tabulate_2d_benchmark_results
+from ..utils.benchmark import benchmark, nvtx_range, tabulate_2d_benchmark_results
 
 
 def _stack(n, N, K, r, device):
@@ -128,6 +133,43 @@ def run_nf4_compare(args):
     return rows
 
 
+def reference_triton_arms(x, w, dy, a, b, M, K, N, args, mode, kw) -> dict:
+    """Times of the reference's kernels for one shape and pass, single adapter and four
+    adapters; ``{"ref_triton_error": message}`` when they cannot be imported or compiled."""
+    from . import reference_kernels as rk
+
+    try:
+        rk.load_reference(args.reference_path)
+        alpha, p, r = 2.0, args.dropout, args.rank
+        out = {}
+        if mode == "fwd":  # numerics once per shape, before any timing
+            errs = rk.check_single(x, w, a, b, dy, alpha, p)
+            out["ref_triton_max_abs_err"] = errs
+            if errs["y"] > 0.05 * max(errs["y_scale"], 1.0) or errs["dx"] > 0.05 * max(errs["dx_scale"], 1.0):
+                raise RuntimeError(f"reference kernels disagree with fp32 math: {errs}")
+        per = (M // 4 // 128) * 128
+        lens = [per] * 3 + [M - 3 * per]
+        info = rk.ref_multi_batch_info(lens, [r] * 4, [alpha] * 4, [p] * 4)
+        a4 = [(torch.randn(r, K, device=x.device) * 0.02).to(x.dtype) for _ in range(4)]
+        b4 = [(torch.randn(N, r, device=x.device) * 0.02).to(x.dtype) for _ in range(4)]
+
+        def single():
+            y, saved = rk.ref_lora_forward(x, w, a, b, alpha, p)
+            return y if mode == "fwd" else rk.ref_lora_backward(dy, w, a, b, alpha, p, saved)
+
+        def multi():
+            y, saved = rk.ref_multi_lora_forward(x, w, a4, b4, info)
+            return y if mode == "fwd" else rk.ref_multi_lora_backward(dy, w, a4, b4, info, saved)
+
+        with nvtx_range("RefTritonLoRA"):
+            out["ref_triton_lora_s"] = benchmark(single, **kw)
+        with nvtx_range("RefTritonMultiLoRA"):
+            out["ref_triton_multi_lora_4x_s"] = benchmark(multi, **kw)
+        return out
+    except Exception as e:  # noqa: BLE001 - foreign code: report, keep the other arms
+        return {"ref_triton_error": f"{type(e).__name__}: {str(e)[:400]}"}
+
+
 def run(args):
     if args.nf4_compare or args.profile_only == "nf4_fwd":
         return run_nf4_compare(args)
@@ -149,19 +191,32 @@ def run(args):
                     torch.cuda.synchronize()
                     return []
                 kw = dict(warmup=args.warmup, number=args.number, flush=True)
-                t_lin = benchmark(lambda: torch_linear(x, w, dy, mode), **kw)
-                t_tl = benchmark(lambda: torch_lora(x, w, dy, a, b, args.dropout, mode), **kw)
+                with nvtx_range("RawLinear"):
+                    t_lin = benchmark(lambda: torch_linear(x, w, dy, mode), **kw)
+                with nvtx_range("RawLoRA"):
+                    t_tl = benchmark(lambda: torch_lora(x, w, dy, a, b, args.dropout, mode), **kw)
                 f1 = fused_fwd if mode == "fwd" else fused_fwd_bwd
-                t_f1 = benchmark(lambda: f1(x, w, dy, stack1, info1), **kw)
-                t_f4 = benchmark(lambda: f1(x, w, dy, stack4, info4), **kw)
+                with nvtx_range("FusedLoRA"):
+                    t_f1 = benchmark(lambda: f1(x, w, dy, stack1, info1), **kw)
+                with nvtx_range("FusedMultiLoRA"):
+                    t_f4 = benchmark(lambda: f1(x, w, dy, stack4, info4), **kw)
                 flops = (2 if mode == "fwd" else 4) * M * K * N
-                results.append({"shape": f"[{M}x{K}x{N}x{args.rank}] {'FWD' if mode == 'fwd' else 'FWD+BWD'}",
-                                "torch_lora_s": t_tl, "torch_linear_s": t_lin, "fused_lora_s": t_f1,
-                                "fused_multi_lora_4x_s": t_f4, "speedup_vs_torch_lora": t_tl / t_f1,
-                                "fused_tflops": flops / t_f1 / 1e12, "linear_tflops": flops / t_lin / 1e12})
+                row = {"shape": f"[{M}x{K}x{N}x{args.rank}] {'FWD' if mode == 'fwd' else 'FWD+BWD'}",
+                       "torch_lora_s": t_tl, "torch_linear_s": t_lin, "fused_lora_s": t_f1,
+                       "fused_multi_lora_4x_s": t_f4, "speedup_vs_torch_lora": t_tl / t_f1,
+                       "fused_tflops": flops / t_f1 / 1e12, "linear_tflops": flops / t_lin / 1e12}
+                if args.reference_triton:
+                    row.update(reference_triton_arms(x, w, dy, a, b, M, K, N, args, mode, kw))
+                    if "ref_triton_lora_s" in row:
+                        row["speedup_vs_ref_triton"] = row["ref_triton_lora_s"] / t_f1
+                        row["multi_speedup_vs_ref_triton"] = row["ref_triton_multi_lora_4x_s"] / t_f4
+                results.append(row)
     rows = [r["shape"] for r in results]
     cols = ["Torch LoRA", "Torch Linear", "FlashLoRA", "MultiLoRA-4x"]
     vals = [[r["torch_lora_s"], r["torch_linear_s"], r["fused_lora_s"], r["fused_multi_lora_4x_s"]] for r in results]
+    if args.reference_triton and all("ref_triton_lora_s" in r for r in results):
+        cols += ["Ref-Triton LoRA", "Ref-Triton MultiLoRA-4x"]
+        vals = [v + [r["ref_triton_lora_s"], r["ref_triton_multi_lora_4x_s"]] for v, r in zip(vals, results)]
     print(tabulate_2d_benchmark_results(rows, cols, vals, fmt="{:.6f}", csv_path=args.csv, title="seconds"))
     for r in results:
         print(json.dumps(r))
@@ -182,6 +237,9 @@ def main(argv=None):
     ap.add_argument("--csv", default=None)
     ap.add_argument("--nf4-compare", action="store_true",
                     help="time the NF4 base GEMM: dequantise-to-scratch + bf16 kernel vs NF4 expanded in the main loop")
+    ap.add_argument("--reference-triton", action="store_true",
+                    help="also time the reference's own Triton kernels on this GPU (needs a copy of its package)")
+    ap.add_argument("--reference-path", default=None, help="directory that holds the reference's lorafusion package")
     ap.add_argument("--profile-only", default=None,
                     choices=["fused_fwd", "fused_fwd_bwd", "multi_fwd_bwd", "nf4_fwd"])
     run(ap.parse_args(argv))

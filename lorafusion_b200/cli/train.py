@@ -83,7 +83,7 @@ def _run(margs, targs, dargs, rank, world, device, health) -> dict:
     engine = EngineConfig(layout=f"dp{dp}pp{pp}tp{tp}", quantize=margs.load_in_4bit,
                           recompute=targs.recompute_mode(), grad_sync=targs.grad_sync,
                           capacity=targs.multi_lora_max_microbatch_tokens, seed=targs.seed, init_b_std=0.01,
-                          use_timers=targs.use_timers)
+                          use_timers=targs.use_timers, use_fsdp=targs.use_fsdp)
     optim = OptimizerConfig(targs.learning_rate, targs.adam_beta1, targs.adam_beta2, targs.adam_epsilon,
                             targs.weight_decay)
     t0 = time.time()

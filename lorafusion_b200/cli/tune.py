@@ -3,6 +3,10 @@ best choice per shape to a JSON file.
 
     python -m lorafusion_b200.cli.tune --shapes 8192x8192 8192x28672 --tokens 16384 --out results/tuning_results.json
 
+The winners are also merged into the launch-parameter table of this GPU
+(``ops/tile_config.py``, file ``lorafusion_b200/ops/tuned/<gpu name>.json`` unless ``--table``
+says otherwise), which the launchers read from then on.
+
 Counterpart of ``tools/tune_kernels.py`` (which sweeps Triton tile sizes / stages / warps,
 ``tune_kernels.py:96-133``).  The tcgen05 kernels have fixed 128-row tiles; what is swept
 here is the N tile (128 / 256), the L2 grouping of M tiles (``group_m``), the number of
@@ -60,6 +64,8 @@ def main(argv=None) -> list:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--number", type=int, default=10)
     ap.add_argument("--out", default="results/tuning_results.json")
+    ap.add_argument("--table", default=None, help="launch-parameter table to merge the winners into "
+                    "(default: the table of this GPU inside the package); 'none' = do not write")
     args = ap.parse_args(argv)
     results = []
     for shape in args.shapes:
@@ -70,6 +76,21 @@ def main(argv=None) -> list:
     nv.check_device_errors()
     Path(args.out).parent.mkdir(parents=True, exist_ok=True)
     Path(args.out).write_text(json.dumps(results, indent=1))
+    if args.table != "none":
+        from ..ops import tile_config as tc
+
+        entries = {}
+        for r in results:
+            M, K, N = (int(v) for v in r["shape"].split("x"))
+            # the single-CTA sweep varies bn; the launchers choose bn themselves (256-wide tiles go
+            # to the CTA-pair kernel), so only the scheduling parameters of the best 256 row are kept
+            for kernel, (m, k, n) in (("fwd", (M, K, N)), ("dx", (M, N, K)), ("dx_dropout", (M, N, K))):
+                rows = [x for x in r[kernel] if x["bn"] == 256] or r[kernel]
+                best = max(rows, key=lambda x: x["tflops"])
+                entries[tc.entry_key(kernel, m, k, n)] = {"group_m": best["group_m"],
+                                                          "max_ctas": best.get("max_ctas", 0),
+                                                          "tflops": round(best["tflops"], 1)}
+        print(f"launch-parameter table: {tc.write_table(entries, None if args.table is None else args.table)}")
     return results
 
 

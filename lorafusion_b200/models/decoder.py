@@ -149,12 +149,12 @@ class DecoderStage:
 
         self.layers: list[LayerWeights] = []
         for _ in range(self.layer_start, self.layer_end):
-            self.layers.append(LayerWeights(
+            self.layers.append(self._adopt_layer(len(self.layers), LayerWeights(
                 ln1=torch.ones(h, dtype=torch.bfloat16, device=self.device),
                 ln2=torch.ones(h, dtype=torch.bfloat16, device=self.device),
                 qkv=frozen(cfg.qkv_size, h), o=frozen(h, cfg.q_size),
                 gate_up=frozen(2 * i, h), down=frozen(h, i),
-                qkv_bias=rnd(cfg.qkv_size) if cfg.qkv_bias else None))
+                qkv_bias=rnd(cfg.qkv_size) if cfg.qkv_bias else None)))
         self.embed = rnd(cfg.vocab_size, h) if self.is_first else None
         self.final_norm = torch.ones(h, dtype=torch.bfloat16, device=self.device) if self.is_last else None
         self.lm_head = rnd(cfg.vocab_size, h) if self.is_last else None
@@ -163,6 +163,11 @@ class DecoderStage:
                                init_b_std=init_b_std, seed=seed,
                                with_optimizer_state=with_optimizer_state,
                                shared_alloc=shared_alloc) if self.adapters else None
+
+    def _adopt_layer(self, li: int, lw: LayerWeights) -> LayerWeights:
+        """Hook called with every freshly initialised layer; a subclass may replace the
+        weights by its own representation (e.g. a shard) before the next layer is created."""
+        return lw
 
     def adopt_weights(self, full: "DecoderStage") -> "DecoderStage":
         """Make this stage a slice of ``full`` (a stage covering at least the same layers):

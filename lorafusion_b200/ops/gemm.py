@@ -15,6 +15,7 @@ from typing import Optional
 import torch
 
 from . import _native as nv
+from .tile_config import get_kernel_config
 
 
 def _check2d(t: torch.Tensor, name: str) -> None:
@@ -67,11 +68,20 @@ def fill_gemm_args(
     stream_id: int = 0,
     row_offset: int = 0,
     col_offset: int = 0,
-    group_m: int = 8,
-    max_ctas: int = 0,
+    group_m: Optional[int] = None,
+    max_ctas: Optional[int] = None,
+    tuned: Optional[str] = None,
 ) -> nv.LfGemmArgs:
     """Describe one GEMM launch (operands, epilogue, dropout, scheduling) as a
-    :class:`LfGemmArgs` for the current stream."""
+    :class:`LfGemmArgs` for the current stream.  ``tuned`` names the kernel family of the
+    launch (``fwd`` / ``dx`` / ``dx_dropout``): scheduling parameters the caller leaves open are
+    then taken from the tuned table (``ops/tile_config.py``) for this GPU and shape."""
+    if tuned is not None and (group_m is None or max_ctas is None):
+        cfg = get_kernel_config(tuned, M, K, N)
+        group_m = cfg.group_m if group_m is None else group_m
+        max_ctas = cfg.max_ctas if max_ctas is None else max_ctas
+    group_m = 8 if group_m is None else group_m
+    max_ctas = 0 if max_ctas is None else max_ctas
     _check2d(a, "a")
     args = nv.LfGemmArgs()
     args.a, args.a_rows, args.a_cols, args.a_ld = a.data_ptr(), a.shape[0], a.shape[1], a.stride(0)

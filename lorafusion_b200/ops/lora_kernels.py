@@ -148,7 +148,7 @@ def base_lora_fwd(x: torch.Tensor, w: torch.Tensor, s: Optional[torch.Tensor],
         n, N2, R = b_all.shape
         assert N2 == N and s.shape == (M, R)
         kw = dict(a2=s, b2=_flat2d(b_all), K2=R, b2_adapter_rows=N, tile_adapter=tile_adapter)
-    launch_gemm(a=x, b=w, out=out, M=M, N=N, K=K, bn=256 if N >= 256 else 128, bias=bias, **kw)
+    launch_gemm(a=x, b=w, out=out, M=M, N=N, K=K, bn=256 if N >= 256 else 128, bias=bias, tuned="fwd", **kw)
     return out
 
 
@@ -210,8 +210,8 @@ def base_lora_dx(dy: torch.Tensor, w: torch.Tensor, ds: Optional[torch.Tensor],
     if ds is not None and dropout.active:
         launch_gemm(a=dy, b=w, out=out, M=M, N=K, K=N, b_mn=True, b2_mn=True,
                     bn=DROPMIX_BN if K >= 256 else 128, nacc=2,
-                    epi=nv.EPI_BF16_DROPMIX, **kw, **dropout.kwargs())
+                    epi=nv.EPI_BF16_DROPMIX, tuned="dx_dropout", **kw, **dropout.kwargs())
     else:
         launch_gemm(a=dy, b=w, out=out, M=M, N=K, K=N, b_mn=True, b2_mn=True,
-                    bn=256 if K >= 256 else 128, **kw)
+                    bn=256 if K >= 256 else 128, tuned="dx", **kw)
     return out

@@ -33,6 +33,7 @@ class EngineConfig:
     seed: int = 0
     init_b_std: float = 0.0
     use_timers: bool = False
+    use_fsdp: bool = False              # ZeRO-3 style baseline: base weights sharded over dp
 
 
 class ParallelTrainer:
@@ -72,9 +73,20 @@ class ParallelTrainer:
                   seed=engine.seed, init_b_std=engine.init_b_std, shared_alloc=alloc,
                   max_inflight=self.layout.pp - st.pp_rank)
         if self.layout.tp > 1:
+            if engine.use_fsdp:
+                raise ValueError("use_fsdp and tensor parallelism cannot be combined")
             from ..models.tp_decoder import TpDecoderStage
 
             self.stage = TpDecoderStage(cfg, adapters, self.device, st.tp_group, max_tokens=engine.capacity, **kw)
+        elif engine.use_fsdp:
+            if self.layout.pp > 1:
+                raise ValueError("use_fsdp shards the base over the data-parallel group of an unpartitioned model: "
+                                 "pipeline_parallel_size must be 1 (the reference's FSDP arm has no pipeline either)")
+            from ..models.fsdp_decoder import FsdpDecoderStage
+
+            self.stage = FsdpDecoderStage(cfg, adapters, self.device, st.dp_group if self.layout.dp > 1 else None, **kw)
+            if engine.recompute == "auto":
+                self.stage.plan_activations(engine.capacity)
         else:
             self.stage = DecoderStage(cfg, adapters, self.device, **kw)
             if engine.recompute == "auto":

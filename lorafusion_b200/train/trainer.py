@@ -18,6 +18,7 @@ import torch.distributed as dist
 
 from ..models.config import AdapterSpec, ModelConfig
 from ..models.decoder import DecoderStage, PackedBatch
+from ..utils.benchmark import nvtx_range
 from .data import MicroBatchSpec, build_packed_batch, stage_host_batch
 
 
@@ -34,7 +35,9 @@ class MultiLoRATrainer:
     def __init__(self, cfg: ModelConfig, adapters: Sequence[AdapterSpec], device, *,
                  quantize: bool = False, recompute=True, optim: Optional[OptimizerConfig] = None,
                  dp_group=None, seed: int = 0, init_b_std: float = 0.0, grad_sync: str = "auto",
-                 use_multimem: bool = False):
+                 use_multimem: bool = False, use_fsdp: bool = False):
+        """``use_fsdp``: ZeRO-3 style baseline -- the frozen base is sharded over the data-parallel
+        group and gathered layer by layer (``models/fsdp_decoder.py``)."""
         self.cfg = cfg
         self.adapters = list(adapters)
         self.device = torch.device(device)
@@ -50,8 +53,13 @@ class MultiLoRATrainer:
             from ..parallel.symmetric import SymmetricAllocator
 
             alloc = SymmetricAllocator(self.device, dp_group)
-        self.stage = DecoderStage(cfg, adapters, device, quantize=quantize, recompute=recompute, seed=seed,
-                                  init_b_std=init_b_std, shared_alloc=alloc)
+        kw = dict(quantize=quantize, recompute=recompute, seed=seed, init_b_std=init_b_std, shared_alloc=alloc)
+        if use_fsdp:
+            from ..models.fsdp_decoder import FsdpDecoderStage
+
+            self.stage = FsdpDecoderStage(cfg, adapters, device, dp_group if self.dp_size > 1 else None, **kw)
+        else:
+            self.stage = DecoderStage(cfg, adapters, device, **kw)
         self.step_count = 0
         self._fused_sync = None
         if self.grad_sync == "fused" and self.stage.arena is not None:
@@ -76,10 +84,12 @@ class MultiLoRATrainer:
         loss_sum = None
         n_tok = 0
         for b in batches:
-            ls = self.stage.forward_backward(b)
+            with nvtx_range("Forward+Backward"):
+                ls = self.stage.forward_backward(b)
             loss_sum = ls if loss_sum is None else loss_sum + ls
             n_tok += b.num_loss_tokens
-        self.reduce_and_step(len(batches), active_adapters)
+        with nvtx_range("Gradient sync + optimizer step"):
+            self.reduce_and_step(len(batches), active_adapters)
         self.step_count += 1
         return loss_sum / max(n_tok, 1)
 

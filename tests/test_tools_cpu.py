@@ -73,3 +73,23 @@ def test_summarize_ncu_tables(tmp_path):
                         '"2","a(int)","gpu__time_duration.sum","ns","1000000"\n')
     text = summarize_ncu.main([str(launches), "--launches"])
     assert "Total 5.0 ms over 3 launches" in text and "| `a` | 2 | 4.000 | 80.0 % |" in text
+
+
+def test_tile_config_registry_round_trip(tmp_path, monkeypatch):
+    """What the tuner writes is what the launchers read; unknown shapes fall back to defaults."""
+    from lorafusion_b200.ops import tile_config as tc
+
+    path = tmp_path / "table.json"
+    tc.write_table({tc.entry_key("fwd", 16000, 8192, 28672): {"group_m": 16, "max_ctas": 132, "tflops": 1400.0}},
+                   path, gpu="test-gpu")
+    monkeypatch.setenv("LORAFUSION_B200_TUNING", str(path))
+    tc.reload()
+    got = tc.get_kernel_config("fwd", 16384, 8192, 28672)          # same power-of-two bucket as 16000
+    assert (got.group_m, got.max_ctas, got.source) == (16, 132, str(path))
+    assert tc.get_kernel_config("fwd", 4096, 8192, 28672) == tc.DEFAULTS["fwd"]
+    assert tc.get_kernel_config("dx", 16384, 8192, 28672).group_m == 8
+    tc.write_table({tc.entry_key("dx", 16384, 28672, 8192): {"group_m": 4, "max_ctas": 0}}, path, gpu="test-gpu")
+    assert tc.get_kernel_config("dx", 16384, 28672, 8192).group_m == 4
+    assert tc.get_kernel_config("fwd", 16384, 8192, 28672).group_m == 16   # merged, not replaced
+    monkeypatch.delenv("LORAFUSION_B200_TUNING")
+    tc.reload()
