@@ -91,12 +91,61 @@ class TpContext:
             torch.cuda.synchronize(self.device)
             dist.barrier(group)
 
+    # ---- one-GPU loop-back: run the copy / reduce warps without a second GPU ----------------
+    @classmethod
+    def loopback(cls, device, *, world: int = 2, max_tokens: int, max_features: int,
+                 max_rank_width: int = 256) -> "TpContext":
+        """A context that makes ONE GPU act as rank 0 of ``world`` ranks: every peer pointer
+        leads back to this GPU's own memory.  The kernels then run their communication warps for
+        real -- shard pushes, flag raises, flag waits, peer pulls -- over local addresses, which
+        is how they are tested and profiled where only one GPU is at hand.  The part of the
+        other ranks is played by the host BEFORE each launch (:meth:`loopback_arm_gather`,
+        :meth:`loopback_arm_reduce`): it puts their data in place and raises their flags, so the
+        kernel never waits for anything that is not already there."""
+        self = cls(None, device, max_tokens=max_tokens * 1, max_features=max_features, max_rank_width=max_rank_width)
+        if max_tokens % (TILE * world):
+            raise ValueError("token count must be a multiple of 128 * world")
+        self.world, self.rank, self.is_loopback = world, 0, True
+        dev = self.device
+        n_flags = world * (max_tokens // TILE)
+        self.n_flags = n_flags
+        self.ag_flags = local_buffer(n_flags + max_tokens // TILE, torch.int32, dev)
+        self.rs_cnt = local_buffer(n_flags * ((max_features + 255) // 256), torch.int32, dev)
+        # pushes of the own shard land on the own rows again; flags raised "at the peers" land in
+        # the own flag array, in this rank's slots
+        self.gather.peer_ptrs = [self.gather.tensor.data_ptr()] * world
+        self.gather2.peer_ptrs = [self.gather2.tensor.data_ptr()] * world
+        self.ag_flags.peer_ptrs = [self.ag_flags.tensor.data_ptr()] * world
+        # partial tiles of the other ranks come from stand-in stages the host fills; completion
+        # flags for rows owned by other ranks go to a scratch array nobody reads
+        self.peer_stages = [self.rs_stage.tensor] + [torch.zeros_like(self.rs_stage.tensor) for _ in range(world - 1)]
+        self.rs_stage.peer_ptrs = [t.data_ptr() for t in self.peer_stages]
+        self._rs_scratch = torch.zeros_like(self.rs_cnt.tensor)
+        self.rs_cnt.peer_ptrs = [self.rs_cnt.tensor.data_ptr()] + [self._rs_scratch.data_ptr()] * (world - 1)
+        return self
+
+    def loopback_arm_gather(self, tokens: int) -> None:
+        """Before an ``ag_gemm`` in loop-back mode: the rows of the other ranks are already in the
+        gather buffers (the caller wrote them); raise their flags for the coming call."""
+        tps = tokens // self.world // TILE
+        self.ag_flags.tensor[tps:self.world * tps] = self.epoch + 1
+
+    def loopback_arm_reduce(self, tokens: int, n: int, partials: list) -> None:
+        """Before a ``gemm_rs`` in loop-back mode: ``partials[r - 1]`` = the ``[tokens, n]`` partial
+        product rank ``r`` would have left in its stage; raise those ranks' completion flags for
+        the rows this rank owns."""
+        tps = tokens // self.world // TILE
+        nnt = (n + 255) // 256
+        for r, part in enumerate(partials, start=1):
+            self.peer_stages[r][:tokens * n].view(tokens, n).copy_(part)
+        self.rs_cnt.tensor[tps * nnt:self.world * tps * nnt] = self.epoch + 1
+
     def order(self, mode: int) -> None:
         """The reuse argument for the gather / stage buffers needs all-gather and
         reduce-scatter uses to alternate.  When the same kind is requested twice in a row
         (e.g. the last backward op of one microbatch and the first forward op of the next are
         both all-gathers) a one-word all-reduce orders the ranks in between."""
-        if self.world > 1 and mode == self._last_mode:
+        if self.world > 1 and mode == self._last_mode and not getattr(self, "is_loopback", False):
             dist.all_reduce(self._fence_word, group=self.group)
         self._last_mode = mode
 

@@ -204,3 +204,53 @@ def test_tp_stage_matches_unpartitioned_stage(tmp_path):
     outs = [p.communicate(timeout=600)[0] for p in procs]
     for r, (p, o) in enumerate(zip(procs, outs)):
         assert p.returncode == 0, f"rank {r} failed:\n{o[-4000:]}"
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_loopback_runs_the_copy_and_reduce_warps_on_one_gpu(world):
+    """One GPU plays rank 0 of ``world``: peer pointers lead back to its own memory, the host
+    plays the other ranks before each launch (data in place, flags raised).  The shard-push
+    warps, the flag waits of the TMA producer, the partial-tile flags of the epilogue and the
+    pulling reduce warps all run; results are checked against fp32 math."""
+    from lorafusion_b200.ops import _native
+    from lorafusion_b200.parallel.tp_ops import TpContext, ag_gemm, gemm_rs
+    from lorafusion_b200.utils.testing import assert_close_two_rounds
+
+    torch.backends.cuda.matmul.allow_tf32 = False
+    dev = "cuda"
+    T_MAX, K, N, R = 1024, 768, 1280, 64
+    ctx = TpContext.loopback(dev, world=world, max_tokens=T_MAX, max_features=2048)
+
+    def rnd(*shape, scale=1.0, seed=0):
+        g = torch.Generator(device=dev).manual_seed(seed)
+        return (torch.randn(*shape, generator=g, device=dev) * scale).to(torch.bfloat16)
+
+    for it, T in enumerate([1024, 512, 1024]):   # sizes change: the same flag words are reused under new epochs
+        ms = T // world
+        # ---- all-gather -> GEMM (+ LoRA slab): the whole [T, K] operand sits in the gather buffer,
+        # rows [0, ms) are "ours" (pushed by the copy warps), the rest arrived "from the peers"
+        x_full, s_full = rnd(T, K, seed=10 + it), rnd(T, R, scale=0.1, seed=20 + it)
+        w, b2 = rnd(N, K, scale=0.05, seed=30 + it), rnd(1, N, R, scale=0.05, seed=40 + it)
+        ctx.gather_view(T, K).copy_(x_full)
+        ctx.gather2_view(T, R).copy_(s_full)
+        ctx.loopback_arm_gather(T)
+        y = ag_gemm(ctx, T, K, w, slab_cols=R, b2=b2, b2_adapter_rows=N)
+        torch.cuda.synchronize()
+        _native.check_device_errors()
+        assert_close_two_rounds(y, x_full.float() @ w.float().t() + s_full.float() @ b2[0].float().t(),
+                                msg=f"loop-back ag_gemm it{it}")
+        tps = ms // 128
+        assert bool((ctx.ag_flags.tensor[:tps] == ctx.epoch).all())      # our tiles were flagged "at the peers"
+        assert torch.equal(ctx.gather_view(T, K), x_full)                 # the self-push left the data intact
+
+        # ---- GEMM -> reduce-scatter (+ slab, + residual): our partial plus the peers' stand-ins
+        xa, wa = rnd(T, K, seed=50 + it), rnd(N, K, scale=0.05, seed=60 + it)
+        sa, res = rnd(T, R, scale=0.1, seed=70 + it), rnd(ms, N, seed=80 + it)
+        others = [rnd(T, N, seed=90 + 10 * it + r) for r in range(1, world)]
+        ctx.loopback_arm_reduce(T, N, others)
+        out = gemm_rs(ctx, xa, wa, s=sa, b2=b2, b2_adapter_rows=N, residual=res)
+        torch.cuda.synchronize()
+        _native.check_device_errors()
+        mine = (xa.float() @ wa.float().t() + sa.float() @ b2[0].float().t()).to(torch.bfloat16).float()
+        ref = mine[:ms] + sum(o.float()[:ms] for o in others) + res.float()
+        assert_close_two_rounds(out, ref, atol=2e-2, msg=f"loop-back gemm_rs it{it}")
