@@ -1,0 +1,9 @@
+#!/usr/bin/env bash
+# llama-3.1-70b, four adapters on the "het" length profile(s), solver schedule and mLoRA-style
+# schedule; counterpart of the reference's scripts/main/3_5_70b_4h100_het.sh.
+set -euo pipefail
+cd "$(dirname "$0")/../.."
+for SCHEDULE in solver mlora; do
+  NGPU=8 MODEL=llama-3.1-70b QUANT=true PP=2 TP=4 ADAPTERS=4 RANKS=16 GBS="16 16 16 16" DATASETS="short medium long xlong" \
+    SCHEDULE=$SCHEDULE OUT=outputs/main/70b_het_$SCHEDULE benchmarks/run_single.sh
+done

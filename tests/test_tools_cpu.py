@@ -93,3 +93,26 @@ def test_tile_config_registry_round_trip(tmp_path, monkeypatch):
     assert tc.get_kernel_config("fwd", 16384, 8192, 28672).group_m == 16   # merged, not replaced
     monkeypatch.delenv("LORAFUSION_B200_TUNING")
     tc.reload()
+
+
+def test_figure_drivers_draw_published_and_measured_data(tmp_path):
+    import json
+
+    from lorafusion_b200.cli import figures
+
+    for name, n in (("end-to-end", 3), ("scaling", 1), ("kernel-dram", 1)):
+        paths = figures.main([name, "--demo", "--out", str(tmp_path)])
+        assert len(paths) == n and all(p.read_text().lstrip().startswith("<svg") for p in paths)
+    (tmp_path / "scale.json").write_text(json.dumps({"scaling": {"values": {"1": 2800.0, "2": 5400.0, "8": 21000.0}}}))
+    p, = figures.main(["scaling", "--results", str(tmp_path / "scale.json"), "--out", str(tmp_path)])
+    assert "this framework" in p.read_text()
+    rows = [{"shape": f"[{m}x4096x4096x16] FWD", "torch_lora_s": 3e-4 * m / 4096, "torch_linear_s": 2e-4 * m / 4096,
+             "fused_lora_s": 2.5e-4 * m / 4096, "fused_multi_lora_4x_s": 2.6e-4 * m / 4096} for m in (4096, 8192)]
+    (tmp_path / "k.jsonl").write_text("\n".join(json.dumps(r) for r in rows))
+    p, = figures.main(["kernel-perf", "--results", str(tmp_path / "k.jsonl"), "--out", str(tmp_path)])
+    assert "FusedLoRA" in p.read_text() and "Reference Triton" not in p.read_text()
+    layer = [{"Mode": "FusedLoRA", "Model": "llama-3.1-8b", "BatchSize": b, "SeqLength": 1024, "NumAdapters": 1,
+              "TimeMs": 5.0 * b, "ThroughputTokensPerSec": 1.0} for b in (4, 8)]
+    (tmp_path / "l.jsonl").write_text("\n".join(json.dumps(r) for r in layer))
+    p, = figures.main(["layer-perf", "--results", str(tmp_path / "l.jsonl"), "--out", str(tmp_path)])
+    assert "llama-3.1-8b" in p.read_text()
