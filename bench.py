@@ -195,7 +195,7 @@ def main():
                                dp_group=dist.group.WORLD if world > 1 else None, seed=1234, init_b_std=0.01,
                                grad_sync=args.grad_sync, use_multimem=args.multimem, use_fsdp=args.fsdp)
     if "expandable_segments:True" in os.environ.get("PYTORCH_CUDA_ALLOC_CONF", ""):
-        trainer.stage.reserve_bytes = 8 << 30  # little fragmentation to provide for
+        trainer.stage.reserve_bytes = 5 << 30  # little fragmentation to provide for
     trainer.stage.plan_activations(args.capacity)
     torch.cuda.synchronize()
     if rank == 0:
@@ -263,7 +263,8 @@ def main():
         d2h, h2d = measure_pcie_bandwidth(device, dist.group.WORLD if world > 1 else None)
         per_gu = args.capacity * 2 * cfg.intermediate_size * 2
         fwd_s = (t_off / 1e3) / args.microbatches / 3.0   # a forward pass is about a third of fwd + bwd
-        n_link = int(0.9 * min(d2h, h2d) * fwd_s / per_gu)
+        # the forward pass sends, the (twice as long) backward pass fetches
+        n_link = int(0.9 * min(d2h * fwd_s, h2d * 2.0 * fwd_s) / per_gu)
         offload_note = f"off (host link {d2h / 1e9:.1f} / {h2d / 1e9:.1f} GB/s out / in takes {n_link} layers per forward pass)"
         if (n_link >= 6 or args.offload == "on") and agree(trainer.stage.prepare_offload(args.capacity, max_layers=n_link)):
             t_on = timed_step(dev0)

@@ -176,6 +176,7 @@ class LoRAArena:
         """Lay out every adapter's regions and assign its dense optimizer-state offsets.
         Adapter ``i`` owns the contiguous state range ``state_range[i]``."""
         self._chunk_rows: dict[int, list] = {}
+        self._chunk_layers: dict[int, list] = {}   # layer of every chunk row (rows are layer-major)
         self.state_offsets: dict[tuple, tuple[int, int]] = {}
         self.state_range: dict[int, tuple[int, int]] = {}
         state = 0
@@ -188,8 +189,10 @@ class LoRAArena:
 
         for adapter in range(self.num_adapters):
             rows = []
+            row_layers: list = []
             lo = state
             for v in self.views.values():
+                n_before = len(rows)
                 a_base = v.a_offset + adapter * v.R * v.K
                 b_base = v.b_offset + adapter * v.N * v.R
                 a_state = {}
@@ -214,9 +217,11 @@ class LoRAArena:
                     else:
                         rows.append((b_base + n0 * v.R, size, v.R, 0, 0, 0))
                     n0 += size
+                row_layers += [v.layer] * (len(rows) - n_before)
             if any(r[1] * r[2] >= 2 ** 31 for r in rows):
                 raise ValueError("an adapter region of 2^31 elements or more is not supported by the optimizer kernels")
             self._chunk_rows[adapter] = rows
+            self._chunk_layers[adapter] = row_layers
             self.state_range[adapter] = (lo, state)
         self.state_numel = max(state, 4)
 
@@ -230,16 +235,24 @@ class LoRAArena:
             self._chunks[adapter] = t
         return t
 
-    def work_items(self, adapter: int, rank: int = 0, world: int = 1) -> torch.Tensor:
+    def work_items(self, adapter: int, rank: int = 0, world: int = 1,
+                   layers: Optional[tuple] = None) -> torch.Tensor:
         """Device table of equal-sized pieces of ``adapter``'s regions for the optimizer
         kernels (``ops.elementwise.build_adam_work_items``); slice ``rank`` of ``world`` for the
-        fused data-parallel kernel."""
+        fused data-parallel kernel.  ``layers = (lo, hi)`` restricts the table to the regions of
+        layers ``lo <= l < hi`` (the gradient sync of a layer group can start as soon as the
+        last backward has passed those layers)."""
         from ..ops.elementwise import build_adam_work_items
 
-        key = (adapter, rank, world)
+        key = (adapter, rank, world, layers)
         t = self._work_items.get(key)
         if t is None:
-            t = build_adam_work_items(self._chunk_rows[adapter], rank=rank, world=world).to(self.device)
+            t = build_adam_work_items(self._chunk_rows[adapter], rank=rank, world=world)
+            if layers is not None:
+                lay = torch.tensor(self._chunk_layers[adapter], dtype=torch.int64)
+                keep = (lay[t[:, 0].long()] >= layers[0]) & (lay[t[:, 0].long()] < layers[1])
+                t = t[keep].contiguous()
+            t = t.to(self.device)
             self._work_items[key] = t
         return t
 

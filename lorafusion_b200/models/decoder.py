@@ -489,17 +489,20 @@ class DecoderStage:
         dh = ew.rmsnorm_bwd(dx, h_fin, self.final_norm, rstd)
         return losses.sum(), dh
 
-    def backward(self, saved: list, dh: torch.Tensor, batch: PackedBatch) -> Optional[torch.Tensor]:
+    def backward(self, saved: list, dh: torch.Tensor, batch: PackedBatch,
+                 on_layer_done=None) -> Optional[torch.Tensor]:
         """Back-propagate ``dh`` (gradient w.r.t. this stage's output) through the layers;
         LoRA gradients accumulate in the arena.  Returns the gradient w.r.t. the stage input
-        (``None`` on the first stage, whose input is the frozen embedding)."""
+        (``None`` on the first stage, whose input is the frozen embedding).
+        ``on_layer_done(global layer index)`` is called right after the backward of each layer
+        has been queued: from then on that layer's LoRA gradients of this microbatch are final."""
         # gate|up outputs parked in host memory come back two layers ahead of their use
         parked = [li for li in reversed(range(len(self.layers)))
                   if saved[li].full is not None and "gu_off" in saved[li].full]
         inflight: dict = {}
 
         def fetch_ahead():
-            while parked and len(inflight) < 2:
+            while parked and len(inflight) < max(1, len(self._offloader.ring) - 1):
                 nxt = parked.pop(0)
                 inflight[nxt] = self._offloader.prefetch(saved[nxt].full["gu_off"])
 
@@ -516,14 +519,16 @@ class DecoderStage:
             if slot is not None:
                 self._offloader.release(slot)
             saved[li] = None
+            if on_layer_done is not None:
+                on_layer_done(self.layer_start + li)
         return dh
 
-    def forward_backward(self, batch: PackedBatch, loss_scale: float = 1.0) -> torch.Tensor:
+    def forward_backward(self, batch: PackedBatch, loss_scale: float = 1.0, on_layer_done=None) -> torch.Tensor:
         """Whole-model step for an unpartitioned model: returns the summed token loss."""
         if not (self.is_first and self.is_last):
             raise RuntimeError("forward_backward needs the whole model on this stage")
         out, saved = self.forward(batch)
         loss, dh = self.loss_and_grad(out, batch, loss_scale)
         del out
-        self.backward(saved, dh, batch)
+        self.backward(saved, dh, batch, on_layer_done=on_layer_done)
         return loss

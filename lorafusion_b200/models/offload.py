@@ -97,8 +97,8 @@ def measure_pcie_bandwidth(device, group=None, nbytes: int = 1 << 30, repeats: i
 
 
 class ActivationOffloader:
-    RING = 3          # device buffers that returning copies land in
-    MAX_BACKLOG = 3   # tensors held on the device while their outgoing copy is in flight
+    RING = 2          # device buffers that returning copies land in (one in use, one arriving)
+    MAX_BACKLOG = 2   # tensors held on the device while their outgoing copy is in flight
 
     def __init__(self, device, slot_numel: int, dtype=torch.bfloat16, ring: int = RING,
                  max_backlog: int = MAX_BACKLOG):

@@ -102,16 +102,32 @@ class FusedGradSync:
             torch.cuda.synchronize(dev)
             dist.barrier(group)  # flags are zeroed everywhere before the first kernel
 
-    def reduce_and_step(self, adapter: int, grad_scale: float) -> None:
+    def begin_step(self, adapter: int) -> int:
+        """Count one optimizer step of ``adapter`` (once per step, however many layer groups the
+        step is launched in) and return its number."""
+        self.arena.steps[adapter] += 1
+        return self.arena.steps[adapter]
+
+    def reduce_and_step(self, adapter: int, grad_scale: float, *, layers: Optional[tuple] = None,
+                        step: Optional[int] = None) -> None:
+        """Launch the fused kernel for ``adapter`` on the current stream.  ``layers = (lo, hi)``
+        limits it to the regions of those layers, with ``step`` from :meth:`begin_step`; every
+        rank must launch the same sequence of groups."""
         o, ar = self.optim, self.arena
-        ar.steps[adapter] += 1
+        if step is None:
+            step = self.begin_step(adapter)
+        items = ar.work_items(adapter, self.rank, self.world, layers=layers)
+        if items.shape[0] == 0:
+            if self.world == 1:
+                return
+            raise RuntimeError("this rank owns no part of the requested layer group; the ranks would fall out of step")
         self.epoch += 1
         launch_allreduce_adam(
-            chunks=ar.chunk_table(adapter), items=ar.work_items(adapter, self.rank, self.world),
+            chunks=ar.chunk_table(adapter), items=items,
             grad_ptrs=self.grad_h.peer_ptrs, work_ptrs=self.work_h.peer_ptrs,
             grad_mc=self.grad_h.multicast_ptr, work_mc=self.work_h.multicast_ptr, master=ar.master, m=ar.m,
             v=ar.v, flag_ptrs=self.flags_h.peer_ptrs, done_counter=self.done, rank=self.rank, world=self.world,
-            epoch=self.epoch, sync=self.world > 1, use_multimem=self.use_multimem, step=ar.steps[adapter],
+            epoch=self.epoch, sync=self.world > 1, use_multimem=self.use_multimem, step=step,
             lr=o.lr, beta1=o.beta1, beta2=o.beta2, eps=o.eps, weight_decay=o.weight_decay,
             grad_scale=grad_scale, device=ar.device)
 

@@ -31,6 +31,46 @@ class OptimizerConfig:
     weight_decay: float = 0.0
 
 
+class _OverlappedSync:
+    """Launches the fused reduce-scatter + AdamW + all-gather kernel per layer group on the
+    trainer's side stream while the last microbatch's backward is still running below that
+    group.  Every data-parallel rank creates the same groups in the same order."""
+
+    def __init__(self, trainer: "MultiLoRATrainer", adapters: list, grad_scale: float):
+        self.t, self.adapters, self.grad_scale = trainer, adapters, grad_scale
+        st = trainer.stage
+        n, g = len(st.layers), trainer.sync_layer_groups
+        cuts = [st.layer_start + (n * k) // g for k in range(g + 1)]
+        self.groups = [(cuts[k], cuts[k + 1]) for k in range(g)]     # ascending layer ranges
+        self.steps = {a: trainer._fused_sync.begin_step(a) for a in adapters}
+        self.launched = 0
+
+    def on_layer_done(self, layer: int) -> None:
+        # the backward walks the layers downwards: group k is complete once its lowest layer is done
+        k = len(self.groups) - 1 - self.launched
+        if k >= 0 and layer == self.groups[k][0]:
+            self._launch(self.groups[k])
+            self.launched += 1
+
+    def _launch(self, layers: tuple) -> None:
+        t = self.t
+        done = torch.cuda.Event()
+        done.record()                              # this group's gradients are complete here
+        t._sync_stream.wait_event(done)
+        with torch.cuda.stream(t._sync_stream):
+            for a in self.adapters:
+                t._fused_sync.reduce_and_step(a, grad_scale=self.grad_scale, layers=layers, step=self.steps[a])
+
+    def finish(self) -> None:
+        """All groups are launched; the compute stream waits for the new weights."""
+        while self.launched < len(self.groups):    # a stage whose backward skipped the hook
+            self._launch(self.groups[len(self.groups) - 1 - self.launched])
+            self.launched += 1
+        ev = torch.cuda.Event()
+        ev.record(self.t._sync_stream)
+        torch.cuda.current_stream(self.t.device).wait_event(ev)
+
+
 class MultiLoRATrainer:
     def __init__(self, cfg: ModelConfig, adapters: Sequence[AdapterSpec], device, *,
                  quantize: bool = False, recompute=True, optim: Optional[OptimizerConfig] = None,
@@ -61,6 +101,11 @@ class MultiLoRATrainer:
         else:
             self.stage = DecoderStage(cfg, adapters, device, **kw)
         self.step_count = 0
+        # Gradient sync + optimizer step of a layer group start on a side stream as soon as the
+        # last microbatch's backward has passed those layers, next to the remaining backward.
+        self.sync_layer_groups = 4
+        self.overlap_grad_sync = True
+        self._sync_stream = None
         self._fused_sync = None
         if self.grad_sync == "fused" and self.stage.arena is not None:
             from ..parallel.dp_sync import FusedGradSync
@@ -83,15 +128,31 @@ class MultiLoRATrainer:
         Returns the mean token loss as a device scalar (no host synchronisation)."""
         loss_sum = None
         n_tok = 0
-        for b in batches:
+        overlap = self._overlap_plan(len(batches), active_adapters)
+        for i, b in enumerate(batches):
+            hook = overlap.on_layer_done if (overlap is not None and i == len(batches) - 1) else None
             with nvtx_range("Forward+Backward"):
-                ls = self.stage.forward_backward(b)
+                ls = self.stage.forward_backward(b, on_layer_done=hook)
             loss_sum = ls if loss_sum is None else loss_sum + ls
             n_tok += b.num_loss_tokens
         with nvtx_range("Gradient sync + optimizer step"):
-            self.reduce_and_step(len(batches), active_adapters)
+            if overlap is not None:
+                overlap.finish()
+            else:
+                self.reduce_and_step(len(batches), active_adapters)
         self.step_count += 1
         return loss_sum / max(n_tok, 1)
+
+    def _overlap_plan(self, num_microbatches: int, active_adapters):
+        """The layer-group launcher of this step, or None when the sync runs after the backward
+        (no fused kernel, overlap switched off, or a stage with too few layers to split)."""
+        n_layers = len(self.stage.layers)
+        if self._fused_sync is None or not self.overlap_grad_sync or n_layers < 2 * self.sync_layer_groups:
+            return None
+        if self._sync_stream is None:
+            self._sync_stream = torch.cuda.Stream(self.device)
+        active = list(range(len(self.adapters)) if active_adapters is None else active_adapters)
+        return _OverlappedSync(self, active, 1.0 / (max(num_microbatches, 1) * self.dp_size))
 
     def reduce_and_step(self, num_microbatches: int, active_adapters: Optional[Sequence[int]] = None) -> None:
         arena = self.stage.arena

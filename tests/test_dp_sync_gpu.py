@@ -122,6 +122,45 @@ def test_checkpoint_after_fused_steps_equals_allreduce_plus_adamw(world, tmp_pat
             assert_close(got[k], want[k], msg=f"work {k}")
 
 
+def test_layer_group_launches_on_a_side_stream_equal_one_whole_launch():
+    """The sync of a step may be launched group of layers by group of layers (so that it can
+    overlap the rest of the backward): same weights, state and cleared gradients as one launch."""
+    from lorafusion_b200.parallel.dp_sync import FusedGradSync
+    from lorafusion_b200.parallel.symmetric import SymmetricAllocator
+    from lorafusion_b200.train.trainer import OptimizerConfig
+
+    cfg = get_model_config("tiny")
+    adapters = [AdapterSpec("a", r=16), AdapterSpec("b", r=8, target_modules=("q_proj", "v_proj", "down_proj"))]
+    opt = OptimizerConfig(lr=1e-2, beta1=0.9, beta2=0.95, weight_decay=0.05)
+    arenas, syncs = [], []
+    for _ in range(2):
+        alloc = SymmetricAllocator("cuda", None)
+        ar = LoRAArena(cfg, adapters, range(cfg.num_layers), "cuda", init_b_std=0.02, seed=0, shared_alloc=alloc)
+        arenas.append(ar)
+        syncs.append(FusedGradSync(ar, alloc, None, opt))
+    side = torch.cuda.Stream()
+    for step in range(1, 3):
+        g = torch.Generator(device="cuda").manual_seed(step)
+        grad = torch.randn(arenas[0].numel, generator=g, device="cuda")
+        for ar in arenas:
+            ar.grad.copy_(grad)
+        for a in range(2):
+            syncs[0].reduce_and_step(a, grad_scale=0.5)
+            n = syncs[1].begin_step(a)
+            for layers in ((1, 2), (0, 1)):       # the order a backward pass completes them in
+                ev = torch.cuda.Event()
+                ev.record()
+                side.wait_event(ev)
+                with torch.cuda.stream(side):
+                    syncs[1].reduce_and_step(a, grad_scale=0.5, layers=layers, step=n)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        assert arenas[1].steps == arenas[0].steps == [step, step]
+        for name in ("work", "master", "m", "v", "grad"):
+            assert torch.equal(getattr(arenas[0], name), getattr(arenas[1], name)), (step, name)
+    assert float(arenas[1].grad.abs().max()) == 0.0
+
+
 _CHILD = r"""
 import os, sys, torch, torch.distributed as dist
 os.environ["NCCL_NVLS_ENABLE"] = "0"
@@ -156,6 +195,27 @@ for step in range(1, 4):
     err = (arena.work.float() - ref.work.float()).abs().max().item()
     assert err < 1e-2, f"rank {rank} step {step}: work copy differs by {err}"
     assert arena.grad.abs().max().item() == 0.0
+# one more step, launched layer group by layer group on a side stream
+side = torch.cuda.Stream()
+g = torch.Generator(device="cuda").manual_seed(900 + rank)
+arena.grad.copy_(torch.randn(arena.numel, generator=g, device="cuda"))
+total = arena.grad.clone()
+dist.all_reduce(total)
+for adapter in range(2):
+    ref.grad.copy_(total)
+    ref.adam_step(adapter, lr=opt.lr, beta1=opt.beta1, beta2=opt.beta2, eps=opt.eps,
+                  weight_decay=opt.weight_decay, grad_scale=0.5)
+    n = sync.begin_step(adapter)
+    for layers in ((1, 2), (0, 1)):
+        ev = torch.cuda.Event(); ev.record(); side.wait_event(ev)
+        with torch.cuda.stream(side):
+            sync.reduce_and_step(adapter, grad_scale=0.5, layers=layers, step=n)
+torch.cuda.current_stream().wait_stream(side)
+torch.cuda.synchronize()
+_native.check_device_errors()
+err = (arena.work.float() - ref.work.float()).abs().max().item()
+assert err < 1e-2, f"rank {rank} grouped step: work copy differs by {err}"
+assert arena.grad.abs().max().item() == 0.0
 dist.barrier()
 dist.destroy_process_group()
 print(f"rank {rank} ok")
