@@ -40,6 +40,8 @@ constexpr int A_BYTES = BM * BK * 2;
 constexpr int B_BYTES = BNH * BK * 2;
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int STAGES = 6;
+constexpr int PAIR_EPI_WARPS = 8;                    // two per TMEM lane quarter
+constexpr int PAIR_THREADS = 64 + 32 * PAIR_EPI_WARPS;  // TMA warp, MMA warp, epilogue warps
 constexpr int SMEM_TOTAL = STAGES * STAGE_BYTES + 512 + 1024;
 
 struct Params {
@@ -98,7 +100,7 @@ __device__ __forceinline__ int slab_passes(const Tile& t, int (&ad)[2]) {
 }
 
 template <bool B_MN, int NACC, int EPI>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1)
     umma_gemm_pair_kernel(const Params p, const __grid_constant__ CUtensorMap tmA,
                           const __grid_constant__ CUtensorMap tmB,
                           const __grid_constant__ CUtensorMap tmA2,
@@ -128,7 +130,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tfull[b], 1);
-      mbar_init(&tempty[b], 256);
+      mbar_init(&tempty[b], 2 * 32 * PAIR_EPI_WARPS);  // every epilogue thread of both CTAs
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -245,7 +247,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
     }
   } else {
     // ------------------------------ epilogue (both CTAs) ------------------------------
+    // Eight warps: two per TMEM lane quarter (a warp may only touch quarter warp % 4), each
+    // taking half of the tile's columns.  The dropout-mixing variant has no second accumulator
+    // buffer, so its epilogue is exposed time between two main loops: halving it matters there.
     const int q = warp & 3;
+    const int half = (warp - 2) >> 2;
+    constexpr int CHUNKS_PER_HALF = BN / 32 / (PAIR_EPI_WARPS / 4);
     int tile_iter = 0;
     bool ok = true;
     for (int tile = pair_id; ok && tile < p.num_tiles; tile += num_pairs, ++tile_iter) {
@@ -270,7 +277,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
         inv_keep = p.adapter_inv_keep[my_adapter];
       }
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = half * CHUNKS_PER_HALF; c < (half + 1) * CHUNKS_PER_HALF; ++c) {
         uint32_t r[32], r2[32];
         tmem_ld_32x32b_x32(acc0 + c * 32, r);
         if (NACC == 2 && has_slab) tmem_ld_32x32b_x32(acc1 + c * 32, r2);
@@ -348,7 +355,7 @@ static int launch(const Params& p, const CUtensorMap& tA, const CUtensorMap& tB,
     fprintf(stderr, "lf_gemm_pair: cudaFuncSetAttribute failed\n");
     return -10;
   }
-  kern<<<2 * pairs, 192, SMEM_TOTAL, st>>>(p, tA, tB, tA2, tB2);
+  kern<<<2 * pairs, PAIR_THREADS, SMEM_TOTAL, st>>>(p, tA, tB, tA2, tB2);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     fprintf(stderr, "lf_gemm_pair: launch failed: %s\n", cudaGetErrorString(e));
