@@ -64,6 +64,11 @@ def parse_args():
     ap.add_argument("--lora-mode", default="fused", choices=["fused", "unfused"],
                     help="unfused = same-GPU baseline: separate base GEMM + cuBLAS LoRA GEMMs + stored mask")
     ap.add_argument("--multimem", action="store_true", help="use NVLS multimem loads/stores in the fused sync")
+    ap.add_argument("--layout", default="auto", choices=["auto", "dp", "tp2"],
+                    help="dp = one replica per GPU; tp2 = every pair of GPUs shares a replica (tensor + sequence "
+                         "parallel, fused all-gather->GEMM / GEMM->reduce-scatter kernels), data parallel over "
+                         "the pairs; auto = tp2 on an even number of GPUs, where halving every kept activation "
+                         "removes the recomputation a 70B replica needs on one GPU")
     ap.add_argument("--fsdp", action="store_true",
                     help="baseline: base weights sharded over the GPUs and all-gathered per layer (ZeRO-3 style)")
     ap.add_argument("--seed", type=int, default=1234, help="seed of the synthetic sample lengths")
@@ -189,11 +194,25 @@ def main():
     if args.layers > 0:
         cfg = cfg.with_layers(args.layers)
     adapters = [AdapterSpec(f"lora_{i}", r=16, lora_alpha=32.0, dropout=args.dropout) for i in range(4)]
+    tp = 2 if (args.layout == "tp2" or (args.layout == "auto" and world >= 2 and world % 2 == 0 and not args.fsdp
+                                        and args.lora_mode == "fused" and args.grad_sync != "nccl")) else 1
+    if world % tp:
+        raise SystemExit(f"--layout tp2 needs an even number of GPUs, got {world}")
+    dp = world // tp
+    dp_group = tp_group = None
+    dp_rank, tp_rank = rank, 0
+    if world > 1:
+        from lorafusion_b200.parallel.layout import ParallelLayout, initialize_parallel_state
+
+        state = initialize_parallel_state(ParallelLayout(world, dp=dp, pp=1, tp=tp))
+        dp_group, tp_group, dp_rank, tp_rank = state.dp_group, state.tp_group, state.dp_rank, state.tp_rank
+    per_replica = args.microbatches * tp   # microbatches a replica (one GPU, or one tp pair) runs per step
     t0 = time.time()
     trainer = MultiLoRATrainer(cfg, adapters, device, quantize=not args.no_quantize,
                                recompute={'auto': 'auto', 'all': True, 'none': False}[args.recompute], optim=OptimizerConfig(lr=1e-4),
-                               dp_group=dist.group.WORLD if world > 1 else None, seed=1234, init_b_std=0.01,
-                               grad_sync=args.grad_sync, use_multimem=args.multimem, use_fsdp=args.fsdp)
+                               dp_group=dp_group if dp > 1 else None, seed=1234, init_b_std=0.01,
+                               grad_sync=args.grad_sync, use_multimem=args.multimem, use_fsdp=args.fsdp,
+                               tp_group=tp_group if tp > 1 else None, max_tokens=args.capacity)
     if "expandable_segments:True" in os.environ.get("PYTORCH_CUDA_ALLOC_CONF", ""):
         trainer.stage.reserve_bytes = 5 << 30  # little fragmentation to provide for
     trainer.stage.plan_activations(args.capacity)
@@ -206,18 +225,22 @@ def main():
     n_total = args.warmup + args.steps
     # Rank 0 packs every step for the whole group (the branch and bound stops on a time limit,
     # so two ranks could find different packings) and hands every rank its share.
-    box = [make_all_step_specs(args.seed, args.capacity, args.microbatches, world, n_total + 1)
+    box = [make_all_step_specs(args.seed, args.capacity, per_replica, dp, n_total + 1)
            if rank == 0 else None]
     if world > 1:
         dist.broadcast_object_list(box, src=0)
     all_specs = box[0]
-    step_specs = [all_specs[s][rank] for s in range(n_total)]
-    probe_specs = all_specs[n_total][rank]
+    for st_ in all_specs:
+        for per in st_:
+            for sp in per:
+                sp.total_multiple = 128 * tp   # token rows are cut in tp equal shards of whole tiles
+    step_specs = [all_specs[s][dp_rank] for s in range(n_total)]   # both ranks of a tp pair run the same batches
+    probe_specs = all_specs[n_total][dp_rank]
     tokens_per_step = [sum(sp.total_tokens for sp in specs) for specs in step_specs]
     sq = [sum(n * n for sp in st_[r] for _, lens in sp.segments for n in lens) for st_ in all_specs[:n_total]
-          for r in range(world)]
+          for r in range(dp)]
     balance = {"attention_cost_max_over_mean": round(max(
-        max(sq[s * world:(s + 1) * world]) * world / max(sum(sq[s * world:(s + 1) * world]), 1)
+        max(sq[s * dp:(s + 1) * dp]) * dp / max(sum(sq[s * dp:(s + 1) * dp]), 1)
         for s in range(n_total)), 3)}
 
     def barrier():
@@ -253,14 +276,19 @@ def main():
     dev0 = trainer.to_device(probe_specs, host0, n_total)
     probe_tokens = sum(sp.total_tokens for sp in probe_specs)
     trainer.step_on_device(dev0)
-    t_off = timed_step(dev0)
-    like_for_like = {"policy": "no host offload (what every N runs when the shared host link is too slow)",
-                     "ms_per_step": round(t_off, 1), "tokens_per_s_per_gpu": round(probe_tokens / (t_off / 1e3), 1),
-                     "steps": 1}
-    if args.offload != "off" and args.recompute == "auto" and args.lora_mode == "fused":
+    t_off = 0.0
+    if tp == 1:
+        t_off = timed_step(dev0)
+        like_for_like = {"policy": "data parallel, no host offload",
+                         "ms_per_step": round(t_off, 1), "tokens_per_s_per_gpu": round(probe_tokens / (t_off / 1e3), 1),
+                         "steps": 1}
+    else:
+        offload_note = "off (not needed: a tp2 replica keeps every layer's activations on its two GPUs)"
+    if tp == 1 and args.offload != "off" and args.recompute == "auto" and args.lora_mode == "fused":
         from lorafusion_b200.models.offload import measure_pcie_bandwidth
 
         d2h, h2d = measure_pcie_bandwidth(device, dist.group.WORLD if world > 1 else None)
+        # (all GPUs of the node copy at once, whatever group they belong to)
         per_gu = args.capacity * 2 * cfg.intermediate_size * 2
         fwd_s = (t_off / 1e3) / args.microbatches / 3.0   # a forward pass is about a third of fwd + bwd
         # the forward pass sends, the (twice as long) backward pass fetches
@@ -310,7 +338,7 @@ def main():
     launches = _native.launch_count() - launches0
     ms_e2e = ev_begin.elapsed_time(ev_end)
     ms = sum(a.elapsed_time(b) for a, b in ev)
-    toks = float(sum(tokens_per_step[args.warmup:]))
+    toks = float(sum(tokens_per_step[args.warmup:])) if tp_rank == 0 else 0.0   # a tp pair's tokens count once
     stats = torch.tensor([ms, ms_e2e, toks], dtype=torch.float64, device=device)
     if world > 1:
         mx = stats.clone()
@@ -337,9 +365,11 @@ def main():
         "impl": "ours",
         "config": {
             "model": cfg.name + ("-nf4" if not args.no_quantize else "-bf16"),
-            "global_batch": f"{args.microbatches} x {args.capacity}-token microbatches per GPU per step",
+            "global_batch": f"{args.microbatches} x {args.capacity}-token microbatches per GPU per step"
+                            + (f" ({per_replica} per tp{tp} replica)" if tp > 1 else ""),
             "seq_len": "lognormal medians 256/512/1024/2048, sigma 0.5-0.8, clip [32,8192], packed",
-            "parallelism": f"dp{world}" + (" + base sharded ZeRO-3 style (baseline)" if args.fsdp else ""),
+            "parallelism": (f"dp{dp}tp{tp}" if tp > 1 else f"dp{world}")
+                           + (" + base sharded ZeRO-3 style (baseline)" if args.fsdp else ""),
             "adapters": "4 x LoRA r16 alpha32 dropout %.2f on q,k,v,o,gate,up,down" % args.dropout,
             "grad_sync": trainer.grad_sync,
             "lora_mode": args.lora_mode,
@@ -350,7 +380,7 @@ def main():
             "l2": "inputs (frozen base weights) far larger than L2",
             "baseline": "vs_baseline = value / (n_gpus * 1278.85 tok/s/GPU), the reference's published "
                         "70B-mixed LoRAFusion throughput on 4xH100 per GPU",
-            "tokens_per_step_per_gpu": tokens_per_step[-1],
+            "tokens_per_step_per_gpu": tokens_per_step[-1] // tp,
             "batches": "solver-packed per step for the whole dp group, dealt by sum(len^2) "
                        "(train.data.pack_balanced_dp_step)",
             "balance": balance,

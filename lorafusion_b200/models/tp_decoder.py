@@ -128,6 +128,47 @@ class TpDecoderStage(DecoderStage):
             self.arena.sync_master_from_work()
         return self
 
+    # ------------------------------------------------------------------ activation memory plan
+    def saved_bytes_per_layer(self, tokens: int, mode="cheap") -> int:
+        """Bytes one layer keeps on THIS rank: column-sharded GEMM outputs over all tokens, the
+        token-sharded residual stream, and (mode True) the tensors "cheap" rebuilds instead."""
+        c, tp = self.cfg, self.tp   # c holds the rank-local sizes
+        ts = tokens // tp
+        kept = tokens * (c.qkv_size + c.q_size + 2 * c.intermediate_size) * 2 + ts * c.hidden_size * 2 \
+            + c.num_heads * tokens * 4 + tokens * 4 * 256 * 2
+        if mode is True:
+            kept += 2 * ts * c.hidden_size * 2 + tokens * c.intermediate_size * 2
+        return kept
+
+    def _plan_modes(self, tokens: int) -> list:
+        """Per-layer keep mode: ``True`` (keep everything), ``"cheap"`` (keep GEMM / attention
+        outputs, rebuild the normalised inputs and the SwiGLU output with elementwise kernels) or
+        ``False`` (recompute the layer, which repeats its collectives).  With ``recompute="auto"``
+        as many trailing layers as fit become ``"cheap"``; the tensor-parallel ranks agree on the
+        smallest count any of them can afford, since a recomputed layer runs fused collectives
+        that every rank must enter."""
+        n = len(self.layers)
+        if self.force_keep_modes is not None:
+            return list(self.force_keep_modes)
+        if self.recompute is True:
+            return [False] * n
+        if self.recompute is False:
+            return [True] * n
+        if self._modes_plan is None or tokens > self._modes_tokens:
+            free, _ = torch.cuda.mem_get_info(self.device)
+            free += torch.cuda.memory_reserved(self.device) - torch.cuda.memory_allocated(self.device)
+            ts = tokens // self.tp
+            h_in_all = n * ts * self.cfg.hidden_size * 2
+            budget = free - self.reserve_bytes - self.working_set_bytes(tokens) - h_in_all * self.max_inflight
+            n_keep = int(max(0, budget) // (self.saved_bytes_per_layer(tokens) * self.max_inflight))
+            n_keep = max(0, min(n, n_keep))
+            if self.tp > 1:
+                t = torch.tensor([n_keep], dtype=torch.int64, device=self.device)
+                dist.all_reduce(t, op=dist.ReduceOp.MIN, group=self.tp_group)
+                n_keep = int(t.item())
+            self._modes_plan, self._modes_tokens = [False] * (n - n_keep) + ["cheap"] * n_keep, tokens
+        return self._modes_plan
+
     # ------------------------------------------------------------------ helpers
     def _shard(self, t: torch.Tensor) -> torch.Tensor:
         ms = t.shape[0] // self.tp
@@ -196,8 +237,10 @@ class TpDecoderStage(DecoderStage):
         d, s_d = row_parallel(act, "down", lw.down, i_loc)
         full = None
         if keep:
-            full = dict(x1=x1, rstd1=rstd1, qkv=qkv, attn=attn, lse=lse, s_qkv=s_qkv, s_o=s_o, h_mid=h_mid,
-                        x2=x2, rstd2=rstd2, gu=gu, act=act, s_gu=s_gu, s_d=s_d)
+            full = dict(rstd1=rstd1, qkv=qkv, attn=attn, lse=lse, s_qkv=s_qkv, s_o=s_o, h_mid=h_mid,
+                        rstd2=rstd2, gu=gu, s_gu=s_gu, s_d=s_d)
+            if keep is True:  # "cheap" drops what one elementwise kernel rebuilds from kept tensors
+                full.update(x1=x1, x2=x2, act=act)
         return h_mid, d, LayerSaved(h_in, full)
 
     def _layer_backward(self, li: int, saved: LayerSaved, dh, batch: PackedBatch, need_input_grad: bool = True):
@@ -212,6 +255,11 @@ class TpDecoderStage(DecoderStage):
         if sv is None:
             _, _, re = self._layer_forward(li, None, saved.h_in, batch, keep=True)
             sv = re.full
+        elif "x1" not in sv:  # "cheap": the normalised token shards and the SwiGLU output are rebuilt
+            sv = dict(sv)
+            sv["x1"] = ew.rmsnorm_fwd(saved.h_in, lw.ln1, cfg.rms_eps, want_rstd=False)[0]
+            sv["x2"] = ew.rmsnorm_fwd(sv["h_mid"], lw.ln2, cfg.rms_eps, want_rstd=False)[0]
+            sv["act"] = ew.swiglu_fwd(sv["gu"])
 
         def row_parallel_bwd(dy_sh, x_loc, s_p, proj, w, k_loc):
             """all-gather(dY | dS) -> dX_local = dY_full W_shard + keep (.) (dS_full A_shard)."""
@@ -272,10 +320,9 @@ class TpDecoderStage(DecoderStage):
         else:
             delta = h_in
         res, saved = None, []
-        n_keep = self._plan_keep(batch.num_tokens)
-        first_keep = len(self.layers) - n_keep
+        modes = self._plan_modes(batch.num_tokens)
         for li in range(len(self.layers)):
-            res, delta, sv = self._layer_forward(li, res, delta, batch, keep=li >= first_keep)
+            res, delta, sv = self._layer_forward(li, res, delta, batch, keep=modes[li])
             saved.append(sv)
         if self.is_last:
             return (res, delta), saved

@@ -75,9 +75,14 @@ class MultiLoRATrainer:
     def __init__(self, cfg: ModelConfig, adapters: Sequence[AdapterSpec], device, *,
                  quantize: bool = False, recompute=True, optim: Optional[OptimizerConfig] = None,
                  dp_group=None, seed: int = 0, init_b_std: float = 0.0, grad_sync: str = "auto",
-                 use_multimem: bool = False, use_fsdp: bool = False):
+                 use_multimem: bool = False, use_fsdp: bool = False, tp_group=None, max_tokens: int = 16384):
         """``use_fsdp``: ZeRO-3 style baseline -- the frozen base is sharded over the data-parallel
-        group and gathered layer by layer (``models/fsdp_decoder.py``)."""
+        group and gathered layer by layer (``models/fsdp_decoder.py``).
+        ``tp_group``: shard every layer over this tensor-parallel group (fused all-gather -> GEMM /
+        GEMM -> reduce-scatter kernels, token-sharded activations; ``models/tp_decoder.py``);
+        ``dp_group`` then holds the ranks with the same position in their tensor-parallel groups,
+        and all ranks of a tensor-parallel group must be given the same microbatches
+        (``max_tokens`` = the largest one, a multiple of 128 x tp)."""
         self.cfg = cfg
         self.adapters = list(adapters)
         self.device = torch.device(device)
@@ -94,7 +99,15 @@ class MultiLoRATrainer:
 
             alloc = SymmetricAllocator(self.device, dp_group)
         kw = dict(quantize=quantize, recompute=recompute, seed=seed, init_b_std=init_b_std, shared_alloc=alloc)
-        if use_fsdp:
+        self.tp_group = tp_group
+        self.tp_size = dist.get_world_size(tp_group) if (dist.is_initialized() and tp_group is not None) else 1
+        if self.tp_size > 1:
+            if use_fsdp:
+                raise ValueError("use_fsdp and tensor parallelism cannot be combined")
+            from ..models.tp_decoder import TpDecoderStage
+
+            self.stage = TpDecoderStage(cfg, adapters, device, tp_group, max_tokens=max_tokens, **kw)
+        elif use_fsdp:
             from ..models.fsdp_decoder import FsdpDecoderStage
 
             self.stage = FsdpDecoderStage(cfg, adapters, device, dp_group if self.dp_size > 1 else None, **kw)
@@ -147,7 +160,8 @@ class MultiLoRATrainer:
         """The layer-group launcher of this step, or None when the sync runs after the backward
         (no fused kernel, overlap switched off, or a stage with too few layers to split)."""
         n_layers = len(self.stage.layers)
-        if self._fused_sync is None or not self.overlap_grad_sync or n_layers < 2 * self.sync_layer_groups:
+        if self._fused_sync is None or not self.overlap_grad_sync or n_layers < 2 * self.sync_layer_groups \
+                or self.tp_size > 1:  # replicated LoRA factors are first summed over the tp group
             return None
         if self._sync_stream is None:
             self._sync_stream = torch.cuda.Stream(self.device)
@@ -161,6 +175,8 @@ class MultiLoRATrainer:
         active = range(len(self.adapters)) if active_adapters is None else active_adapters
         scale = 1.0 / (max(num_microbatches, 1) * self.dp_size)
         o = self.optim
+        if self.tp_size > 1:
+            self.stage.reduce_replicated_grads()   # partial sums of the replicated factors, every adapter
         if self._fused_sync is not None:
             for a in active:
                 self._fused_sync.reduce_and_step(a, grad_scale=scale)

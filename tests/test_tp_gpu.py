@@ -128,12 +128,15 @@ from lorafusion_b200.utils.testing import assert_close_two_rounds
 
 cfg = get_model_config("tiny")
 adapters = [AdapterSpec("lora_0", r=16, lora_alpha=32, dropout=0.1), AdapterSpec("lora_1", r=8, lora_alpha=16)]
-for quantize, recompute in ((False, False), (False, True)):
+for quantize, recompute in ((False, False), (False, True), (False, "auto")):   # "auto" -> the "cheap" level
     full = DecoderStage(cfg, adapters, dev, quantize=quantize, init_b_std=0.02, seed=3, recompute=False)
     spec = MicroBatchSpec([(0, [100, 37, 200]), (1, [129, 64, 100])])   # 384 + 384 = 768 tokens
     batch = build_packed_batch(spec, adapters, cfg.vocab_size, dev, seed=5)
     assert batch.num_tokens % (128 * world) == 0, batch.num_tokens
     tp = TpDecoderStage.from_full(full, dist.group.WORLD, max_tokens=batch.num_tokens, recompute=recompute)
+    if recompute == "auto":
+        assert tp.plan_activations(batch.num_tokens)["keep_all_gemm_outputs"] == len(tp.layers)
+        assert set(tp._plan_modes(batch.num_tokens)) == {"cheap"}
     for step in range(2):          # two microbatches back to back exercise buffer reuse
         loss_full = full.forward_backward(batch)
         out, saved = tp.forward(batch)
@@ -157,7 +160,7 @@ for quantize, recompute in ((False, False), (False, True)):
         kw = dict(atol=3e-2, rtol=5e-2, scale_atol_by_rms=True, max_mismatch_ratio=1e-2)
         assert_close_two_rounds(la, exp_a, msg=f"dA {l} {proj} (quantize={quantize}, recompute={recompute})", **kw)
         assert_close_two_rounds(lb, exp_b, msg=f"dB {l} {proj} (quantize={quantize}, recompute={recompute})", **kw)
-    if not recompute:
+    if recompute is False:
         # checkpoint round trip under tensor parallelism: shards are gathered into full PEFT
         # tensors on save and cut again on load
         from lorafusion_b200.train import checkpoint as ck
