@@ -103,6 +103,8 @@ typedef struct LfNf4Args {
 } LfNf4Args;
 
 int lf_gemm_nf4(const LfGemmArgs* args, const LfNf4Args* nf4);
+// Tensor-parallel fused variants reading an NF4 weight shard (see lf_gemm_tp and lf_gemm_nf4).
+int lf_gemm_tp_nf4(const LfGemmArgs* args, const LfTpArgs* tp, const LfNf4Args* nf4);
 
 #ifdef __cplusplus
 }

@@ -148,15 +148,19 @@ constexpr int kNumCommWarps = 4;
 
 template <int BN, int NACC, bool A_MN, bool B_MN, bool B2_MN, int EPI, bool MASK_A, int TP = 0,
           bool NF4B = false>
-__global__ void __launch_bounds__((MASK_A || NF4B) ? (192 + 32 * kNumMaskWarps)
-                                                   : (TP != 0 ? 192 + 32 * kNumCommWarps : 192), 1)
+__global__ void __launch_bounds__(192 + ((MASK_A || NF4B) ? 32 * kNumMaskWarps : 0) +
+                                      (TP != 0 ? 32 * kNumCommWarps : 0), 1)
     umma_gemm_kernel(const GemmKParams p, const __grid_constant__ CUtensorMap tmA,
                      const __grid_constant__ CUtensorMap tmB,
                      const __grid_constant__ CUtensorMap tmA2,
                      const __grid_constant__ CUtensorMap tmB2, const TpParams tp) {
   static_assert(!(MASK_A && TP != 0), "dropout-in-smem and TP fusion are not combined");
-  static_assert(!NF4B || (BN == 256 && !MASK_A && TP == 0 && !A_MN),
+  static_assert(!NF4B || (BN == 256 && !MASK_A && !A_MN),
                 "the NF4 main loop exists for 256-wide dense tiles only");
+  // Thread layout: warp 0 TMA, warp 1 MMA, warps 2-5 epilogue, then (if any) the eight warps
+  // that rewrite a stage (dropout mask or NF4 expansion), then (if any) the four warps that
+  // move data between GPUs.  COMM_T0 = first thread of the latter.
+  constexpr int COMM_T0 = 192 + ((MASK_A || NF4B) ? 32 * kNumMaskWarps : 0);
   using Plan = SmemPlan<BN, NF4B>;
   constexpr bool XFORM = MASK_A || NF4B;  // extra warps rewrite a stage before the MMA reads it
   __shared__ float nf4_lut[16];
@@ -479,12 +483,12 @@ __global__ void __launch_bounds__((MASK_A || NF4B) ? (192 + 32 * kNumMaskWarps)
         }
       }
     }
-  } else if (TP == 2) {
+  } else if (TP == 2 && int(threadIdx.x) >= COMM_T0) {
     // ---- reduce the partials of the rows this rank owns, as they arrive ----
     // Four dedicated warps, concurrent with the GEMM of the other warps: they poll the
     // per-(source, row tile, column tile) flags and sum the bf16 partials in fp32 (+ residual).
     // Every thread keeps the loads of two output vectors from all sources in flight.
-    const int et = threadIdx.x - 192;  // 0..127
+    const int et = threadIdx.x - COMM_T0;  // 0..127
     const int ms = tp.tiles_per_shard * BM;
     const int items = tp.tiles_per_shard * p.num_n_tiles;
     constexpr int VEC_PER_ROW = BN / 8;
@@ -551,9 +555,9 @@ __global__ void __launch_bounds__((MASK_A || NF4B) ? (192 + 32 * kNumMaskWarps)
         }
       }
     }
-  } else if (TP == 1 && !MASK_A) {
+  } else if (TP == 1 && !MASK_A && int(threadIdx.x) >= COMM_T0) {
     // ------------- push this rank's token shard to every peer's gathered buffer -------------
-    const int ct = threadIdx.x - 192;  // 0..127
+    const int ct = threadIdx.x - COMM_T0;  // 0..127
     const int tps = tp.tiles_per_shard;
     const int ms = tps * BM;
     // A row tile is pushed by up to eight CTAs (row slices), so that every SM's copy warps take
@@ -796,7 +800,7 @@ static int launch_variant(const GemmKParams& kp, const CUtensorMap& tA, const CU
       return -10;
     }
   }
-  const int threads = (MASK_A || NF4B) ? (192 + 32 * kNumMaskWarps) : (TP != 0 ? 192 + 32 * kNumCommWarps : 192);
+  const int threads = 192 + ((MASK_A || NF4B) ? 32 * kNumMaskWarps : 0) + (TP != 0 ? 32 * kNumCommWarps : 0);
   kern<<<grid, threads, smem, stream>>>(kp, tA, tB, tA2, tB2, tp);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
@@ -831,6 +835,13 @@ extern "C" int lf_gemm_tp(const LfGemmArgs* a, const LfTpArgs* t) { return gemm_
 extern "C" int lf_gemm_nf4(const LfGemmArgs* a, const LfNf4Args* q) {
   if (q == nullptr || q->block_scales == nullptr) return -1;
   return gemm_entry(a, nullptr, q);
+}
+
+// Both at once: the tensor-parallel fused kernels with the NF4 weight shard expanded in their
+// main loop (the QLoRA configuration of the tensor-parallel layouts).
+extern "C" int lf_gemm_tp_nf4(const LfGemmArgs* a, const LfTpArgs* t, const LfNf4Args* q) {
+  if (t == nullptr || q == nullptr || q->block_scales == nullptr) return -1;
+  return gemm_entry(a, t, q);
 }
 
 static int gemm_entry(const LfGemmArgs* a, const LfTpArgs* t, const LfNf4Args* q) {
@@ -946,6 +957,27 @@ static int gemm_entry(const LfGemmArgs* a, const LfTpArgs* t, const LfNf4Args* q
     kp.group_m = t->tiles_per_shard < kp.group_m ? t->tiles_per_shard : kp.group_m;
     const int tkey = (t->mode << 8) | (a->nacc << 4) | ((a->b_mn ? 1 : 0) << 1) | (a->epi == LF_EPI_BF16_DROPMIX);
     if (BN != 256 || a->a_mn) return -9;
+    if (q != nullptr) {
+      // NF4 weight expanded inside the main loop of the fused compute + collective kernel
+      if (a->K2 > 0 && (a->b2_mn != a->b_mn)) return -5;
+      switch (tkey) {
+        case (1 << 8) | (1 << 4) | 0:
+          return launch_variant<256, 1, false, false, false, LF_EPI_BF16, false, 1, true>(kp, tA, tB, tA2, tB2, grid, st, tp);
+        case (1 << 8) | (1 << 4) | 2:
+          return launch_variant<256, 1, false, true, true, LF_EPI_BF16, false, 1, true>(kp, tA, tB, tA2, tB2, grid, st, tp);
+        case (1 << 8) | (2 << 4) | 3:
+          return launch_variant<256, 2, false, true, true, LF_EPI_BF16_DROPMIX, false, 1, true>(kp, tA, tB, tA2, tB2, grid, st, tp);
+        case (2 << 8) | (1 << 4) | 0:
+          return launch_variant<256, 1, false, false, false, LF_EPI_BF16, false, 2, true>(kp, tA, tB, tA2, tB2, grid, st, tp);
+        case (2 << 8) | (1 << 4) | 2:
+          return launch_variant<256, 1, false, true, true, LF_EPI_BF16, false, 2, true>(kp, tA, tB, tA2, tB2, grid, st, tp);
+        case (2 << 8) | (2 << 4) | 3:
+          return launch_variant<256, 2, false, true, true, LF_EPI_BF16_DROPMIX, false, 2, true>(kp, tA, tB, tA2, tB2, grid, st, tp);
+        default:
+          fprintf(stderr, "lf_gemm_tp_nf4: no kernel variant for key 0x%x\n", tkey);
+          return -5;
+      }
+    }
     switch (tkey) {
       case (1 << 8) | (1 << 4) | 0:
         return launch_variant<256, 1, false, false, false, LF_EPI_BF16, false, 1>(kp, tA, tB, tA2, tB2, grid, st, tp);

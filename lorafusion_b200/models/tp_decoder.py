@@ -216,7 +216,7 @@ class TpDecoderStage(DecoderStage):
             lk.lora_down(x_sh, stack.a, tile_adapter=ta_shard, adapter_scale=info.adapter_scale,
                          dropout=self._drop(info, self._sid(l, proj), row_offset=r * ms),
                          out=ctx.own_gather2_rows(T, R))
-            y = ag_gemm(ctx, T, H, materialize_weight(w), slab_cols=R, b2=stack.b, b2_adapter_rows=stack.b.shape[1],
+            y = ag_gemm(ctx, T, H, materialize_weight(w, T), slab_cols=R, b2=stack.b, b2_adapter_rows=stack.b.shape[1],
                         tile_adapter=info.tile_adapter, bias=bias)
             return y, x_sh.clone(), h_sh, rstd, ctx.gather2_view(T, R).clone()
 
@@ -224,7 +224,7 @@ class TpDecoderStage(DecoderStage):
             stack = st[proj]
             s_p = lk.lora_down(x_loc, stack.a, tile_adapter=info.tile_adapter, adapter_scale=info.adapter_scale,
                                dropout=self._drop(info, self._sid(l, proj), col_offset=r * k_loc))
-            y_sh = gemm_rs(ctx, x_loc, materialize_weight(w), s=s_p, b2=stack.b, b2_adapter_rows=stack.b.shape[1],
+            y_sh = gemm_rs(ctx, x_loc, materialize_weight(w, T), s=s_p, b2=stack.b, b2_adapter_rows=stack.b.shape[1],
                            tile_adapter=info.tile_adapter, residual=residual)
             return y_sh, s_p
 
@@ -269,7 +269,7 @@ class TpDecoderStage(DecoderStage):
             lk.lora_ds(dy_sh, stack.b, tile_adapter=ta_shard, adapter_scale=info.adapter_scale,
                        out=ctx.own_gather2_rows(T, R))
             drop = self._drop(info, self._sid(l, proj), col_offset=r * k_loc)
-            dx_loc = ag_gemm(ctx, T, H, materialize_weight(w), w_mn=True, slab_cols=R, b2=stack.a,
+            dx_loc = ag_gemm(ctx, T, H, materialize_weight(w, T), w_mn=True, slab_cols=R, b2=stack.a,
                              b2_adapter_rows=R, tile_adapter=info.tile_adapter,
                              dropout_kwargs=drop.kwargs() if drop.active else None)
             dy_full, ds_full = ctx.gather_view(T, H), ctx.gather2_view(T, R)
@@ -294,7 +294,7 @@ class TpDecoderStage(DecoderStage):
             if not need_dx:
                 return None
             drop = self._drop(info, self._sid(l, proj))
-            return gemm_rs(ctx, dy_loc, materialize_weight(w), w_mn=True, s=ds_p, b2=stack.a,
+            return gemm_rs(ctx, dy_loc, materialize_weight(w, T), w_mn=True, s=ds_p, b2=stack.a,
                            b2_adapter_rows=stack.a.shape[1], tile_adapter=info.tile_adapter,
                            dropout_kwargs=drop.kwargs() if drop.active else None)
 

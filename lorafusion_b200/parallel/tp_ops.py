@@ -183,6 +183,19 @@ def _launch(gemm_kwargs: dict, tp: LfTpArgs) -> None:
         lib._lf_tp_declared = True
     args = fill_gemm_args(**gemm_kwargs)
     nv.note_launch()
+    qw = gemm_kwargs["b"]
+    if hasattr(qw, "packed"):  # NF4 weight shard, expanded inside the kernel's main loop
+        if not getattr(lib, "_lf_tp_nf4_declared", False):
+            lib.lf_gemm_tp_nf4.argtypes = [C.POINTER(nv.LfGemmArgs), C.POINTER(LfTpArgs), C.POINTER(nv.LfNf4Args)]
+            lib.lf_gemm_tp_nf4.restype = C.c_int
+            lib._lf_tp_nf4_declared = True
+        q = nv.LfNf4Args()
+        scales = qw.fp32_block_scales()
+        q.block_scales, q.w_rows, q.w_cols = scales.data_ptr(), qw.shape[0], qw.shape[1]
+        rc = lib.lf_gemm_tp_nf4(C.byref(args), C.byref(tp), C.byref(q))
+        if rc != 0:
+            raise RuntimeError(f"lf_gemm_tp_nf4 failed with code {rc}")
+        return
     rc = lib.lf_gemm_tp(C.byref(args), C.byref(tp))
     if rc != 0:
         raise RuntimeError(f"lf_gemm_tp failed with code {rc}")
@@ -198,7 +211,8 @@ def ag_gemm(ctx: TpContext, tokens: int, k: int, w: torch.Tensor, *, w_mn: bool 
     k)`` (and of the slab operand into ``ctx.own_gather2_rows(tokens, slab_cols)``); the
     kernel pushes them to the peers and consumes the peers' rows as they land.  ``w`` is
     ``[N, k]`` (``w_mn=False``) or ``[k, N]`` consumed MN-major (``w_mn=True``, used for
-    ``dY_full @ W_shard`` in the backward)."""
+    ``dY_full @ W_shard`` in the backward); an :class:`~lorafusion_b200.ops.nf4.NF4Weight` is
+    expanded inside the kernel's main loop."""
     a = ctx.gather_view(tokens, k)
     N = w.shape[1] if w_mn else w.shape[0]
     if out is None:

@@ -71,6 +71,19 @@ for it, T in enumerate([1024, 512, 1024]):
     ref = tot[rank * ms:(rank + 1) * ms] + res.float()
     torch.cuda.synchronize(); _native.check_device_errors()
     assert_close_two_rounds(out, ref, atol=2e-2, msg=f"gemm_rs it{it}")
+    if it == 0:   # the weight shard as NF4, expanded inside the fused kernels
+        from lorafusion_b200.ops.nf4 import dequantize_nf4_reference, quantize_nf4
+        qw, qa = quantize_nf4(w), quantize_nf4(wa)
+        ctx.own_gather_rows(T, K).copy_(x_shard)
+        ctx.own_gather2_rows(T, R).copy_(s_shard)
+        yq = ag_gemm(ctx, T, K, qw, slab_cols=R, b2=b2, b2_adapter_rows=N)
+        outq = gemm_rs(ctx, xa, qa, s=sa, b2=b2, b2_adapter_rows=N, residual=res)
+        torch.cuda.synchronize(); _native.check_device_errors()
+        assert_close_two_rounds(yq, x_full @ dequantize_nf4_reference(qw).float().t() + s_full @ b2[0].float().t(),
+                                msg="ag_gemm NF4")
+        part = xa.float() @ dequantize_nf4_reference(qa).float().t() + sa.float() @ b2[0].float().t()
+        tot = part.to(torch.bfloat16).float(); dist.all_reduce(tot)
+        assert_close_two_rounds(outq, tot[rank * ms:(rank + 1) * ms] + res.float(), atol=2e-2, msg="gemm_rs NF4")
 dist.barrier()
 dist.destroy_process_group()
 print(f"rank {rank} ok")
@@ -257,3 +270,26 @@ def test_loopback_runs_the_copy_and_reduce_warps_on_one_gpu(world):
         mine = (xa.float() @ wa.float().t() + sa.float() @ b2[0].float().t()).to(torch.bfloat16).float()
         ref = mine[:ms] + sum(o.float()[:ms] for o in others) + res.float()
         assert_close_two_rounds(out, ref, atol=2e-2, msg=f"loop-back gemm_rs it{it}")
+
+        if it == 0:
+            # ---- the same two fused kernels reading their weight shard as NF4, expanded in the main loop
+            from lorafusion_b200.ops.nf4 import dequantize_nf4_reference, quantize_nf4
+
+            qw, qwt = quantize_nf4(w), quantize_nf4(rnd(K, N, scale=0.05, seed=33))
+            wd, wtd = dequantize_nf4_reference(qw).float(), dequantize_nf4_reference(qwt).float()
+            ctx.gather_view(T, K).copy_(x_full)
+            ctx.gather2_view(T, R).copy_(s_full)
+            ctx.loopback_arm_gather(T)
+            yq = ag_gemm(ctx, T, K, qw, slab_cols=R, b2=b2, b2_adapter_rows=N)
+            ctx.loopback_arm_gather(T)
+            yq2 = ag_gemm(ctx, T, K, qwt, w_mn=True)
+            ctx.loopback_arm_reduce(T, N, others)
+            outq = gemm_rs(ctx, xa, qw, s=sa, b2=b2, b2_adapter_rows=N, residual=res)
+            torch.cuda.synchronize()
+            _native.check_device_errors()
+            assert_close_two_rounds(yq, x_full.float() @ wd.t() + s_full.float() @ b2[0].float().t(),
+                                    msg="loop-back ag_gemm NF4 (K-major weight)")
+            assert_close_two_rounds(yq2, x_full.float() @ wtd, msg="loop-back ag_gemm NF4 (MN-major weight)")
+            mine = (xa.float() @ wd.t() + sa.float() @ b2[0].float().t()).to(torch.bfloat16).float()
+            assert_close_two_rounds(outq, mine[:ms] + sum(o.float()[:ms] for o in others) + res.float(), atol=2e-2,
+                                    msg="loop-back gemm_rs NF4")
