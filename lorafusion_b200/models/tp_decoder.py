@@ -348,21 +348,27 @@ class TpDecoderStage(DecoderStage):
         return loss, ew.rmsnorm_bwd(dx, h_fin, self.final_norm, rstd)
 
     # ------------------------------------------------------------------ replicated-factor gradients
-    def replicated_grad_views(self, adapter: Optional[int] = None) -> list:
+    def replicated_grad_views(self, adapter: Optional[int] = None, layers: Optional[tuple] = None) -> list:
         """fp32 gradient tensors that are partial sums per TP rank: A of column-parallel and
-        B of row-parallel projections (of one adapter, or of all)."""
+        B of row-parallel projections (of one adapter, or of all; of layers ``lo <= l < hi``, or
+        of all)."""
         out = []
         for (l, proj), v in self.arena.views.items():
+            if layers is not None and not (layers[0] <= l < layers[1]):
+                continue
             g = v.stack.da if proj in ("qkv", "gate_up") else v.stack.db
             out.append(g if adapter is None else g[adapter])
         return out
 
-    def reduce_replicated_grads(self, adapter: Optional[int] = None) -> None:
+    def reduce_replicated_grads(self, adapter: Optional[int] = None, layers: Optional[tuple] = None) -> None:
         """Sum the partial gradients of replicated LoRA factors over the TP group (call right
-        before the optimizer step of ``adapter``; ``None`` = every adapter)."""
+        before the optimizer step of ``adapter``; ``None`` = every adapter; ``layers`` limits
+        it to a group of layers so that it can run while the backward is still below them)."""
         if self.tp <= 1 or self.arena is None:
             return
-        views = self.replicated_grad_views(adapter)
+        views = self.replicated_grad_views(adapter, layers)
+        if not views:
+            return
         flat = torch.cat([v.reshape(-1) for v in views])
         dist.all_reduce(flat, group=self.tp_group)
         off = 0

@@ -58,6 +58,8 @@ class _OverlappedSync:
         done.record()                              # this group's gradients are complete here
         t._sync_stream.wait_event(done)
         with torch.cuda.stream(t._sync_stream):
+            if t.tp_size > 1:   # partial sums of the replicated LoRA factors of this group, over the tp pair
+                t.stage.reduce_replicated_grads(layers=layers)
             for a in self.adapters:
                 t._fused_sync.reduce_and_step(a, grad_scale=self.grad_scale, layers=layers, step=self.steps[a])
 
@@ -160,8 +162,7 @@ class MultiLoRATrainer:
         """The layer-group launcher of this step, or None when the sync runs after the backward
         (no fused kernel, overlap switched off, or a stage with too few layers to split)."""
         n_layers = len(self.stage.layers)
-        if self._fused_sync is None or not self.overlap_grad_sync or n_layers < 2 * self.sync_layer_groups \
-                or self.tp_size > 1:  # replicated LoRA factors are first summed over the tp group
+        if self._fused_sync is None or not self.overlap_grad_sync or n_layers < 2 * self.sync_layer_groups:
             return None
         if self._sync_stream is None:
             self._sync_stream = torch.cuda.Stream(self.device)
