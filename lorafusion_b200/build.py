@@ -96,11 +96,16 @@ def _build_lib(sources: list[Path], compiler: list[str], flags: list[str], out: 
                 sys.stderr.write(text)
                 raise RuntimeError(f"compilation of {src} failed")
     if changed or not out.exists():
-        cmd = link_cmd + [str(o) for o in objs] + ["-o", str(out)]
+        # link next to the target and swap it in with one rename: whoever copies or loads the
+        # library meanwhile sees either the old file or the new one, never a half-written one
+        tmp = out.with_name(out.name + f".tmp{os.getpid()}")
+        cmd = link_cmd + [str(o) for o in objs] + ["-o", str(tmp)]
         proc = subprocess.run(cmd, capture_output=True, text=True)
         if proc.returncode != 0:
             sys.stderr.write(proc.stdout + proc.stderr)
+            tmp.unlink(missing_ok=True)
             raise RuntimeError(f"link of {out} failed")
+        os.replace(tmp, out)
         changed = True
     return changed
 

@@ -2,8 +2,12 @@
 // Replaces the FlashAttention-2 varlen call of the reference
 // (lorafusion/patch/patch_transformers.py:150-159).
 //
-// One CTA handles one 128-row query tile of one sequence for one query head:
-//   warp 0      TMA producer: Q once, then (K, V) tiles through a 2-stage ring
+// One CTA handles one 128-row query tile of one sequence for one KV head and walks the query
+// heads of that head's group one after the other ("persistent" over the group): TMEM, the
+// barriers and the K/V ring are set up once, and the next head's Q and first K/V tiles are
+// already on their way while the current head is normalised and stored.  With one CTA per
+// (tile, query head) the fixed cost per CTA was two thirds of the time on short sequences.
+//   warp 0      TMA producer: per head Q, then (K, V) tiles through a 2-stage ring
 //   warp 1      tcgen05.mma issuer: S = Q K^T into one of two TMEM buffers, O += P V
 //   warps 2..9  softmax: read S from TMEM (two threads per row, 64 key columns each), online
 //               max/sum with lazy rescaling of O (only when the running max grows by more
@@ -54,7 +58,9 @@ attn_fwd_kernel(const AttnFwdParams p, const __grid_constant__ CUtensorMap tm) {
   uint64_t* p_full = bars + 9;
   uint64_t* pv_done = bars + 10;
   uint64_t* x_full = bars + 11;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+  uint64_t* q_empty = bars + 12;  // every S = Q K^T of the current head has completed: sQ may be refilled
+  uint64_t* o_empty = bars + 13;  // the softmax warps have read the finished O: the next head may overwrite it
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   float* xchg = reinterpret_cast<float*>(smem + ATT_TILE_BYTES * 6 + 256);
 
@@ -62,9 +68,11 @@ attn_fwd_kernel(const AttnFwdParams p, const __grid_constant__ CUtensorMap tm) {
   AbortCtx ctx{p.err, abort_flag};
   const int4 tile = p.tiles[blockIdx.x];
   const int row0 = tile.x, rows = tile.y, seq_row0 = tile.z;
-  const int h = blockIdx.y;
-  const int g = h / (p.Hq / p.Hkv);
+  const int g = blockIdx.y;            // KV head
+  const int group = p.Hq / p.Hkv;      // query heads that share it, walked in turn
+  const int h0 = g * group;
   const int n_kv = (row0 - seq_row0) / ATT_TILE + 1;
+  const int total = group * n_kv;      // the flat (head, key tile) sequence J = hi * n_kv + j
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
@@ -77,6 +85,8 @@ attn_fwd_kernel(const AttnFwdParams p, const __grid_constant__ CUtensorMap tm) {
     mbar_init(p_full, 256);
     mbar_init(pv_done, 1);
     mbar_init(x_full, 256);
+    mbar_init(q_empty, 1);
+    mbar_init(o_empty, 256);
     *abort_flag = 0;
     fence_mbar_init();
     tma_prefetch_desc(&tm);
@@ -94,16 +104,31 @@ attn_fwd_kernel(const AttnFwdParams p, const __grid_constant__ CUtensorMap tm) {
 
   if (warp == 0) {
     if (lane == 0) {
-      mbar_expect_tx(q_full, ATT_TILE_BYTES);
-      att_load_tile(sQ, &tm, q_full, p.q_col0 + h * ATT_D, row0);
-      for (int j = 0; j < n_kv; ++j) {
-        const int s = j & 1;
-        if (!mbar_wait(&kv_empty[s], ((j >> 1) & 1) ^ 1, ctx, ERR_WAIT_EMPTY)) break;
-        mbar_expect_tx(&kv_full[s], 2 * ATT_TILE_BYTES);
-        uint8_t* sK = sKV + s * 2 * ATT_TILE_BYTES;
-        att_load_tile(sK, &tm, &kv_full[s], p.k_col0 + g * ATT_D, seq_row0 + j * ATT_TILE);
-        att_load_tile(sK + ATT_TILE_BYTES, &tm, &kv_full[s], p.v_col0 + g * ATT_D,
-                      seq_row0 + j * ATT_TILE);
+      bool ok = true;
+      for (int hi = 0; ok && hi < group; ++hi) {
+        for (int j = 0; j < n_kv; ++j) {
+          const int J = hi * n_kv + j;
+          const int s = J & 1;
+          if (!mbar_wait(&kv_empty[s], ((J >> 1) & 1) ^ 1, ctx, ERR_WAIT_EMPTY)) {
+            ok = false;
+            break;
+          }
+          mbar_expect_tx(&kv_full[s], 2 * ATT_TILE_BYTES);
+          uint8_t* sK = sKV + s * 2 * ATT_TILE_BYTES;
+          att_load_tile(sK, &tm, &kv_full[s], p.k_col0 + g * ATT_D, seq_row0 + j * ATT_TILE);
+          att_load_tile(sK + ATT_TILE_BYTES, &tm, &kv_full[s], p.v_col0 + g * ATT_D,
+                        seq_row0 + j * ATT_TILE);
+          if (j == 0) {
+            // Q of this head, right behind its first K/V tile; the single Q buffer is free once
+            // the previous head's last S product has completed
+            if (hi > 0 && !mbar_wait(q_empty, (hi - 1) & 1, ctx, ERR_WAIT_EMPTY)) {
+              ok = false;
+              break;
+            }
+            mbar_expect_tx(q_full, ATT_TILE_BYTES);
+            att_load_tile(sQ, &tm, q_full, p.q_col0 + (h0 + hi) * ATT_D, row0);
+          }
+        }
       }
     }
   } else if (warp == 1) {
@@ -114,12 +139,19 @@ attn_fwd_kernel(const AttnFwdParams p, const __grid_constant__ CUtensorMap tm) {
         tc_fence_after_sync();
         att_mma_kk(tS[0], smem_u32(sQ), smem_u32(sKV), false);
         tc_commit(&s_full[0]);
+        if (n_kv == 1) tc_commit(q_empty);
       }
-      for (int j = 0; ok && j < n_kv; ++j) {
-        if (j + 1 < n_kv) {
-          const int s1 = (j + 1) & 1;
-          const uint32_t ph = ((j + 1) >> 1) & 1;
-          if (!mbar_wait(&kv_full[s1], ph, ctx, ERR_WAIT_FULL) ||
+      for (int J = 0; ok && J < total; ++J) {
+        const int hi = J / n_kv, j = J - hi * n_kv;
+        if (J + 1 < total) {
+          // S of the next element of the sequence goes out before this element's P V, so that
+          // the softmax warps always have a tile waiting (two S buffers in TMEM)
+          const int J1 = J + 1;
+          const int hi1 = J1 / n_kv, j1 = J1 - hi1 * n_kv;
+          const int s1 = J1 & 1;
+          const uint32_t ph = (J1 >> 1) & 1;
+          if ((j1 == 0 && !mbar_wait(q_full, hi1 & 1, ctx, ERR_WAIT_FULL)) ||
+              !mbar_wait(&kv_full[s1], ph, ctx, ERR_WAIT_FULL) ||
               !mbar_wait(&s_empty[s1], ph ^ 1, ctx, ERR_WAIT_TMEM_EMPTY)) {
             ok = false;
             break;
@@ -127,15 +159,17 @@ attn_fwd_kernel(const AttnFwdParams p, const __grid_constant__ CUtensorMap tm) {
           tc_fence_after_sync();
           att_mma_kk(tS[s1], smem_u32(sQ), smem_u32(sKV + s1 * 2 * ATT_TILE_BYTES), false);
           tc_commit(&s_full[s1]);
+          if (j1 == n_kv - 1) tc_commit(q_empty);  // last use of this head's Q
         }
-        if (!mbar_wait(p_full, j & 1, ctx, ERR_WAIT_READY)) {
+        if (!mbar_wait(p_full, J & 1, ctx, ERR_WAIT_READY) ||
+            (j == 0 && hi > 0 && !mbar_wait(o_empty, (hi - 1) & 1, ctx, ERR_WAIT_TMEM_EMPTY))) {
           ok = false;
           break;
         }
         tc_fence_after_sync();
-        att_mma_kmn(tO, smem_u32(sP), smem_u32(sKV + (j & 1) * 2 * ATT_TILE_BYTES + ATT_TILE_BYTES),
+        att_mma_kmn(tO, smem_u32(sP), smem_u32(sKV + (J & 1) * 2 * ATT_TILE_BYTES + ATT_TILE_BYTES),
                     j > 0);
-        tc_commit(&kv_empty[j & 1]);
+        tc_commit(&kv_empty[J & 1]);
         tc_commit(pv_done);
       }
     }
@@ -149,97 +183,106 @@ attn_fwd_kernel(const AttnFwdParams p, const __grid_constant__ CUtensorMap tm) {
     const int r = q * 32 + lane;  // row inside the tile
     const int c0 = half * 64;
     const uint32_t lane_addr = uint32_t(q * 32) << 16;
-    float m_ref = -INFINITY, l = 0.f;
     const float c = p.scale_log2e;
     bool ok = true;
-    for (int j = 0; j < n_kv; ++j) {
-      const int b = j & 1;
-      if (!mbar_wait(&s_full[b], (j >> 1) & 1, ctx, ERR_WAIT_TMEM_FULL)) {
-        ok = false;
-        break;
-      }
-      tc_fence_after_sync();
-      float s[64];
-#pragma unroll
-      for (int cc = 0; cc < 2; ++cc) {
-        uint32_t(&dst)[32] = *reinterpret_cast<uint32_t(*)[32]>(&s[cc * 32]);
-        tmem_ld_32x32b_x32(tS[b] + lane_addr + c0 + cc * 32, dst);
-      }
-      tmem_ld_wait();
-      tc_fence_before_sync();
-      mbar_arrive(&s_empty[b]);
-      if (j == n_kv - 1) {
-#pragma unroll
-        for (int col = 0; col < 64; ++col)
-          if (c0 + col > r) s[col] = -INFINITY;
-      }
-      float mx = s[0];
-#pragma unroll
-      for (int col = 1; col < 64; ++col) mx = fmaxf(mx, s[col]);
-      xchg[b * 256 + half * 128 + r] = mx;
-      mbar_arrive(x_full);
-      if (!mbar_wait(x_full, j & 1, ctx, ERR_WAIT_MISC)) {
-        ok = false;
-        break;
-      }
-      mx = fmaxf(mx, xchg[b * 256 + (half ^ 1) * 128 + r]);
-      float alpha = 1.f;
-      bool need = false;
-      if (j == 0) {
-        m_ref = mx;
-      } else {
-        need = (mx - m_ref) * c > 8.f;
-        if (need) {
-          alpha = exp2f((m_ref - mx) * c);
-          m_ref = mx;
-          l *= alpha;
-        }
-      }
-      const bool warp_need = __any_sync(0xffffffffu, need);
-      const float mc = m_ref * c;
-      float sum = 0.f;
-#pragma unroll
-      for (int col = 0; col < 64; ++col) {
-        s[col] = exp2f(s[col] * c - mc);
-        sum += s[col];
-      }
-      l += sum;
-      if (j > 0) {
-        if (!mbar_wait(pv_done, (j - 1) & 1, ctx, ERR_WAIT_MISC)) {
+    for (int hi = 0; ok && hi < group; ++hi) {
+      const int h = h0 + hi;
+      float m_ref = -INFINITY, l = 0.f;
+      for (int j = 0; j < n_kv; ++j) {
+        const int J = hi * n_kv + j;          // position in the flat sequence: S / P / K-V ring parities
+        const int X = hi * (n_kv + 1) + j;    // exchanges through shared memory so far (one more per head)
+        const int b = J & 1, xb = X & 1;
+        if (!mbar_wait(&s_full[b], (J >> 1) & 1, ctx, ERR_WAIT_TMEM_FULL)) {
           ok = false;
           break;
         }
         tc_fence_after_sync();
-      }
+        float s[64];
 #pragma unroll
-      for (int cc = 0; cc < 2; ++cc) {
-        float(&src)[32] = *reinterpret_cast<float(*)[32]>(&s[cc * 32]);
-        att_store_row_chunk(sP, r, c0 + cc * 32, src);
-      }
-      if (warp_need) {
-#pragma unroll 1
         for (int cc = 0; cc < 2; ++cc) {
-          uint32_t o[32];
-          tmem_ld_32x32b_x32(tO + lane_addr + c0 + cc * 32, o);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-          tmem_st_32x32b_x32(tO + lane_addr + c0 + cc * 32, o);
+          uint32_t(&dst)[32] = *reinterpret_cast<uint32_t(*)[32]>(&s[cc * 32]);
+          tmem_ld_32x32b_x32(tS[b] + lane_addr + c0 + cc * 32, dst);
         }
-        tmem_st_wait();
+        tmem_ld_wait();
+        tc_fence_before_sync();
+        mbar_arrive(&s_empty[b]);
+        if (j == n_kv - 1) {
+#pragma unroll
+          for (int col = 0; col < 64; ++col)
+            if (c0 + col > r) s[col] = -INFINITY;
+        }
+        float mx = s[0];
+#pragma unroll
+        for (int col = 1; col < 64; ++col) mx = fmaxf(mx, s[col]);
+        xchg[xb * 256 + half * 128 + r] = mx;
+        mbar_arrive(x_full);
+        if (!mbar_wait(x_full, X & 1, ctx, ERR_WAIT_MISC)) {
+          ok = false;
+          break;
+        }
+        mx = fmaxf(mx, xchg[xb * 256 + (half ^ 1) * 128 + r]);
+        float alpha = 1.f;
+        bool need = false;
+        if (j == 0) {
+          m_ref = mx;
+        } else {
+          need = (mx - m_ref) * c > 8.f;
+          if (need) {
+            alpha = exp2f((m_ref - mx) * c);
+            m_ref = mx;
+            l *= alpha;
+          }
+        }
+        const bool warp_need = __any_sync(0xffffffffu, need);
+        const float mc = m_ref * c;
+        float sum = 0.f;
+#pragma unroll
+        for (int col = 0; col < 64; ++col) {
+          s[col] = exp2f(s[col] * c - mc);
+          sum += s[col];
+        }
+        l += sum;
+        if (j > 0) {
+          // (for j == 0 the previous head's last P V was awaited by that head's final store)
+          if (!mbar_wait(pv_done, (J - 1) & 1, ctx, ERR_WAIT_MISC)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+        }
+#pragma unroll
+        for (int cc = 0; cc < 2; ++cc) {
+          float(&src)[32] = *reinterpret_cast<float(*)[32]>(&s[cc * 32]);
+          att_store_row_chunk(sP, r, c0 + cc * 32, src);
+        }
+        if (warp_need) {
+#pragma unroll 1
+          for (int cc = 0; cc < 2; ++cc) {
+            uint32_t o[32];
+            tmem_ld_32x32b_x32(tO + lane_addr + c0 + cc * 32, o);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st_32x32b_x32(tO + lane_addr + c0 + cc * 32, o);
+          }
+          tmem_st_wait();
+        }
+        fence_proxy_async_smem();
+        tc_fence_before_sync();
+        mbar_arrive(p_full);
       }
-      fence_proxy_async_smem();
-      tc_fence_before_sync();
-      mbar_arrive(p_full);
-    }
-    if (ok) {
-      // combine the two partial row sums (both were kept relative to the same m_ref)
+      if (!ok) break;
+      // ---- this head is complete: combine the two partial row sums (both relative to the same
+      // m_ref), normalise, store, and hand the O accumulator to the next head
+      const int Xs = hi * (n_kv + 1) + n_kv;
       xchg[512 + half * 128 + r] = l;
       mbar_arrive(x_full);
-      ok = mbar_wait(x_full, n_kv & 1, ctx, ERR_WAIT_MISC);
-      if (ok) l += xchg[512 + (half ^ 1) * 128 + r];
-    }
-    if (ok && mbar_wait(pv_done, (n_kv - 1) & 1, ctx, ERR_WAIT_MISC)) {
+      if (!mbar_wait(x_full, Xs & 1, ctx, ERR_WAIT_MISC) ||
+          !mbar_wait(pv_done, (hi * n_kv + n_kv - 1) & 1, ctx, ERR_WAIT_MISC)) {
+        ok = false;
+        break;
+      }
+      l += xchg[512 + (half ^ 1) * 128 + r];
       tc_fence_after_sync();
       const float inv_l = 1.f / l;
       const long long grow = (long long)row0 + r;
@@ -261,6 +304,8 @@ attn_fwd_kernel(const AttnFwdParams p, const __grid_constant__ CUtensorMap tm) {
         }
       }
       if (half == 0 && r < rows) p.lse[(long long)h * p.M_total + grow] = m_ref * p.scale + __logf(l);
+      tc_fence_before_sync();
+      mbar_arrive(o_empty);
     }
   }
 
@@ -308,7 +353,7 @@ extern "C" int lf_attn_fwd(const void* qkv, long long M, long long ld_qkv, int q
   p.scale = scale;
   p.scale_log2e = scale * 1.4426950408889634f;
   p.err = err;
-  dim3 grid(num_tiles, Hq);
+  dim3 grid(num_tiles, Hkv);  // one CTA per (query tile, KV head); it walks the group's query heads
   attn_fwd_kernel<<<grid, FWD_THREADS, FWD_SMEM, (cudaStream_t)stream>>>(p, tm);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
