@@ -1,6 +1,7 @@
 // Backward of the causal varlen GQA attention (head_dim 128) on sm_100a, as three kernels:
 //   1. attn_delta_kernel : delta[h, m] = sum_d O[m, h, d] * dO[m, h, d]
-//   2. attn_dq_kernel    : one CTA per (query tile, query head) loops over key tiles,
+//   2. attn_dq_kernel    : one CTA per (query tile, kv head) walks the group's query heads and
+//                          for each loops over key tiles,
 //                          recomputes P from the saved log-sum-exp and accumulates
 //                          dQ += dS K in TMEM.
 //   3. attn_dkdv_kernel  : one CTA per (key tile, kv head) loops over the query heads of
@@ -79,16 +80,22 @@ attn_dq_kernel(const AttnBwdParams p, const __grid_constant__ CUtensorMap tmQKV,
   uint64_t* sdp_empty = bars + 6;
   uint64_t* ds_full = bars + 7;
   uint64_t* dq_done = bars + 8;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+  uint64_t* q_empty = bars + 9;    // every S / dP product of the current head has completed: sQ, sDO may be refilled
+  uint64_t* dq_empty = bars + 10;  // the finished dQ has been read: the next head may overwrite the accumulator
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   AbortCtx ctx{p.err, abort_flag};
   const int4 tile = p.tiles[blockIdx.x];
   const int row0 = tile.x, rows = tile.y, seq_row0 = tile.z;
-  const int h = blockIdx.y;
-  const int g = h / (p.Hq / p.Hkv);
+  // One CTA per (query tile, KV head): it walks the query heads of the group one after the
+  // other, so TMEM, barriers and the K/V ring are set up once (see attn_fwd.cu).
+  const int g = blockIdx.y;
+  const int group = p.Hq / p.Hkv;
+  const int h0 = g * group;
   const int n_kv = (row0 - seq_row0) / ATT_TILE + 1;
+  const int total = group * n_kv;  // flat (head, key tile) sequence J = hi * n_kv + j
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
@@ -100,6 +107,8 @@ attn_dq_kernel(const AttnBwdParams p, const __grid_constant__ CUtensorMap tmQKV,
     mbar_init(sdp_empty, 256);
     mbar_init(ds_full, 256);
     mbar_init(dq_done, 1);
+    mbar_init(q_empty, 1);
+    mbar_init(dq_empty, 256);
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -115,27 +124,42 @@ attn_dq_kernel(const AttnBwdParams p, const __grid_constant__ CUtensorMap tmQKV,
 
   if (warp == 0) {
     if (lane == 0) {
-      mbar_expect_tx(q_full, 2 * ATT_TILE_BYTES);
-      att_load_tile(sQ, &tmQKV, q_full, p.q_col0 + h * ATT_D, row0);
-      att_load_tile(sDO, &tmDO, q_full, h * ATT_D, row0);
-      for (int j = 0; j < n_kv; ++j) {
-        const int s = j & 1;
-        if (!mbar_wait(&kv_empty[s], ((j >> 1) & 1) ^ 1, ctx, ERR_WAIT_EMPTY)) break;
-        mbar_expect_tx(&kv_full[s], 2 * ATT_TILE_BYTES);
-        uint8_t* sK = sKV + s * 2 * ATT_TILE_BYTES;
-        att_load_tile(sK, &tmQKV, &kv_full[s], p.k_col0 + g * ATT_D, seq_row0 + j * ATT_TILE);
-        att_load_tile(sK + ATT_TILE_BYTES, &tmQKV, &kv_full[s], p.v_col0 + g * ATT_D,
-                      seq_row0 + j * ATT_TILE);
+      bool ok = true;
+      for (int hi = 0; ok && hi < group; ++hi) {
+        for (int j = 0; j < n_kv; ++j) {
+          const int J = hi * n_kv + j;
+          const int s = J & 1;
+          if (!mbar_wait(&kv_empty[s], ((J >> 1) & 1) ^ 1, ctx, ERR_WAIT_EMPTY)) {
+            ok = false;
+            break;
+          }
+          mbar_expect_tx(&kv_full[s], 2 * ATT_TILE_BYTES);
+          uint8_t* sK = sKV + s * 2 * ATT_TILE_BYTES;
+          att_load_tile(sK, &tmQKV, &kv_full[s], p.k_col0 + g * ATT_D, seq_row0 + j * ATT_TILE);
+          att_load_tile(sK + ATT_TILE_BYTES, &tmQKV, &kv_full[s], p.v_col0 + g * ATT_D,
+                        seq_row0 + j * ATT_TILE);
+          if (j == 0) {
+            if (hi > 0 && !mbar_wait(q_empty, (hi - 1) & 1, ctx, ERR_WAIT_EMPTY)) {
+              ok = false;
+              break;
+            }
+            mbar_expect_tx(q_full, 2 * ATT_TILE_BYTES);
+            att_load_tile(sQ, &tmQKV, q_full, p.q_col0 + (h0 + hi) * ATT_D, row0);
+            att_load_tile(sDO, &tmDO, q_full, (h0 + hi) * ATT_D, row0);
+          }
+        }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      bool ok = mbar_wait(q_full, 0, ctx, ERR_WAIT_FULL);
-      for (int j = 0; ok && j < n_kv; ++j) {
-        const int s = j & 1;
+      bool ok = true;
+      for (int J = 0; ok && J < total; ++J) {
+        const int hi = J / n_kv, j = J - hi * n_kv;
+        const int s = J & 1;
         const uint32_t sK = smem_u32(sKV + s * 2 * ATT_TILE_BYTES);
-        if (!mbar_wait(&kv_full[s], (j >> 1) & 1, ctx, ERR_WAIT_FULL) ||
-            !mbar_wait(sdp_empty, (j & 1) ^ 1, ctx, ERR_WAIT_TMEM_EMPTY)) {
+        if ((j == 0 && !mbar_wait(q_full, hi & 1, ctx, ERR_WAIT_FULL)) ||
+            !mbar_wait(&kv_full[s], (J >> 1) & 1, ctx, ERR_WAIT_FULL) ||
+            !mbar_wait(sdp_empty, (J & 1) ^ 1, ctx, ERR_WAIT_TMEM_EMPTY)) {
           ok = false;
           break;
         }
@@ -143,7 +167,9 @@ attn_dq_kernel(const AttnBwdParams p, const __grid_constant__ CUtensorMap tmQKV,
         att_mma_kk(tS, smem_u32(sQ), sK, false);
         att_mma_kk(tDP, smem_u32(sDO), sK + ATT_TILE_BYTES, false);
         tc_commit(sdp_full);
-        if (!mbar_wait(ds_full, j & 1, ctx, ERR_WAIT_READY)) {
+        if (j == n_kv - 1) tc_commit(q_empty);  // last use of this head's Q and dO
+        if (!mbar_wait(ds_full, J & 1, ctx, ERR_WAIT_READY) ||
+            (j == 0 && hi > 0 && !mbar_wait(dq_empty, (hi - 1) & 1, ctx, ERR_WAIT_TMEM_EMPTY))) {
           ok = false;
           break;
         }
@@ -160,42 +186,51 @@ attn_dq_kernel(const AttnBwdParams p, const __grid_constant__ CUtensorMap tmQKV,
     const uint32_t lane_addr = uint32_t(q * 32) << 16;
     const long long grow = (long long)row0 + r;
     const bool row_valid = r < rows;
-    const float lse2 = row_valid ? p.lse[(long long)h * p.M_total + grow] * 1.4426950408889634f : 0.f;
-    const float dlt = row_valid ? p.delta[(long long)h * p.M_total + grow] : 0.f;
     bool ok = true;
-    for (int j = 0; j < n_kv; ++j) {
-      if (!mbar_wait(sdp_full, j & 1, ctx, ERR_WAIT_TMEM_FULL)) {
-        ok = false;
-        break;
-      }
-      if (j > 0 && !mbar_wait(dq_done, (j - 1) & 1, ctx, ERR_WAIT_MISC)) {
-        ok = false;
-        break;
-      }
-      tc_fence_after_sync();
-      const bool diag = (j == n_kv - 1);
-#pragma unroll 1
-      for (int cc = 0; cc < 2; ++cc) {
-        uint32_t sv[32], dv[32];
-        tmem_ld_32x32b_x32(tS + lane_addr + c0 + cc * 32, sv);
-        tmem_ld_32x32b_x32(tDP + lane_addr + c0 + cc * 32, dv);
-        tmem_ld_wait();
-        float ds[32];
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int col = c0 + cc * 32 + i;
-          float pv = exp2f(__uint_as_float(sv[i]) * p.scale_log2e - lse2);
-          if (!row_valid || (diag && col > r)) pv = 0.f;
-          ds[i] = pv * (__uint_as_float(dv[i]) - dlt) * p.scale;
+    for (int hi = 0; ok && hi < group; ++hi) {
+      const int h = h0 + hi;
+      const float lse2 = row_valid ? p.lse[(long long)h * p.M_total + grow] * 1.4426950408889634f : 0.f;
+      const float dlt = row_valid ? p.delta[(long long)h * p.M_total + grow] : 0.f;
+      for (int j = 0; j < n_kv; ++j) {
+        const int J = hi * n_kv + j;
+        if (!mbar_wait(sdp_full, J & 1, ctx, ERR_WAIT_TMEM_FULL)) {
+          ok = false;
+          break;
         }
-        att_store_row_chunk(sDS, r, c0 + cc * 32, ds);
+        // sDS is still being read by the previous tile's dQ product (for j == 0 the previous
+        // head's final store has already waited for it)
+        if (j > 0 && !mbar_wait(dq_done, (J - 1) & 1, ctx, ERR_WAIT_MISC)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        const bool diag = (j == n_kv - 1);
+#pragma unroll 1
+        for (int cc = 0; cc < 2; ++cc) {
+          uint32_t sv[32], dv[32];
+          tmem_ld_32x32b_x32(tS + lane_addr + c0 + cc * 32, sv);
+          tmem_ld_32x32b_x32(tDP + lane_addr + c0 + cc * 32, dv);
+          tmem_ld_wait();
+          float ds[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int col = c0 + cc * 32 + i;
+            float pv = exp2f(__uint_as_float(sv[i]) * p.scale_log2e - lse2);
+            if (!row_valid || (diag && col > r)) pv = 0.f;
+            ds[i] = pv * (__uint_as_float(dv[i]) - dlt) * p.scale;
+          }
+          att_store_row_chunk(sDS, r, c0 + cc * 32, ds);
+        }
+        tc_fence_before_sync();
+        mbar_arrive(sdp_empty);
+        fence_proxy_async_smem();
+        mbar_arrive(ds_full);
       }
-      tc_fence_before_sync();
-      mbar_arrive(sdp_empty);
-      fence_proxy_async_smem();
-      mbar_arrive(ds_full);
-    }
-    if (ok && mbar_wait(dq_done, (n_kv - 1) & 1, ctx, ERR_WAIT_MISC)) {
+      if (!ok) break;
+      if (!mbar_wait(dq_done, (hi * n_kv + n_kv - 1) & 1, ctx, ERR_WAIT_MISC)) {
+        ok = false;
+        break;
+      }
       tc_fence_after_sync();
       __nv_bfloat16* orow = p.dqkv + grow * p.ld_qkv + p.q_col0 + h * ATT_D + c0;
 #pragma unroll 1
@@ -213,6 +248,8 @@ attn_dq_kernel(const AttnBwdParams p, const __grid_constant__ CUtensorMap tmQKV,
                          pack_bf16x2(__uint_as_float(o[gq * 8 + 6]), __uint_as_float(o[gq * 8 + 7])));
         }
       }
+      tc_fence_before_sync();
+      mbar_arrive(dq_empty);
     }
   }
 
@@ -494,7 +531,7 @@ extern "C" int lf_attn_bwd(const void* qkv, const void* out, const void* d_out, 
   p.scale = scale;
   p.scale_log2e = scale * 1.4426950408889634f;
   p.err = err;
-  attn_dq_kernel<<<dim3(num_tiles, Hq), BWD_THREADS, BWD_SMEM, st>>>(p, tmQKV, tmDO);
+  attn_dq_kernel<<<dim3(num_tiles, Hkv), BWD_THREADS, BWD_SMEM, st>>>(p, tmQKV, tmDO);  // walks the group's q heads
   attn_dkdv_kernel<<<dim3(num_tiles, Hkv), BWD_THREADS, BWD_SMEM, st>>>(p, tmQKV, tmDO);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }

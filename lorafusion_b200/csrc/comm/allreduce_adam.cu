@@ -61,6 +61,9 @@ struct ArAdamParams {
   unsigned int* done_counter;        // local, zero before launch, reset by the kernel
   float lr, beta1, beta2, eps, weight_decay, bias_c1, bias_c2, grad_scale;
   int* err;
+  // optional [gridDim.x, 3] nanosecond stamps (globaltimer): block entry, every rank's gradients
+  // seen complete, block exit -- what a trace needs to tell waiting for peers from working
+  unsigned long long* trace;
 };
 
 __device__ __forceinline__ float4 multimem_ld_reduce_f32x4(const float* mc_ptr) {
@@ -97,6 +100,7 @@ allreduce_adam_kernel(const ArAdamParams p) {
   if (threadIdx.x == 0) abort_smem = 0;
   __syncthreads();
   AbortCtx ctx{p.err, &abort_smem};
+  if (p.trace != nullptr && threadIdx.x == 0) p.trace[3 * blockIdx.x] = globaltimer_ns();
 
   // ---- phase 0: every rank's gradients are complete ---------------------------------
   if (p.sync_mode) {
@@ -110,6 +114,7 @@ allreduce_adam_kernel(const ArAdamParams p) {
     __syncthreads();
   }
 
+  if (p.trace != nullptr && threadIdx.x == 0) p.trace[3 * blockIdx.x + 1] = globaltimer_ns();
   if (!aborted(ctx)) {
     const ArAdamWorkItem item = p.items[blockIdx.x];
     const ArAdamChunk c = p.chunks[item.chunk];
@@ -209,6 +214,7 @@ allreduce_adam_kernel(const ArAdamParams p) {
       if (threadIdx.x == 0) *p.done_counter = 0u;
     }
   }
+  if (p.trace != nullptr && threadIdx.x == 0) p.trace[3 * blockIdx.x + 2] = globaltimer_ns();
 }
 
 }  // namespace lf
@@ -233,6 +239,7 @@ typedef struct LfArAdamArgs {
   int num_chunks, rank, world, epoch, sync_mode, use_multimem, step;
   int wait_ms;  // limit of the cross-rank flag waits in milliseconds; 0 = the 10 s default
   float lr, beta1, beta2, eps, weight_decay, grad_scale;
+  void* trace;  // optional device uint64 [num_items, 3]: entry / peers ready / exit stamps in ns
 } LfArAdamArgs;
 
 extern "C" int lf_allreduce_adam(const LfArAdamArgs* a) {
@@ -267,6 +274,7 @@ extern "C" int lf_allreduce_adam(const LfArAdamArgs* a) {
   p.bias_c2 = 1.f - powf(a->beta2, (float)a->step);
   p.grad_scale = a->grad_scale;
   p.err = (int*)a->err;
+  p.trace = (unsigned long long*)a->trace;
   p.wait_ns = a->wait_ms > 0 ? (unsigned long long)a->wait_ms * 1000000ull : kPeerWaitNs;
   if (p.sync_mode && p.done_counter == nullptr) return -2;
   // Blocks only ever wait on flags written by other GPUs, never on sibling blocks, so the

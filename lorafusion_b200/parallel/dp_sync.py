@@ -41,6 +41,7 @@ class LfArAdamArgs(C.Structure):
         ("sync_mode", C.c_int), ("use_multimem", C.c_int), ("step", C.c_int), ("wait_ms", C.c_int),
         ("lr", C.c_float), ("beta1", C.c_float), ("beta2", C.c_float), ("eps", C.c_float),
         ("weight_decay", C.c_float), ("grad_scale", C.c_float),
+        ("trace", C.c_void_p),
     ]
 
 
@@ -48,7 +49,11 @@ def launch_allreduce_adam(*, chunks: torch.Tensor, items: Optional[torch.Tensor]
                           master: torch.Tensor, m: torch.Tensor, v: torch.Tensor, flag_ptrs,
                           done_counter: Optional[torch.Tensor], rank: int, world: int, epoch: int,
                           sync: bool, use_multimem: bool, step: int, lr: float, beta1: float, beta2: float,
-                          eps: float, weight_decay: float, grad_scale: float, device, wait_ms: int = 0) -> None:
+                          eps: float, weight_decay: float, grad_scale: float, device, wait_ms: int = 0,
+                          trace: Optional[torch.Tensor] = None) -> None:
+    """``trace`` (optional, int64 ``[num_items, 3]`` on the device) receives per block the
+    ``globaltimer`` nanoseconds at entry, when every rank's gradients were seen complete, and at
+    exit (see :func:`summarize_sync_trace`)."""
     lib = nv.cuda_lib()
     if not getattr(lib, "_lf_ar_declared", False):
         lib.lf_allreduce_adam.argtypes = [C.POINTER(LfArAdamArgs)]
@@ -75,10 +80,27 @@ def launch_allreduce_adam(*, chunks: torch.Tensor, items: Optional[torch.Tensor]
     a.wait_ms = int(wait_ms)  # 0 = default limit (10 s) of the cross-rank flag waits
     a.lr, a.beta1, a.beta2, a.eps = lr, beta1, beta2, eps
     a.weight_decay, a.grad_scale = weight_decay, grad_scale
+    if trace is not None:
+        if trace.dtype != torch.int64 or trace.numel() < 3 * items.shape[0]:
+            raise ValueError("trace must be int64 with at least 3 entries per work item")
+        a.trace = trace.data_ptr()
     nv.note_launch()
     rc = lib.lf_allreduce_adam(C.byref(a))
     if rc != 0:
         raise RuntimeError(f"lf_allreduce_adam failed with code {rc}")
+
+
+def summarize_sync_trace(trace: torch.Tensor, num_items: int) -> dict:
+    """Microseconds from the in-kernel stamps of one launch: how long the first block waited
+    for the peers' gradients, how long the reduce + Adam + broadcast part took, and the span of
+    the whole kernel on the device (same clock for every kernel of a GPU, so spans of different
+    kernels can be laid over each other to see overlap)."""
+    t = trace[:3 * num_items].view(num_items, 3).cpu()
+    t0, t1, t2 = t[:, 0], t[:, 1], t[:, 2]
+    return {"start_ns": int(t0.min()), "end_ns": int(t2.max()),
+            "span_us": float(t2.max() - t0.min()) / 1e3,
+            "max_wait_for_peers_us": float((t1 - t0).max()) / 1e3,
+            "mean_work_us": float((t2 - t1).double().mean()) / 1e3}
 
 
 class FusedGradSync:
@@ -97,6 +119,8 @@ class FusedGradSync:
         self.flags_h.tensor.zero_()
         self.done = torch.zeros(1, dtype=torch.int32, device=dev)
         self.epoch = 0
+        self.trace: Optional[torch.Tensor] = None   # set to an int64 device tensor to collect in-kernel stamps
+        self.last_num_items = 0
         self.use_multimem = bool(use_multimem and self.grad_h.has_multicast and self.work_h.has_multicast)
         if self.world > 1:
             torch.cuda.synchronize(dev)
@@ -129,7 +153,8 @@ class FusedGradSync:
             v=ar.v, flag_ptrs=self.flags_h.peer_ptrs, done_counter=self.done, rank=self.rank, world=self.world,
             epoch=self.epoch, sync=self.world > 1, use_multimem=self.use_multimem, step=step,
             lr=o.lr, beta1=o.beta1, beta2=o.beta2, eps=o.eps, weight_decay=o.weight_decay,
-            grad_scale=grad_scale, device=ar.device)
+            grad_scale=grad_scale, device=ar.device, trace=self.trace)
+        self.last_num_items = int(items.shape[0])
 
 
 class NcclGradSync:

@@ -139,6 +139,7 @@ def test_layer_group_launches_on_a_side_stream_equal_one_whole_launch():
         arenas.append(ar)
         syncs.append(FusedGradSync(ar, alloc, None, opt))
     side = torch.cuda.Stream()
+    syncs[0].trace = torch.zeros(3 * 4096, dtype=torch.int64, device="cuda")   # in-kernel time stamps
     for step in range(1, 3):
         g = torch.Generator(device="cuda").manual_seed(step)
         grad = torch.randn(arenas[0].numel, generator=g, device="cuda")
@@ -159,6 +160,11 @@ def test_layer_group_launches_on_a_side_stream_equal_one_whole_launch():
         for name in ("work", "master", "m", "v", "grad"):
             assert torch.equal(getattr(arenas[0], name), getattr(arenas[1], name)), (step, name)
     assert float(arenas[1].grad.abs().max()) == 0.0
+    from lorafusion_b200.parallel.dp_sync import summarize_sync_trace
+
+    tr = summarize_sync_trace(syncs[0].trace, syncs[0].last_num_items)
+    assert tr["end_ns"] > tr["start_ns"] > 0 and 0.0 < tr["span_us"] < 1e5
+    assert 0.0 <= tr["max_wait_for_peers_us"] <= tr["span_us"] and tr["mean_work_us"] > 0.0
 
 
 _CHILD = r"""
