@@ -90,7 +90,7 @@ def run(args) -> list:
     kw = dict(device=device, world=world, warmup=args.warmup, number=args.number)
 
     # ---------------- all-gather -> GEMM (column parallel) ----------------
-    for name, n_full in (("qkv", cfg.qkv_size), ("gate_up", 2 * I)):
+    for name, n_full in (() if args.only_dp else (("qkv", cfg.qkv_size), ("gate_up", 2 * I))):
         n_loc = n_full // world
         w = (torch.randn(n_loc, H, device=device) * 0.02).to(torch.bfloat16)
         x_loc = torch.randn(ms, H, device=device).to(torch.bfloat16)
@@ -119,7 +119,7 @@ def run(args) -> list:
         del w, out, gathered
 
     # ---------------- GEMM -> reduce-scatter (row parallel) ----------------
-    for name, k_full in (("o", cfg.q_size), ("down", I)):
+    for name, k_full in (() if args.only_dp else (("o", cfg.q_size), ("down", I))):
         k_loc = k_full // world
         w = (torch.randn(H, k_loc, device=device) * 0.02).to(torch.bfloat16)
         x = torch.randn(T, k_loc, device=device).to(torch.bfloat16)
@@ -174,6 +174,31 @@ def run(args) -> list:
             nccl.reduce_and_step(a, grad_scale=1.0 / world)
 
     t_f, t_u = _time(fused, **kw), _time(unfused, **kw)
+    extra = {}
+    if world > 1:
+        # where the fused kernel's time goes, from its own time stamps (one launch, adapter 0)
+        from ..parallel.dp_sync import summarize_sync_trace
+
+        fused_sync.trace = torch.zeros(3 * 65536, dtype=torch.int64, device=device)
+        fused_sync.reduce_and_step(0, grad_scale=1.0 / world)
+        torch.cuda.synchronize()
+        tr = summarize_sync_trace(fused_sync.trace, fused_sync.last_num_items)
+        extra["in_kernel_us"] = {k: round(v, 1) for k, v in tr.items() if k.endswith("_us")}
+        fused_sync.trace = None
+    if world > 1 and args.multimem:
+        # same kernel with NVLS: multimem.ld_reduce pulls the sum of all ranks' gradients through the
+        # switch, multimem.st broadcasts the new weights
+        arena_m = LoRAArena(cfg, adapters, range(layers), device, init_b_std=0.01, shared_alloc=alloc)
+        mm_sync = FusedGradSync(arena_m, alloc, group, optim, use_multimem=True)
+        if mm_sync.use_multimem:
+            def fused_mm():
+                for a in range(len(adapters)):
+                    mm_sync.reduce_and_step(a, grad_scale=1.0 / world)
+
+            extra["fused_multimem_ms"] = _time(fused_mm, **kw) * 1e3
+        else:
+            extra["fused_multimem_ms"] = None
+            extra["multimem_note"] = "no multicast address for the symmetric buffers on this system"
     n_pad = arena_f.numel
     n_train = sum(arena_f.trainable_numel(a) for a in range(len(adapters)))
     # per GPU: receive (world-1)/world of the fp32 gradients, send the same share of bf16 weights to each peer
@@ -183,7 +208,7 @@ def run(args) -> list:
     emit({"path": "LoRA grad reduce-scatter + AdamW + all-gather", "world": world,
           "shape": f"{layers} layers x 4 adapters r16: {n_pad / 1e6:.0f}M padded / {n_train / 1e6:.0f}M trainable elements",
           "fused_ms": t_f * 1e3, "nccl_allreduce_plus_adam_ms": t_u * 1e3, "speedup": t_u / t_f,
-          "roofline_ms": roof * 1e3, "roofline_fraction": roof / t_f,
+          "roofline_ms": roof * 1e3, "roofline_fraction": roof / t_f, **extra,
           "bound": "link" if link_bytes / (LINK_GBS * 1e9) >= hbm_bytes / 6546e9 / max(world, 1) else "hbm"})
     _native.check_device_errors()
     if world > 1:
@@ -197,6 +222,9 @@ def main(argv=None):
     ap.add_argument("--model", default="llama-3.1-70b")
     ap.add_argument("--tokens", type=int, default=16384)
     ap.add_argument("--dp-layers", type=int, default=8, help="layers of adapters in the gradient-sync case")
+    ap.add_argument("--multimem", action="store_true",
+                    help="also time the gradient-sync kernel on its NVLS path (multimem.ld_reduce / multimem.st)")
+    ap.add_argument("--only-dp", action="store_true", help="skip the tensor-parallel cases")
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--number", type=int, default=10)
     run(ap.parse_args(argv))
