@@ -90,6 +90,8 @@ typedef struct LfTpArgs {
 } LfTpArgs;
 
 int lf_gemm_tp(const LfGemmArgs* args, const LfTpArgs* tp);
+// CTA-pair (256 x 256 tile) variants of the same; -5 = shape not covered, use lf_gemm_tp.
+int lf_gemm_pair_tp(const LfGemmArgs* args, const LfTpArgs* tp);
 
 // NF4 main loop: `args->b` points at the PACKED weight (uint8 [w_rows, w_cols / 2], two 4-bit
 // codes per byte, even element in the high nibble) while b_rows / b_cols / b_ld / b_mn describe

@@ -25,6 +25,7 @@
 #include "../common/ptx.cuh"
 #include "../common/tensormap.h"
 #include "gemm_api.h"
+#include "tp_params.cuh"
 
 namespace lf {
 
@@ -79,27 +80,6 @@ __constant__ float kNf4Values[16] = {
 //           the memory of the rank that owns those token rows; four extra warps, concurrent
 //           with the GEMM, pull the partials of the rows this rank owns from every source with
 //           coalesced peer loads as their flags arrive and sum them in fp32 (+ residual).
-struct TpParams {
-  int rank, world, tiles_per_shard, epoch;
-  const int* ag_flags;
-  int* ag_peer_flags[8];
-  const __nv_bfloat16* ag_src;
-  long long ag_ld;
-  int ag_cols;
-  __nv_bfloat16* ag_peer_dst[8];
-  const __nv_bfloat16* ag2_src;
-  long long ag2_ld;
-  int ag2_cols;
-  __nv_bfloat16* ag2_peer_dst[8];
-  __nv_bfloat16* rs_peer_stage[8];
-  int* rs_peer_cnt[8];
-  const int* rs_cnt;
-  int rs_target;
-  __nv_bfloat16* rs_out;
-  long long rs_ldo;
-  const __nv_bfloat16* rs_residual;
-};
-
 struct TileCoord {
   int m0, n0, k0, nkb, adapter;
 };
@@ -144,7 +124,6 @@ struct SmemPlan {
   static constexpr int TOTAL = STAGES * STAGE_BYTES + BAR_BYTES + 1024;  // + alignment slack
 };
 
-constexpr int kNumCommWarps = 4;
 
 template <int BN, int NACC, bool A_MN, bool B_MN, bool B2_MN, int EPI, bool MASK_A, int TP = 0,
           bool NF4B = false>
@@ -928,30 +907,7 @@ static int gemm_entry(const LfGemmArgs* a, const LfTpArgs* t, const LfNf4Args* q
     if (a->seg_tiles != nullptr || a->mask_a) return -6;
     if (t->world < 1 || t->world > 8 || t->rank < 0 || t->rank >= t->world) return -7;
     if (kp.num_m_tiles != t->world * t->tiles_per_shard) return -8;
-    TpParams tp;
-    tp.rank = t->rank;
-    tp.world = t->world;
-    tp.tiles_per_shard = t->tiles_per_shard;
-    tp.epoch = t->epoch;
-    tp.ag_flags = (const int*)t->ag_flags;
-    tp.ag_src = (const __nv_bfloat16*)t->ag_src;
-    tp.ag_ld = t->ag_ld;
-    tp.ag_cols = t->ag_cols;
-    tp.ag2_src = (const __nv_bfloat16*)t->ag2_src;
-    tp.ag2_ld = t->ag2_ld;
-    tp.ag2_cols = t->ag2_cols;
-    for (int r = 0; r < 8; ++r) {
-      tp.ag_peer_flags[r] = (int*)t->ag_peer_flags[r];
-      tp.ag_peer_dst[r] = (__nv_bfloat16*)t->ag_peer_dst[r];
-      tp.ag2_peer_dst[r] = (__nv_bfloat16*)t->ag2_peer_dst[r];
-      tp.rs_peer_stage[r] = (__nv_bfloat16*)t->rs_peer_stage[r];
-      tp.rs_peer_cnt[r] = (int*)t->rs_peer_cnt[r];
-    }
-    tp.rs_cnt = (const int*)t->rs_cnt;
-    tp.rs_target = t->rs_target;
-    tp.rs_out = (__nv_bfloat16*)t->rs_out;
-    tp.rs_ldo = t->rs_ldo;
-    tp.rs_residual = (const __nv_bfloat16*)t->rs_residual;
+    TpParams tp = make_tp_params(t);
     // all-gather: start with this rank's own rows; reduce-scatter: finish with them
     kp.m_rotate = (t->mode == 1 ? t->rank : (t->rank + 1) % t->world) * t->tiles_per_shard;
     kp.group_m = t->tiles_per_shard < kp.group_m ? t->tiles_per_shard : kp.group_m;

@@ -28,6 +28,7 @@
 #include "../common/ptx.cuh"
 #include "../common/tensormap.h"
 #include "gemm_api.h"
+#include "tp_params.cuh"
 
 namespace lf {
 namespace pair {
@@ -60,6 +61,7 @@ struct Params {
   uint32_t seed_lo, seed_hi, stream_id;
   int row_offset, col_offset;
   int zero_row;  // a row coordinate outside A2: TMA reads zeros there
+  int m_rotate;  // pair rows the tile order is rotated by (tensor-parallel variants start / end with the own shard)
   int* err;
 };
 
@@ -75,7 +77,8 @@ __device__ __forceinline__ Tile decode(const Params& p, int idx) {
   const int first = g * p.group_m;
   const int gsz = min(p.group_m, p.num_pair_m - first);
   const int r = idx - g * per_group;
-  t.pm = first + r % gsz;
+  t.pm = first + r % gsz + p.m_rotate;
+  if (t.pm >= p.num_pair_m) t.pm -= p.num_pair_m;
   t.n_tile = r / gsz;
   const int mt0 = 2 * t.pm, mt1 = 2 * t.pm + 1;
   const int n_mt = (p.M + BM - 1) / BM;
@@ -99,12 +102,18 @@ __device__ __forceinline__ int slab_passes(const Tile& t, int (&ad)[2]) {
   return n;
 }
 
-template <bool B_MN, int NACC, int EPI>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1)
+// TP = 0: plain.  TP = 1: all-gather -> GEMM (four extra warps per CTA push this rank's token
+// shard to the peers; a CTA's producer waits for the flag of its own 128-row tile before the first
+// load).  TP = 2: GEMM -> reduce-scatter (each CTA leaves its 128 x 256 partial in this GPU's stage
+// and flags it at the owner of the rows; four extra warps per CTA pull and sum the partials of the
+// rows this rank owns).  Same protocol, flags and buffers as the single-CTA template in
+// umma_gemm.cu; 128-row tile granularity is kept because each CTA of a pair owns one such tile.
+template <bool B_MN, int NACC, int EPI, int TP = 0>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS + (TP != 0 ? 32 * kNumCommWarps : 0), 1)
     umma_gemm_pair_kernel(const Params p, const __grid_constant__ CUtensorMap tmA,
                           const __grid_constant__ CUtensorMap tmB,
                           const __grid_constant__ CUtensorMap tmA2,
-                          const __grid_constant__ CUtensorMap tmB2) {
+                          const __grid_constant__ CUtensorMap tmB2, const TpParams tp) {
   constexpr int NBUF = (NACC == 1) ? 2 : 1;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -159,6 +168,20 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1)
         const int n_slab = slab_passes(t, ad);
         const int my_adapter = cta == 0 ? t.a0 : t.a1;
         const int total = p.nkb_main + n_slab * p.nkb2;
+        if (TP == 1) {
+          // the rows of this CTA's A tile (and of its slab tile) come from rank `src`: they are
+          // in LOCAL memory once that rank has pushed them and raised the tile's flag
+          const int mt = m0 / BM;
+          const int src = mt / tp.tiles_per_shard;
+          if (src != tp.rank) {
+            if (!wait_flag_ge(tp.ag_flags + src * tp.tiles_per_shard + (mt - src * tp.tiles_per_shard), tp.epoch,
+                              ctx)) {
+              ok = false;
+              break;
+            }
+            fence_proxy_async_all();
+          }
+        }
         for (int kb = 0; kb < total; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
@@ -245,7 +268,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1)
         tc_commit_pair(mapa_shared(&tfull[buf], 1));
       }
     }
-  } else {
+  } else if (threadIdx.x < PAIR_THREADS) {
     // ------------------------------ epilogue (both CTAs) ------------------------------
     // Eight warps: two per TMEM lane quarter (a warp may only touch quarter warp % 4), each
     // taking half of the tile's columns.  The dropout-mixing variant has no second accumulator
@@ -261,7 +284,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1)
       const bool has_slab = p.nkb2 > 0 && my_adapter >= 0;
       const int buf = tile_iter % NBUF;
       const uint32_t bph = (tile_iter / NBUF) & 1;
-      if (!mbar_wait(&tfull[buf], bph, ctx, ERR_WAIT_TMEM_FULL)) {
+      bool got = mbar_wait(&tfull[buf], bph, ctx, ERR_WAIT_TMEM_FULL);
+      // the reduce-scatter epilogue ends in a named barrier of its 256 threads: one answer for all
+      if (TP == 2) got = named_bar_and<1, 32 * PAIR_EPI_WARPS>(got);
+      if (!got) {
         ok = false;
         break;
       }
@@ -308,7 +334,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1)
             if (col0 + j < p.N) v[j] += __bfloat162float(p.bias[col0 + j]);
         }
         if (row < p.M) {
-          __nv_bfloat16* out = p.out + (long long)row * p.ldo;
+          // reduce-scatter: the partial tile stays in THIS GPU's stage [M, N]; the owner pulls it
+          __nv_bfloat16* out = (TP == 2) ? tp.rs_peer_stage[tp.rank] + (long long)row * p.N
+                                         : p.out + (long long)row * p.ldo;
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
             const int col = col0 + g * 8;
@@ -325,6 +353,167 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1)
       }
       tc_fence_before_sync();
       mbar_arrive_cluster(mapa_shared(&tempty[buf], 0));
+      if (TP == 2) {
+        // all 256 epilogue threads of this CTA have stored their part of the 128 x 256 partial
+        __threadfence_system();
+        asm volatile("bar.sync 1, %0;" ::"n"(32 * PAIR_EPI_WARPS) : "memory");
+        if (threadIdx.x == 64) {
+          const int mt = 2 * t.pm + int(cta);
+          const int owner = mt / tp.tiles_per_shard;
+          st_release_sys(tp.rs_peer_cnt[owner] +
+                             (tp.rank * tp.tiles_per_shard + (mt - owner * tp.tiles_per_shard)) * p.num_n_tiles +
+                             t.n_tile,
+                         tp.epoch);
+        }
+      }
+    }
+  } else if (TP == 2) {
+    // ---- reduce the partials of the rows this rank owns, as they arrive ----
+    // Four dedicated warps, concurrent with the GEMM of the other warps: they poll the
+    // per-(source, row tile, column tile) flags and sum the bf16 partials in fp32 (+ residual).
+    // Every thread keeps the loads of two output vectors from all sources in flight.
+    const int et = threadIdx.x - PAIR_THREADS;  // 0..127
+    const int ms = tp.tiles_per_shard * BM;
+    const int items = tp.tiles_per_shard * p.num_n_tiles;
+    constexpr int VEC_PER_ROW = BN / 8;
+    constexpr int NV = BM * VEC_PER_ROW;
+    bool ok = true;
+    for (int item = blockIdx.x; ok && item < items; item += gridDim.x) {
+      const int lt = item / p.num_n_tiles, nt = item - lt * p.num_n_tiles;
+      if (et < tp.world) {
+        if (!wait_flag_ge(tp.rs_cnt + (et * tp.tiles_per_shard + lt) * p.num_n_tiles + nt, tp.epoch, ctx))
+          ok = false;
+      }
+      // one agreed answer for the 128 reduce threads (see named_bar_and)
+      ok = named_bar_and<2, 128>(ok && !aborted(ctx));
+      if (!ok) break;
+      // row of this item inside every source's stage [M, N]
+      const long long grow0 = (long long)tp.rank * ms;
+      for (int v0 = et; v0 < NV; v0 += 256) {
+        uint4 raw[2][8];
+        uint4 res[2];
+        long long out_off[2];
+        bool live[2];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const int v = v0 + u * 128;
+          const int lr = lt * BM + v / VEC_PER_ROW;
+          const int col = nt * BN + (v % VEC_PER_ROW) * 8;
+          live[u] = v < NV && col < p.N;
+          out_off[u] = (long long)lr * tp.rs_ldo + col;
+#pragma unroll
+          for (int src = 0; src < 8; ++src)
+            if (live[u] && src < tp.world)
+              raw[u][src] = ld_global_v4(tp.rs_peer_stage[src] + (grow0 + lr) * p.N + col);
+          if (live[u] && tp.rs_residual != nullptr) res[u] = ld_global_v4(tp.rs_residual + out_off[u]);
+        }
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          if (!live[u]) continue;
+          float acc[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+#pragma unroll
+          for (int src = 0; src < 8; ++src) {
+            if (src < tp.world) {
+              const uint32_t w[4] = {raw[u][src].x, raw[u][src].y, raw[u][src].z, raw[u][src].w};
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const float2 f = unpack_bf16x2(w[j]);
+                acc[2 * j] += f.x;
+                acc[2 * j + 1] += f.y;
+              }
+            }
+          }
+          if (tp.rs_residual != nullptr) {
+            const uint32_t w[4] = {res[u].x, res[u].y, res[u].z, res[u].w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float2 f = unpack_bf16x2(w[j]);
+              acc[2 * j] += f.x;
+              acc[2 * j + 1] += f.y;
+            }
+          }
+          st_global_v4(tp.rs_out + out_off[u], pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]),
+                       pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7]));
+        }
+      }
+    }
+  } else if (TP == 1) {
+    // ------------- push this rank's token shard to every peer's gathered buffer -------------
+    const int ct = threadIdx.x - PAIR_THREADS;  // 0..127
+    const int tps = tp.tiles_per_shard;
+    const int ms = tps * BM;
+    // A row tile is pushed by up to eight CTAs (row slices), so that every SM's copy warps take
+    // part even when the shard has fewer row tiles than the grid has CTAs.  The slices of a
+    // tile count themselves as (epoch << 4 | arrivals) in a counter region that follows the
+    // flags in the same local buffer (`rs_target` = its offset in ints in this mode; the
+    // counters must never share words with flags: a stale count would read as a huge epoch);
+    // whoever completes the count raises the tile's flag at the peers.
+    int parts = 1;
+    if (tp.rs_target > 0)
+      while (parts < 8 && parts * 2 * tps <= int(gridDim.x)) parts *= 2;
+    const int rows_per = BM / parts;
+    int* my_cnt = const_cast<int*>(tp.ag_flags) + tp.rs_target;
+    for (int u = blockIdx.x; u < tps * parts; u += gridDim.x) {
+      const int lt = u / parts, part = u - lt * parts;
+      const long long row0 = (long long)tp.rank * ms + lt * BM + part * rows_per;
+      const int vec_per_row = tp.ag_cols / 8;
+      const int nvec = rows_per * vec_per_row;
+      for (int v0 = ct; v0 < nvec; v0 += 4 * 32 * kNumCommWarps) {
+        uint4 val[4];
+        long long off[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {  // four local loads in flight before the first peer store
+          const int v = v0 + i * 32 * kNumCommWarps;
+          off[i] = (row0 + v / vec_per_row) * tp.ag_ld + (v % vec_per_row) * 8;
+          if (v < nvec) val[i] = *reinterpret_cast<const uint4*>(tp.ag_src + off[i]);
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          if (v0 + i * 32 * kNumCommWarps < nvec) {
+            for (int d = 1; d < tp.world; ++d) {
+              const int q = (tp.rank + d) % tp.world;
+              *reinterpret_cast<uint4*>(tp.ag_peer_dst[q] + off[i]) = val[i];
+            }
+          }
+        }
+      }
+      if (tp.ag2_src != nullptr) {
+        const int vec2 = tp.ag2_cols / 8;
+        for (int v = ct; v < rows_per * vec2; v += 32 * kNumCommWarps) {
+          const long long off = (row0 + v / vec2) * tp.ag2_ld + (v % vec2) * 8;
+          const uint4 val = *reinterpret_cast<const uint4*>(tp.ag2_src + off);
+          for (int d = 1; d < tp.world; ++d) {
+            const int q = (tp.rank + d) % tp.world;
+            *reinterpret_cast<uint4*>(tp.ag2_peer_dst[q] + off) = val;
+          }
+        }
+      }
+      __threadfence_system();
+      asm volatile("bar.sync 2, 128;" ::: "memory");
+      if (ct == 0) {
+        bool last = true;
+        if (parts > 1) {
+          int seen = *reinterpret_cast<volatile int*>(my_cnt + lt);
+          for (;;) {
+            const int want = ((seen >> 4) == tp.epoch) ? seen + 1 : ((tp.epoch << 4) | 1);
+            const int prev = atomicCAS(my_cnt + lt, seen, want);
+            if (prev == seen) {
+              last = (want & 15) == parts;
+              break;
+            }
+            seen = prev;
+          }
+        }
+        if (last) {
+          __threadfence_system();
+          for (int d = 1; d < tp.world; ++d) {
+            const int q = (tp.rank + d) % tp.world;
+            st_release_sys(tp.ag_peer_flags[q] + tp.rank * tps + lt, tp.epoch);
+          }
+        }
+      }
     }
   }
 
@@ -346,16 +535,16 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1)
   }
 }
 
-template <bool B_MN, int NACC, int EPI>
+template <bool B_MN, int NACC, int EPI, int TP = 0>
 static int launch(const Params& p, const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tA2,
-                  const CUtensorMap& tB2, int pairs, cudaStream_t st) {
-  auto kern = umma_gemm_pair_kernel<B_MN, NACC, EPI>;
+                  const CUtensorMap& tB2, int pairs, cudaStream_t st, const TpParams& tp = TpParams()) {
+  auto kern = umma_gemm_pair_kernel<B_MN, NACC, EPI, TP>;
   static lf::PerDeviceOnce configured;  // one per template instantiation
   if (lf::ensure_max_dynamic_smem(configured, kern, SMEM_TOTAL) != cudaSuccess) {
     fprintf(stderr, "lf_gemm_pair: cudaFuncSetAttribute failed\n");
     return -10;
   }
-  kern<<<2 * pairs, PAIR_THREADS, SMEM_TOTAL, st>>>(p, tA, tB, tA2, tB2);
+  kern<<<2 * pairs, PAIR_THREADS + (TP != 0 ? 32 * kNumCommWarps : 0), SMEM_TOTAL, st>>>(p, tA, tB, tA2, tB2, tp);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     fprintf(stderr, "lf_gemm_pair: launch failed: %s\n", cudaGetErrorString(e));
@@ -370,7 +559,7 @@ static int launch(const Params& p, const CUtensorMap& tA, const CUtensorMap& tB,
 // Same argument struct as lf_gemm.  Supported: a / a2 K-major; b and b2 both K-major or both
 // MN-major; bn = 256; epilogues LF_EPI_BF16 (nacc 1) and LF_EPI_BF16_DROPMIX (nacc 2); dense
 // mode only.  Returns -5 for anything else so that callers can fall back to lf_gemm.
-extern "C" int lf_gemm_pair(const LfGemmArgs* a) {
+static int pair_entry(const LfGemmArgs* a, const LfTpArgs* t) {
   using namespace lf;
   using namespace lf::pair;
   if (a == nullptr || a->a == nullptr || a->b == nullptr || a->out == nullptr) return -1;
@@ -419,7 +608,21 @@ extern "C" int lf_gemm_pair(const LfGemmArgs* a) {
   p.col_offset = a->col_offset;
   p.zero_row = int(a->a2_rows) + BM;  // beyond the last row of S': the TMA box reads zeros
   p.err = a->err;
+  p.m_rotate = 0;
   if (p.num_tiles <= 0) return 0;
+  TpParams tp{};
+  const int mode = (t != nullptr) ? t->mode : 0;
+  if (mode != 0) {
+    if (t->world < 1 || t->world > 8 || t->rank < 0 || t->rank >= t->world) return -7;
+    // a pair owns two 128-row tiles of ONE rank's shard: whole pairs per shard, no ragged last pair
+    if (t->tiles_per_shard % 2 != 0 || a->M != (long long)t->world * t->tiles_per_shard * BM) return -5;
+    if (a->bn != BN) return -5;
+    tp = make_tp_params(t);
+    // all-gather: start with this rank's own rows; reduce-scatter: finish with them
+    const int pairs_per_shard = t->tiles_per_shard / 2;
+    p.m_rotate = (mode == 1 ? t->rank : (t->rank + 1) % t->world) * pairs_per_shard;
+    if (pairs_per_shard < p.group_m) p.group_m = pairs_per_shard;
+  }
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -428,10 +631,25 @@ extern "C" int lf_gemm_pair(const LfGemmArgs* a) {
   if (p.num_tiles < pairs) pairs = p.num_tiles;
   if (pairs < 1) pairs = 1;
   cudaStream_t st = (cudaStream_t)a->stream;
-  if (dropmix) {
-    if (!a->b_mn) return -5;
-    return launch<true, 2, LF_EPI_BF16_DROPMIX>(p, tA, tB, tA2, tB2, pairs, st);
-  }
-  if (a->b_mn) return launch<true, 1, LF_EPI_BF16>(p, tA, tB, tA2, tB2, pairs, st);
-  return launch<false, 1, LF_EPI_BF16>(p, tA, tB, tA2, tB2, pairs, st);
+  if (dropmix && !a->b_mn) return -5;
+#define LF_PAIR_DISPATCH(TPV)                                                                                  \
+  do {                                                                                                         \
+    if (dropmix) return launch<true, 2, LF_EPI_BF16_DROPMIX, TPV>(p, tA, tB, tA2, tB2, pairs, st, tp);         \
+    if (a->b_mn) return launch<true, 1, LF_EPI_BF16, TPV>(p, tA, tB, tA2, tB2, pairs, st, tp);                 \
+    return launch<false, 1, LF_EPI_BF16, TPV>(p, tA, tB, tA2, tB2, pairs, st, tp);                             \
+  } while (0)
+  if (mode == 1) LF_PAIR_DISPATCH(1);
+  if (mode == 2) LF_PAIR_DISPATCH(2);
+  LF_PAIR_DISPATCH(0);
+#undef LF_PAIR_DISPATCH
+}
+
+extern "C" int lf_gemm_pair(const LfGemmArgs* a) { return pair_entry(a, nullptr); }
+
+// CTA-pair variants of the tensor-parallel fused kernels (see lf_gemm_tp).  Returns -5 for
+// shapes the pair kernels do not cover (odd number of 128-row tiles per shard, ...): the caller
+// falls back to lf_gemm_tp.
+extern "C" int lf_gemm_pair_tp(const LfGemmArgs* a, const LfTpArgs* t) {
+  if (t == nullptr || t->mode == 0) return -5;
+  return pair_entry(a, t);
 }

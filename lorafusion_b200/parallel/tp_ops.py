@@ -28,6 +28,7 @@ previous gather (and vice versa).
 from __future__ import annotations
 
 import ctypes as C
+import os
 from typing import Optional
 
 import torch
@@ -38,6 +39,15 @@ from ..ops.gemm import fill_gemm_args
 from .symmetric import SymmetricBuffer, allocate_symmetric, local_buffer
 
 TILE = 128
+# CTA-pair variants of the fused kernels; "0" keeps everything on the single-CTA template
+_PAIR_TP = os.environ.get("LORAFUSION_B200_PAIR_TP", "1") == "1"
+
+
+def set_pair_tp_kernels(enabled: bool) -> None:
+    """Route the tensor-parallel fused GEMMs to the CTA-pair kernels (True) or to the single-CTA
+    template (False); shapes the pair kernels do not cover always use the template."""
+    global _PAIR_TP
+    _PAIR_TP = bool(enabled)
 
 
 class LfTpArgs(C.Structure):
@@ -196,6 +206,17 @@ def _launch(gemm_kwargs: dict, tp: LfTpArgs) -> None:
         if rc != 0:
             raise RuntimeError(f"lf_gemm_tp_nf4 failed with code {rc}")
         return
+    if _PAIR_TP:
+        # CTA-pair (256 x 256 tile, tcgen05 cta_group::2) variant first; -5 = shape not covered
+        if not getattr(lib, "_lf_pair_tp_declared", False):
+            lib.lf_gemm_pair_tp.argtypes = [C.POINTER(nv.LfGemmArgs), C.POINTER(LfTpArgs)]
+            lib.lf_gemm_pair_tp.restype = C.c_int
+            lib._lf_pair_tp_declared = True
+        rc = lib.lf_gemm_pair_tp(C.byref(args), C.byref(tp))
+        if rc == 0:
+            return
+        if rc != -5:
+            raise RuntimeError(f"lf_gemm_pair_tp failed with code {rc}")
     rc = lib.lf_gemm_tp(C.byref(args), C.byref(tp))
     if rc != 0:
         raise RuntimeError(f"lf_gemm_tp failed with code {rc}")

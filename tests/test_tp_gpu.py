@@ -222,20 +222,23 @@ def test_tp_stage_matches_unpartitioned_stage(tmp_path):
         assert p.returncode == 0, f"rank {r} failed:\n{o[-4000:]}"
 
 
-@pytest.mark.parametrize("world", [2, 4])
-def test_loopback_runs_the_copy_and_reduce_warps_on_one_gpu(world):
+@pytest.mark.parametrize("world,pair", [(2, True), (2, False), (4, True)])
+def test_loopback_runs_the_copy_and_reduce_warps_on_one_gpu(world, pair):
     """One GPU plays rank 0 of ``world``: peer pointers lead back to its own memory, the host
     plays the other ranks before each launch (data in place, flags raised).  The shard-push
     warps, the flag waits of the TMA producer, the partial-tile flags of the epilogue and the
     pulling reduce warps all run; results are checked against fp32 math."""
     from lorafusion_b200.ops import _native
-    from lorafusion_b200.parallel.tp_ops import TpContext, ag_gemm, gemm_rs
+    from lorafusion_b200.parallel.tp_ops import TpContext, ag_gemm, gemm_rs, set_pair_tp_kernels
     from lorafusion_b200.utils.testing import assert_close_two_rounds
 
     torch.backends.cuda.matmul.allow_tf32 = False
     dev = "cuda"
     T_MAX, K, N, R = 1024, 768, 1280, 64
     ctx = TpContext.loopback(dev, world=world, max_tokens=T_MAX, max_features=2048)
+    # pair = the CTA-pair kernels where the shape allows (an even number of 128-row tiles per
+    # shard: 1024 and 512 tokens at world 2, 1024 at world 4), else the single-CTA template
+    set_pair_tp_kernels(pair)
 
     def rnd(*shape, scale=1.0, seed=0):
         g = torch.Generator(device=dev).manual_seed(seed)
@@ -293,3 +296,4 @@ def test_loopback_runs_the_copy_and_reduce_warps_on_one_gpu(world):
             mine = (xa.float() @ wd.t() + sa.float() @ b2[0].float().t()).to(torch.bfloat16).float()
             assert_close_two_rounds(outq, mine[:ms] + sum(o.float()[:ms] for o in others) + res.float(), atol=2e-2,
                                     msg="loop-back gemm_rs NF4")
+    set_pair_tp_kernels(True)
