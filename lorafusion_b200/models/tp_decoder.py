@@ -218,7 +218,8 @@ class TpDecoderStage(DecoderStage):
                          out=ctx.own_gather2_rows(T, R))
             y = ag_gemm(ctx, T, H, materialize_weight(w, T), slab_cols=R, b2=stack.b, b2_adapter_rows=stack.b.shape[1],
                         tile_adapter=info.tile_adapter, bias=bias)
-            return y, x_sh.clone(), h_sh, rstd, ctx.gather2_view(T, R).clone()
+            # (the normalised shard lives in the gather buffer: copy it out only if the backward will want it)
+            return y, (x_sh.clone() if keep is True else None), h_sh, rstd, ctx.gather2_view(T, R).clone()
 
         def row_parallel(x_loc, proj, w, k_loc, residual=None):
             stack = st[proj]
