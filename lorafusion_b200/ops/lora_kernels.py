@@ -32,7 +32,7 @@ Conventions
 
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass, field, replace
 from typing import Optional, Sequence
 
 import torch
@@ -92,6 +92,15 @@ class SegmentTable:
     total_rows: Optional[int] = None
     _cache: dict = field(default_factory=dict)
 
+    def split_plan(self, features: int):
+        """``(work list, owner)`` with long segments cut into token chunks, or ``None`` when the
+        plain work list already fills the GPU.  The work list's fourth column is the CHUNK index
+        (the slice of a partial-result buffer the chunk writes); ``owner[chunk]`` = its adapter."""
+        key = ("split", features)
+        if key not in self._cache:
+            self._cache[key] = _split_plan(self, features)
+        return self._cache[key]
+
     def tiles_for(self, features: int) -> torch.Tensor:
         """int32 ``[n_tiles, 4]`` work list ``(feature0, token0, k_blocks, adapter)``."""
         t = self._cache.get(features)
@@ -112,6 +121,38 @@ class SegmentTable:
             t = torch.tensor(rows, dtype=torch.int32).reshape(-1, 4).to(self.device)
             self._cache[features] = t
         return t
+
+
+# A gradient kernel gives every (segment, 128-feature tile) to one CTA, which walks all tokens of
+# the segment.  With few long segments (one adapter, 8K tokens, 4096 features: 32 work items) most
+# SMs idle, so such segments are cut in token chunks that write PARTIAL results, summed afterwards.
+_SPLIT_BELOW_ITEMS = 96      # enough work items already: leave the segments whole
+_SPLIT_TARGET_ITEMS = 148
+_SPLIT_MAX_CHUNKS = 8
+_SPLIT_MIN_TOKENS = 1024
+
+
+def _split_plan(table: SegmentTable, features: int):
+    segs = [(a, s0, e0) for a, s0, e0 in table.segments if a >= 0 and e0 > s0]
+    f_tiles = (features + TILE_M - 1) // TILE_M
+    items = len(segs) * f_tiles
+    if not segs or items >= _SPLIT_BELOW_ITEMS:
+        return None
+    want = min(_SPLIT_MAX_CHUNKS, -(-_SPLIT_TARGET_ITEMS // items))
+    rows, owner = [], []
+    for a, s0, e0 in segs:
+        n_chunks = max(1, min(want, (e0 - s0) // _SPLIT_MIN_TOKENS))
+        step = -(-(e0 - s0) // n_chunks)
+        step = -(-step // TILE_M) * TILE_M
+        for c0 in range(s0, e0, step):
+            c1 = min(e0, c0 + step)
+            v = len(owner)
+            owner.append(a)
+            for f0 in range(0, features, TILE_M):
+                rows.append((f0, c0, (c1 - c0 + 63) // 64, v))
+    if len(owner) == len(segs):
+        return None   # nothing was cut
+    return torch.tensor(rows, dtype=torch.int32).reshape(-1, 4).to(table.device), owner
 
 
 def _flat2d(t: torch.Tensor) -> torch.Tensor:
@@ -172,6 +213,14 @@ def lora_db(dy: torch.Tensor, s: torch.Tensor, segs: SegmentTable, db_all: torch
     M, N = dy.shape
     n, N2, R = db_all.shape
     assert N2 == N and s.shape == (M, R) and db_all.dtype == torch.float32
+    plan = segs.split_plan(N)
+    if plan is not None:
+        tiles, owner = plan
+        tmp = torch.zeros((len(owner), N, R), dtype=torch.float32, device=dy.device)
+        launch_gemm(a=dy, b=s, out=tmp, M=N, N=R, K=M, a_mn=True, b_mn=True, bn=R,
+                    epi=nv.EPI_F32_ACCUM, seg_tiles=tiles, ldo=R, out_adapter_stride=N * R)
+        _fold_chunks(tmp, owner, db_all)
+        return
     tiles = segs.tiles_for(N)
     if tiles.shape[0] == 0:
         return
@@ -185,12 +234,38 @@ def lora_da(x: torch.Tensor, ds: torch.Tensor, segs: SegmentTable, da_all: torch
     M, K = x.shape
     n, R, K2 = da_all.shape
     assert K2 == K and ds.shape == (M, R) and da_all.dtype == torch.float32
+    plan = segs.split_plan(K)
+    if plan is not None:
+        tiles, owner = plan
+        drop = dropout
+        if dropout.adapter_thresh16 is not None:   # per-adapter rates follow the chunks
+            idx = torch.tensor(owner, dtype=torch.long, device=x.device)
+            drop = replace(dropout, adapter_thresh16=dropout.adapter_thresh16[idx].contiguous(),
+                           adapter_inv_keep=dropout.adapter_inv_keep[idx].contiguous())
+        tmp = torch.zeros((len(owner), R, K), dtype=torch.float32, device=x.device)
+        launch_gemm(a=x, b=ds, out=tmp, M=K, N=R, K=M, a_mn=True, b_mn=True, bn=R,
+                    epi=nv.EPI_F32_ACCUM, mask_a=drop.active, seg_tiles=tiles, ldo=K,
+                    out_transposed=True, out_adapter_stride=R * K, **drop.kwargs())
+        _fold_chunks(tmp, owner, da_all)
+        return
     tiles = segs.tiles_for(K)
     if tiles.shape[0] == 0:
         return
     launch_gemm(a=x, b=ds, out=da_all, M=K, N=R, K=M, a_mn=True, b_mn=True, bn=R,
                 epi=nv.EPI_F32_ACCUM, mask_a=dropout.active, seg_tiles=tiles, ldo=K,
                 out_transposed=True, out_adapter_stride=R * K, **dropout.kwargs())
+
+
+def _fold_chunks(tmp: torch.Tensor, owner: Sequence[int], out_all: torch.Tensor) -> None:
+    """``out_all[a] += sum of the chunk partials of adapter a``, chunks in token order (a fixed
+    order, so the result does not depend on which CTA finished first)."""
+    start = 0
+    while start < len(owner):
+        end = start
+        while end < len(owner) and owner[end] == owner[start]:
+            end += 1
+        out_all[owner[start]] += tmp[start:end].sum(0)
+        start = end
 
 
 def base_lora_dx(dy: torch.Tensor, w: torch.Tensor, ds: Optional[torch.Tensor],

@@ -122,6 +122,47 @@ def test_lora_linear_blocks(p):
                                 atol=1e-2, msg=f"lora_da[{a}]")
 
 
+@pytest.mark.parametrize("mixed_p", [False, True])
+def test_gradient_kernels_split_long_segments_into_chunks(mixed_p):
+    """Two long segments and few feature tiles: the work list is cut into token chunks that write
+    partial sums, folded in a fixed order.  Same results as fp32 math, and bitwise the same from
+    run to run."""
+    from lorafusion_b200.ops import lora_kernels as lk
+    from lorafusion_b200.ops.philox import keep_mask
+
+    N, K, n, R = 256, 384, 2, 64
+    segs = [(1, 0, 3072), (0, 3072, 5248)]          # 5 feature tiles at most -> 10 work items uncut
+    M = 5248
+    x, dy = _rand(M, K, seed=40), _rand(M, N, seed=41)
+    s, ds = _rand(M, R, scale=0.1, seed=42), _rand(M, R, scale=0.1, seed=43)
+    table = lk.SegmentTable(segs, torch.device("cuda"), total_rows=M)
+    plan = table.split_plan(K)
+    assert plan is not None and len(plan[1]) > 2 and plan[1] == sorted(plan[1], reverse=True)
+    ps = [0.1, 0.2] if mixed_p else [0.1, 0.1]
+    if mixed_p:
+        from lorafusion_b200.ops.philox import dropout_threshold
+        drop = lk.DropoutSpec(seed=77, stream_id=3, p=0.0,
+                              adapter_thresh16=torch.tensor([dropout_threshold(q) for q in ps], dtype=torch.int32,
+                                                            device="cuda"),
+                              adapter_inv_keep=torch.tensor([1 / (1 - q) for q in ps], device="cuda"))
+    else:
+        drop = lk.DropoutSpec(seed=77, stream_id=3, p=0.1)
+    outs = []
+    for _ in range(2):
+        da_all = torch.zeros(n, R, K, device="cuda")
+        db_all = torch.zeros(n, N, R, device="cuda")
+        lk.lora_db(dy, s, table, db_all)
+        lk.lora_da(x, ds, table, da_all, dropout=drop)
+        outs.append((da_all, db_all))
+    assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+    da_all, db_all = outs[0]
+    for a, r0, r1 in segs:
+        keep = keep_mask(M, K, ps[a], 77, 3).cuda()[r0:r1]
+        xh = torch.where(keep, x[r0:r1].float() / (1 - ps[a]), torch.zeros((), device="cuda")).to(torch.bfloat16)
+        assert_close_two_rounds(db_all[a], _f32mm(dy[r0:r1].t(), s[r0:r1]), rtol=1e-3, atol=2e-2, msg=f"split lora_db[{a}]")
+        assert_close_two_rounds(da_all[a], _f32mm(ds[r0:r1].t(), xh), rtol=1e-3, atol=2e-2, msg=f"split lora_da[{a}]")
+
+
 def test_dropout_keep_fraction():
     from lorafusion_b200.ops.philox import keep_mask
 
