@@ -302,20 +302,33 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS + (TP !
         thresh = p.adapter_thresh16[my_adapter];
         inv_keep = p.adapter_inv_keep[my_adapter];
       }
+      // The TMEM loads of chunk c + 1 are in flight while chunk c is masked, mixed and stored: the
+      // dropout-mixing variant has no second accumulator buffer, so every cycle of this loop is
+      // time the tensor pipe waits.
+      const int c_begin = half * CHUNKS_PER_HALF, c_end = (half + 1) * CHUNKS_PER_HALF;
+      const bool mix = EPI == LF_EPI_BF16_DROPMIX && NACC == 2 && has_slab;
+      uint32_t r[32], r2[32];
+      tmem_ld_32x32b_x32(acc0 + c_begin * 32, r);
+      if (mix) tmem_ld_32x32b_x32(acc1 + c_begin * 32, r2);
 #pragma unroll 1
-      for (int c = half * CHUNKS_PER_HALF; c < (half + 1) * CHUNKS_PER_HALF; ++c) {
-        uint32_t r[32], r2[32];
-        tmem_ld_32x32b_x32(acc0 + c * 32, r);
-        if (NACC == 2 && has_slab) tmem_ld_32x32b_x32(acc1 + c * 32, r2);
+      for (int c = c_begin; c < c_end; ++c) {
         tmem_ld_wait();
         const int col0 = t.n_tile * BN + c * 32;
-        float v[32];
+        float v[32], w2[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-        if (EPI == LF_EPI_BF16_DROPMIX && NACC == 2 && has_slab) {
+        if (mix) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) w2[j] = __uint_as_float(r2[j]);
+        }
+        if (c + 1 < c_end) {
+          tmem_ld_32x32b_x32(acc0 + (c + 1) * 32, r);
+          if (mix) tmem_ld_32x32b_x32(acc1 + (c + 1) * 32, r2);
+        }
+        if (mix) {
           if (thresh == 0) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] += __uint_as_float(r2[j]);
+            for (int j = 0; j < 32; ++j) v[j] += w2[j];
           } else {
 #pragma unroll
             for (int g = 0; g < 4; ++g) {
@@ -324,7 +337,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS + (TP !
                                                   p.seed_lo, p.seed_hi, thresh);
 #pragma unroll
               for (int j = 0; j < 8; ++j)
-                if ((keep >> j) & 1u) v[g * 8 + j] += inv_keep * __uint_as_float(r2[g * 8 + j]);
+                if ((keep >> j) & 1u) v[g * 8 + j] += inv_keep * w2[g * 8 + j];
             }
           }
         }
