@@ -172,7 +172,7 @@ __global__ void __launch_bounds__(192 + ((MASK_A || NF4B) ? 32 * kNumMaskWarps :
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
-      mbar_init(&ready[s], 32 * kNumMaskWarps);
+      mbar_init(&ready[s], kNumMaskWarps);  // lane 0 of every rewriting warp reports for its warp
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tfull[b], 1);
@@ -641,7 +641,8 @@ __global__ void __launch_bounds__(192 + ((MASK_A || NF4B) ? 32 * kNumMaskWarps :
           if (wrow < p.nf4_rows && wblk < p.nf4_blocks_per_row)
             scale = __ldg(p.nf4_scales + wrow * p.nf4_blocks_per_row + wblk);
         }
-        if (!mbar_wait(&full[s], ph, ctx, ERR_WAIT_FULL)) {
+        // one answer per warp: its lanes meet again in __syncwarp below
+        if (!__all_sync(0xffffffffu, mbar_wait(&full[s], ph, ctx, ERR_WAIT_FULL))) {
           ok = false;
           break;
         }
@@ -677,7 +678,10 @@ __global__ void __launch_bounds__(192 + ((MASK_A || NF4B) ? 32 * kNumMaskWarps :
           }
           fence_proxy_async_smem();
         }
-        mbar_arrive(&ready[s]);
+        // one arrival per warp: 256 arrivals on one barrier word serialise and cost as much as
+        // the rewrite itself
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&ready[s]);
       }
     }
   } else if (MASK_A) {
@@ -700,7 +704,8 @@ __global__ void __launch_bounds__(192 + ((MASK_A || NF4B) ? 32 * kNumMaskWarps :
       for (int kb = 0; kb < total; ++kb, ++it) {
         const int s = it % STAGES;
         const uint32_t ph = (it / STAGES) & 1;
-        if (!mbar_wait(&full[s], ph, ctx, ERR_WAIT_FULL)) {
+        // one answer per warp: its lanes meet again in __syncwarp below
+        if (!__all_sync(0xffffffffu, mbar_wait(&full[s], ph, ctx, ERR_WAIT_FULL))) {
           ok = false;
           break;
         }
@@ -740,7 +745,8 @@ __global__ void __launch_bounds__(192 + ((MASK_A || NF4B) ? 32 * kNumMaskWarps :
           }
           fence_proxy_async_smem();
         }
-        mbar_arrive(&ready[s]);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&ready[s]);
       }
     }
   }

@@ -11,13 +11,14 @@
 // Covered ops (the ones that dominate a training step):
 //   forward  Y  = X W^T + S' B_a^T (+ bias)                 B K-major,  one accumulator
 //   dX       dX = dY W + dS A_a                             B MN-major, one accumulator
-//   dX with dropout: second accumulator for dS A_a, Philox mask regenerated in the epilogue
+//   dX with dropout: the slab dS A_a goes into the accumulator first, is masked in place in
+//                    TMEM by the epilogue warps (Philox mask regenerated), dY W lands on top
 // Adapters are chosen per 128-row tile, so the two CTAs of a pair may need different LoRA
 // weights: the LoRA slab is issued once per distinct adapter of the pair, and a CTA whose
 // rows belong to another adapter loads zeros for its S' rows (an out-of-range TMA box).
 //
 // Roles per CTA: warp 0 = TMA producer (both CTAs), warp 1 = TMEM allocator (both) and MMA
-// issuer (leader CTA only), warps 2..5 = epilogue (both).  Barriers: "stage full" lives in
+// issuer (leader CTA only), warps 2..9 = epilogue (both).  Barriers: "stage full" lives in
 // the leader and is credited by both CTAs' loads; "stage empty" and "accumulator full" exist
 // in both CTAs and are signalled by two tcgen05.commit (own + peer address); "accumulator
 // empty" lives in the leader and collects 256 arrivals.  All waits are bounded.
@@ -108,13 +109,27 @@ __device__ __forceinline__ int slab_passes(const Tile& t, int (&ad)[2]) {
 // and flags it at the owner of the rows; four extra warps per CTA pull and sum the partials of the
 // rows this rank owns).  Same protocol, flags and buffers as the single-CTA template in
 // umma_gemm.cu; 128-row tile granularity is kept because each CTA of a pair owns one such tile.
-template <bool B_MN, int NACC, int EPI, int TP = 0>
+//
+// EPI = LF_EPI_BF16: per tile the main product, then the LoRA slab on top; two accumulator
+// buffers, the epilogue of tile j drains one while the main loop of tile j + 1 fills the other.
+//
+// EPI = LF_EPI_BF16_DROPMIX ("slab first"): dX = dY W + keep (.) (dS A) / (1 - p).  The slab
+// product of tile j + 1 is issued in the MIDDLE of tile j's main loop into the other accumulator
+// buffer; the epilogue warps multiply it by the regenerated dropout mask IN PLACE in TMEM
+// (tcgen05.ld -> Philox -> tcgen05.st) while tile j's main loop goes on, and tile j + 1's main
+// product then accumulates on top of the masked slab.  Both passes of the epilogue warps (mask
+// of the next tile, drain of the current one) are hidden behind a main loop, so the kernel keeps
+// ONE accumulator per tile, double-buffered, exactly like the plain variant.  Barriers added for
+// this: "slab full" (both CTAs, tcgen05.commit) and "slab masked" (leader, every epilogue thread
+// of both CTAs arrives).
+template <bool B_MN, int EPI, int TP = 0>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS + (TP != 0 ? 32 * kNumCommWarps : 0), 1)
     umma_gemm_pair_kernel(const Params p, const __grid_constant__ CUtensorMap tmA,
                           const __grid_constant__ CUtensorMap tmB,
                           const __grid_constant__ CUtensorMap tmA2,
                           const __grid_constant__ CUtensorMap tmB2, const TpParams tp) {
-  constexpr int NBUF = (NACC == 1) ? 2 : 1;
+  constexpr bool SLAB_FIRST = (EPI == LF_EPI_BF16_DROPMIX);
+  constexpr int NBUF = 2;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~uintptr_t(1023));
@@ -123,7 +138,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS + (TP !
   uint64_t* empty = bars + STAGES;       // both
   uint64_t* tfull = bars + 2 * STAGES;   // both [2]
   uint64_t* tempty = tfull + 2;          // leader [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  uint64_t* sfull = tempty + 2;          // both [2]: the slab product of a tile is in its buffer
+  uint64_t* masked = sfull + 2;          // leader [2]: ... and has been masked in place
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(masked + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -131,6 +148,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS + (TP !
   const int pair_id = blockIdx.x >> 1;
   const int num_pairs = gridDim.x >> 1;
   AbortCtx ctx{p.err, abort_flag};
+  // main-loop block before which the next tile's slab is slipped in (slab-first variant)
+  const int ks = SLAB_FIRST ? p.nkb_main / 2 : p.nkb_main;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -140,6 +159,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS + (TP !
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tfull[b], 1);
       mbar_init(&tempty[b], 2 * 32 * PAIR_EPI_WARPS);  // every epilogue thread of both CTAs
+      mbar_init(&sfull[b], 1);
+      mbar_init(&masked[b], 2 * 32 * PAIR_EPI_WARPS);
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -159,110 +180,181 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS + (TP !
     // ------------------------------ producer (both CTAs) ------------------------------
     if (lane == 0) {
       int it = 0;
-      bool ok = true;
-      for (int tile = pair_id; ok && tile < p.num_tiles; tile += num_pairs) {
-        const Tile t = decode(p, tile);
+      // one 64-deep k-block into the next free stage: block `kb` of the main product, or block
+      // `slab_idx` (>= 0) of the tile's slab passes
+      auto load_block = [&](const Tile& t, const int (&ad)[2], int kb, int slab_idx) -> bool {
+        const int s = it % STAGES;
+        const uint32_t ph = (it / STAGES) & 1;
+        if (!mbar_wait(&empty[s], ph ^ 1, ctx, ERR_WAIT_EMPTY)) return false;
+        ++it;
         const int m0 = (2 * t.pm + int(cta)) * BM;
         const int n0 = t.n_tile * BN + int(cta) * BNH;
-        int ad[2];
-        const int n_slab = slab_passes(t, ad);
-        const int my_adapter = cta == 0 ? t.a0 : t.a1;
-        const int total = p.nkb_main + n_slab * p.nkb2;
+        uint8_t* sA = smem + s * STAGE_BYTES;
+        uint8_t* sB = sA + A_BYTES;
+        const uint32_t fbar = mapa_shared(&full[s], 0);
+        if (cta == 0) mbar_expect_tx(&full[s], 2 * STAGE_BYTES);
+        if (slab_idx < 0) {
+          const int kk = kb * BK;
+          tma_load_2d_pair(sA, &tmA, fbar, kk, m0);
+          if (!B_MN) {
+            tma_load_2d_pair(sB, &tmB, fbar, kk, n0);
+          } else {
+            tma_load_2d_pair(sB, &tmB, fbar, n0, kk);
+            tma_load_2d_pair(sB + 8192, &tmB, fbar, n0 + 64, kk);
+          }
+        } else {
+          const int sp = slab_idx / p.nkb2;
+          const int kk2 = (slab_idx - sp * p.nkb2) * BK;
+          const int a = ad[sp];
+          const int my_adapter = cta == 0 ? t.a0 : t.a1;
+          // rows of another adapter contribute nothing to this pass: read zeros
+          tma_load_2d_pair(sA, &tmA2, fbar, kk2, my_adapter == a ? m0 : p.zero_row);
+          const int by2 = a * p.b2_adapter_rows;
+          if (!B_MN) {
+            tma_load_2d_pair(sB, &tmB2, fbar, kk2, by2 + n0);
+          } else {
+            tma_load_2d_pair(sB, &tmB2, fbar, n0, by2 + kk2);
+            tma_load_2d_pair(sB + 8192, &tmB2, fbar, n0 + 64, by2 + kk2);
+          }
+        }
+        return true;
+      };
+      // all-gather variant: the rows of this CTA's A tile (and of its slab tile) come from rank
+      // `src`; they are in LOCAL memory once that rank has pushed them and raised the tile's flag
+      auto rows_ready = [&](const Tile& t) -> bool {
         if (TP == 1) {
-          // the rows of this CTA's A tile (and of its slab tile) come from rank `src`: they are
-          // in LOCAL memory once that rank has pushed them and raised the tile's flag
-          const int mt = m0 / BM;
+          const int mt = 2 * t.pm + int(cta);
           const int src = mt / tp.tiles_per_shard;
           if (src != tp.rank) {
             if (!wait_flag_ge(tp.ag_flags + src * tp.tiles_per_shard + (mt - src * tp.tiles_per_shard), tp.epoch,
-                              ctx)) {
-              ok = false;
-              break;
-            }
+                              ctx))
+              return false;
             fence_proxy_async_all();
           }
         }
-        for (int kb = 0; kb < total; ++kb, ++it) {
-          const int s = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1;
-          if (!mbar_wait(&empty[s], ph ^ 1, ctx, ERR_WAIT_EMPTY)) {
-            ok = false;
-            break;
+        return true;
+      };
+      auto load_slabs = [&](const Tile& t) -> bool {
+        int ad[2] = {0, 0};
+        const int n = slab_passes(t, ad) * p.nkb2;
+        for (int i = 0; i < n; ++i)
+          if (!load_block(t, ad, 0, i)) return false;
+        return true;
+      };
+      auto load_main = [&](const Tile& t, int kb0, int kb1) -> bool {
+        const int ad[2] = {0, 0};
+        for (int kb = kb0; kb < kb1; ++kb)
+          if (!load_block(t, ad, kb, -1)) return false;
+        return true;
+      };
+      bool ok = true;
+      if (SLAB_FIRST && pair_id < p.num_tiles) {
+        const Tile t = decode(p, pair_id);
+        ok = rows_ready(t) && load_slabs(t);
+      }
+      for (int tile = pair_id; ok && tile < p.num_tiles; tile += num_pairs) {
+        const Tile t = decode(p, tile);
+        if (!SLAB_FIRST) ok = rows_ready(t);
+        ok = ok && load_main(t, 0, ks);
+        if (SLAB_FIRST) {
+          if (ok && tile + num_pairs < p.num_tiles) {
+            const Tile tn = decode(p, tile + num_pairs);
+            ok = rows_ready(tn) && load_slabs(tn);
           }
-          uint8_t* sA = smem + s * STAGE_BYTES;
-          uint8_t* sB = sA + A_BYTES;
-          const uint32_t fbar = mapa_shared(&full[s], 0);
-          if (cta == 0) mbar_expect_tx(&full[s], 2 * STAGE_BYTES);
-          if (kb < p.nkb_main) {
-            const int kk = kb * BK;
-            tma_load_2d_pair(sA, &tmA, fbar, kk, m0);
-            if (!B_MN) {
-              tma_load_2d_pair(sB, &tmB, fbar, kk, n0);
-            } else {
-              tma_load_2d_pair(sB, &tmB, fbar, n0, kk);
-              tma_load_2d_pair(sB + 8192, &tmB, fbar, n0 + 64, kk);
-            }
-          } else {
-            const int sp = (kb - p.nkb_main) / p.nkb2;
-            const int kk2 = ((kb - p.nkb_main) - sp * p.nkb2) * BK;
-            const int a = ad[sp];
-            // rows of another adapter contribute nothing to this pass: read zeros
-            tma_load_2d_pair(sA, &tmA2, fbar, kk2, my_adapter == a ? m0 : p.zero_row);
-            const int by2 = a * p.b2_adapter_rows;
-            if (!B_MN) {
-              tma_load_2d_pair(sB, &tmB2, fbar, kk2, by2 + n0);
-            } else {
-              tma_load_2d_pair(sB, &tmB2, fbar, n0, by2 + kk2);
-              tma_load_2d_pair(sB + 8192, &tmB2, fbar, n0 + 64, by2 + kk2);
-            }
-          }
+        } else {
+          ok = ok && load_slabs(t);
         }
+        ok = ok && load_main(t, ks, p.nkb_main);
       }
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer (leader only) ------------------------------
     if (cta == 0 && lane == 0) {
       constexpr uint32_t IDESC = make_idesc_bf16(256, BN, 0, B_MN ? 1 : 0);
-      int it = 0, tile_iter = 0;
+      int it = 0;
+      // one k-block from the next full stage into accumulator `d`; `fresh` = overwrite it
+      auto issue_block = [&](uint32_t d, bool fresh) -> bool {
+        const int s = it % STAGES;
+        const uint32_t ph = (it / STAGES) & 1;
+        if (!mbar_wait(&full[s], ph, ctx, ERR_WAIT_FULL)) return false;
+        ++it;
+        tc_fence_after_sync();
+        const uint32_t sA = smem_u32(smem + s * STAGE_BYTES);
+        const uint32_t sB = sA + A_BYTES;
+#pragma unroll
+        for (int kk = 0; kk < BK / 16; ++kk) {
+          const uint64_t da = make_smem_desc_sw128(sA + kk * 32, 16, 1024);
+          const uint64_t db = B_MN ? make_smem_desc_sw128(sB + kk * 2048, 8192, 1024)
+                                   : make_smem_desc_sw128(sB + kk * 32, 16, 1024);
+          umma_bf16_ss_pair(d, da, db, IDESC, uint32_t(!(fresh && kk == 0)));
+        }
+        tc_commit_pair(mapa_shared(&empty[s], 0));
+        tc_commit_pair(mapa_shared(&empty[s], 1));
+        return true;
+      };
+      // slab passes of a tile; in the slab-first variant they open the accumulator
+      auto issue_slabs = [&](const Tile& t, uint32_t d) -> bool {
+        int ad[2] = {0, 0};
+        const int n = slab_passes(t, ad) * p.nkb2;
+        for (int i = 0; i < n; ++i)
+          if (!issue_block(d, SLAB_FIRST && i == 0)) return false;
+        return true;
+      };
+      auto issue_main = [&](uint32_t d, int kb0, int kb1, bool opens) -> bool {
+        for (int kb = kb0; kb < kb1; ++kb)
+          if (!issue_block(d, opens && kb == 0)) return false;
+        return true;
+      };
+      int tile_iter = 0;
       bool ok = true;
+      if (SLAB_FIRST && pair_id < p.num_tiles) {
+        const Tile t = decode(p, pair_id);
+        ok = mbar_wait(&tempty[0], 1, ctx, ERR_WAIT_TMEM_EMPTY);   // fresh barrier: passes at once
+        if (ok) {
+          tc_fence_after_sync();
+          ok = issue_slabs(t, tmem_base);
+        }
+        if (ok) {
+          tc_commit_pair(mapa_shared(&sfull[0], 0));
+          tc_commit_pair(mapa_shared(&sfull[0], 1));
+        }
+      }
       for (int tile = pair_id; ok && tile < p.num_tiles; tile += num_pairs, ++tile_iter) {
         const Tile t = decode(p, tile);
-        int ad[2];
-        const int n_slab = slab_passes(t, ad);
-        const int total = p.nkb_main + n_slab * p.nkb2;
         const int buf = tile_iter % NBUF;
         const uint32_t bph = (tile_iter / NBUF) & 1;
-        if (!mbar_wait(&tempty[buf], bph ^ 1, ctx, ERR_WAIT_TMEM_EMPTY)) {
-          ok = false;
-          break;
+        const uint32_t acc = tmem_base + uint32_t(buf * BN);
+        bool opens = true;   // does the main product start from a fresh accumulator?
+        if (SLAB_FIRST) {
+          int ad[2];
+          opens = slab_passes(t, ad) * p.nkb2 == 0;
+          ok = mbar_wait(&masked[buf], bph, ctx, ERR_WAIT_READY);
+        } else {
+          ok = mbar_wait(&tempty[buf], bph ^ 1, ctx, ERR_WAIT_TMEM_EMPTY);
         }
+        if (!ok) break;
         tc_fence_after_sync();
-        const uint32_t acc0 = tmem_base + uint32_t(buf * BN * NACC);
-        const uint32_t acc1 = acc0 + BN;
-        for (int kb = 0; kb < total; ++kb, ++it) {
-          const int s = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1;
-          if (!mbar_wait(&full[s], ph, ctx, ERR_WAIT_FULL)) {
-            ok = false;
-            break;
+        ok = issue_main(acc, 0, ks, opens);
+        if (SLAB_FIRST) {
+          if (ok && tile + num_pairs < p.num_tiles) {
+            const Tile tn = decode(p, tile + num_pairs);
+            const int nbuf = (tile_iter + 1) % NBUF;
+            const uint32_t nph = ((tile_iter + 1) / NBUF) & 1;
+            ok = mbar_wait(&tempty[nbuf], nph ^ 1, ctx, ERR_WAIT_TMEM_EMPTY);
+            if (ok) {
+              tc_fence_after_sync();
+              ok = issue_slabs(tn, tmem_base + uint32_t(nbuf * BN));
+            }
+            if (ok) {
+              tc_commit_pair(mapa_shared(&sfull[nbuf], 0));
+              tc_commit_pair(mapa_shared(&sfull[nbuf], 1));
+            }
           }
-          tc_fence_after_sync();
-          const uint32_t sA = smem_u32(smem + s * STAGE_BYTES);
-          const uint32_t sB = sA + A_BYTES;
-          const bool slab = kb >= p.nkb_main;
-          const uint32_t d = (NACC == 2 && slab) ? acc1 : acc0;
-#pragma unroll
-          for (int kk = 0; kk < BK / 16; ++kk) {
-            const uint64_t da = make_smem_desc_sw128(sA + kk * 32, 16, 1024);
-            const uint64_t db = B_MN ? make_smem_desc_sw128(sB + kk * 2048, 8192, 1024)
-                                     : make_smem_desc_sw128(sB + kk * 32, 16, 1024);
-            const uint32_t accum = (NACC == 2 && slab) ? uint32_t(kb > p.nkb_main || kk > 0)
-                                                       : uint32_t(kb > 0 || kk > 0);
-            umma_bf16_ss_pair(d, da, db, IDESC, accum);
-          }
-          tc_commit_pair(mapa_shared(&empty[s], 0));
-          tc_commit_pair(mapa_shared(&empty[s], 1));
+        } else {
+          ok = ok && issue_slabs(t, acc);
         }
+        // with ks == 0 (a single main block) the main product opens here instead
+        ok = ok && issue_main(acc, ks, p.nkb_main, opens && ks == 0);
         if (!ok) break;
         tc_commit_pair(mapa_shared(&tfull[buf], 0));
         tc_commit_pair(mapa_shared(&tfull[buf], 1));
@@ -271,17 +363,72 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS + (TP !
   } else if (threadIdx.x < PAIR_THREADS) {
     // ------------------------------ epilogue (both CTAs) ------------------------------
     // Eight warps: two per TMEM lane quarter (a warp may only touch quarter warp % 4), each
-    // taking half of the tile's columns.  The dropout-mixing variant has no second accumulator
-    // buffer, so its epilogue is exposed time between two main loops: halving it matters there.
+    // taking half of the tile's columns.
     const int q = warp & 3;
     const int half = (warp - 2) >> 2;
     constexpr int CHUNKS_PER_HALF = BN / 32 / (PAIR_EPI_WARPS / 4);
+    const int c_begin = half * CHUNKS_PER_HALF, c_end = (half + 1) * CHUNKS_PER_HALF;
+    const uint32_t lane_addr = uint32_t(q * 32) << 16;
+
+    // Slab-first variant: multiply the slab product of tile `t` (in buffer `iter % 2`) by its
+    // dropout mask, in place.  A CTA whose rows have no adapter (or an adapter without dropout)
+    // only reports in.
+    auto mask_slab = [&](const Tile& t, int iter) -> bool {
+      const int buf = iter % NBUF;
+      bool got = mbar_wait(&sfull[buf], uint32_t(iter / NBUF) & 1, ctx, ERR_WAIT_TMEM_FULL);
+      // the reduce-scatter epilogue meets in named barriers: one answer for all 256 threads
+      if (TP == 2) got = named_bar_and<1, 32 * PAIR_EPI_WARPS>(got);
+      if (!got) return false;
+      tc_fence_after_sync();
+      const int my_adapter = cta == 0 ? t.a0 : t.a1;
+      uint32_t thresh = p.thresh16;
+      float inv_keep = p.inv_keep;
+      if (my_adapter >= 0 && p.adapter_thresh16 != nullptr) {
+        thresh = p.adapter_thresh16[my_adapter];
+        inv_keep = p.adapter_inv_keep[my_adapter];
+      }
+      if (p.nkb2 > 0 && my_adapter >= 0 && thresh != 0) {
+        const int row = (2 * t.pm + int(cta)) * BM + q * 32 + lane;
+        const uint32_t acc = tmem_base + uint32_t(buf * BN) + lane_addr;
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(acc + c_begin * 32, r);
+#pragma unroll 1
+        for (int c = c_begin; c < c_end; ++c) {
+          tmem_ld_wait();
+          uint32_t w[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) w[j] = r[j];
+          if (c + 1 < c_end) tmem_ld_32x32b_x32(acc + (c + 1) * 32, r);
+          const int col0 = t.n_tile * BN + c * 32;
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            const uint32_t keep = dropout_keep8(uint32_t(row + p.row_offset),
+                                                uint32_t((col0 + p.col_offset) >> 3) + g, p.stream_id,
+                                                p.seed_lo, p.seed_hi, thresh);
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              w[g * 8 + j] = ((keep >> j) & 1u) ? __float_as_uint(inv_keep * __uint_as_float(w[g * 8 + j])) : 0u;
+          }
+          tmem_st_32x32b_x32(acc + c * 32, w);
+        }
+        tmem_st_wait();
+      }
+      tc_fence_before_sync();
+      mbar_arrive_cluster(mapa_shared(&masked[buf], 0));
+      return true;
+    };
+
     int tile_iter = 0;
     bool ok = true;
+    if (SLAB_FIRST && pair_id < p.num_tiles) ok = mask_slab(decode(p, pair_id), 0);
     for (int tile = pair_id; ok && tile < p.num_tiles; tile += num_pairs, ++tile_iter) {
       const Tile t = decode(p, tile);
-      const int my_adapter = cta == 0 ? t.a0 : t.a1;
-      const bool has_slab = p.nkb2 > 0 && my_adapter >= 0;
+      if (SLAB_FIRST && tile + num_pairs < p.num_tiles) {
+        if (!mask_slab(decode(p, tile + num_pairs), tile_iter + 1)) {
+          ok = false;
+          break;
+        }
+      }
       const int buf = tile_iter % NBUF;
       const uint32_t bph = (tile_iter / NBUF) & 1;
       bool got = mbar_wait(&tfull[buf], bph, ctx, ERR_WAIT_TMEM_FULL);
@@ -293,54 +440,18 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS + (TP !
       }
       tc_fence_after_sync();
       const int row = (2 * t.pm + int(cta)) * BM + q * 32 + lane;
-      const uint32_t lane_addr = uint32_t(q * 32) << 16;
-      const uint32_t acc0 = tmem_base + uint32_t(buf * BN * NACC) + lane_addr;
-      const uint32_t acc1 = acc0 + BN;
-      uint32_t thresh = p.thresh16;
-      float inv_keep = p.inv_keep;
-      if (EPI == LF_EPI_BF16_DROPMIX && my_adapter >= 0 && p.adapter_thresh16 != nullptr) {
-        thresh = p.adapter_thresh16[my_adapter];
-        inv_keep = p.adapter_inv_keep[my_adapter];
-      }
-      // The TMEM loads of chunk c + 1 are in flight while chunk c is masked, mixed and stored: the
-      // dropout-mixing variant has no second accumulator buffer, so every cycle of this loop is
-      // time the tensor pipe waits.
-      const int c_begin = half * CHUNKS_PER_HALF, c_end = (half + 1) * CHUNKS_PER_HALF;
-      const bool mix = EPI == LF_EPI_BF16_DROPMIX && NACC == 2 && has_slab;
-      uint32_t r[32], r2[32];
-      tmem_ld_32x32b_x32(acc0 + c_begin * 32, r);
-      if (mix) tmem_ld_32x32b_x32(acc1 + c_begin * 32, r2);
+      const uint32_t acc = tmem_base + uint32_t(buf * BN) + lane_addr;
+      // the TMEM load of chunk c + 1 is in flight while chunk c is converted and stored
+      uint32_t r[32];
+      tmem_ld_32x32b_x32(acc + c_begin * 32, r);
 #pragma unroll 1
       for (int c = c_begin; c < c_end; ++c) {
         tmem_ld_wait();
         const int col0 = t.n_tile * BN + c * 32;
-        float v[32], w2[32];
+        float v[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-        if (mix) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) w2[j] = __uint_as_float(r2[j]);
-        }
-        if (c + 1 < c_end) {
-          tmem_ld_32x32b_x32(acc0 + (c + 1) * 32, r);
-          if (mix) tmem_ld_32x32b_x32(acc1 + (c + 1) * 32, r2);
-        }
-        if (mix) {
-          if (thresh == 0) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] += w2[j];
-          } else {
-#pragma unroll
-            for (int g = 0; g < 4; ++g) {
-              const uint32_t keep = dropout_keep8(uint32_t(row + p.row_offset),
-                                                  uint32_t((col0 + p.col_offset) >> 3) + g, p.stream_id,
-                                                  p.seed_lo, p.seed_hi, thresh);
-#pragma unroll
-              for (int j = 0; j < 8; ++j)
-                if ((keep >> j) & 1u) v[g * 8 + j] += inv_keep * w2[g * 8 + j];
-            }
-          }
-        }
+        if (c + 1 < c_end) tmem_ld_32x32b_x32(acc + (c + 1) * 32, r);
         if (EPI == LF_EPI_BF16 && p.bias != nullptr) {
 #pragma unroll
           for (int j = 0; j < 32; ++j)
@@ -548,10 +659,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS + (TP !
   }
 }
 
-template <bool B_MN, int NACC, int EPI, int TP = 0>
+template <bool B_MN, int EPI, int TP = 0>
 static int launch(const Params& p, const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tA2,
                   const CUtensorMap& tB2, int pairs, cudaStream_t st, const TpParams& tp = TpParams()) {
-  auto kern = umma_gemm_pair_kernel<B_MN, NACC, EPI, TP>;
+  auto kern = umma_gemm_pair_kernel<B_MN, EPI, TP>;
   static lf::PerDeviceOnce configured;  // one per template instantiation
   if (lf::ensure_max_dynamic_smem(configured, kern, SMEM_TOTAL) != cudaSuccess) {
     fprintf(stderr, "lf_gemm_pair: cudaFuncSetAttribute failed\n");
@@ -570,7 +681,8 @@ static int launch(const Params& p, const CUtensorMap& tA, const CUtensorMap& tB,
 }  // namespace lf
 
 // Same argument struct as lf_gemm.  Supported: a / a2 K-major; b and b2 both K-major or both
-// MN-major; bn = 256; epilogues LF_EPI_BF16 (nacc 1) and LF_EPI_BF16_DROPMIX (nacc 2); dense
+// MN-major; bn = 256; epilogues LF_EPI_BF16 (nacc 1) and LF_EPI_BF16_DROPMIX (callers pass nacc 2,
+// the layout of the single-CTA kernel; here the slab is masked in place in one accumulator); dense
 // mode only.  Returns -5 for anything else so that callers can fall back to lf_gemm.
 static int pair_entry(const LfGemmArgs* a, const LfTpArgs* t) {
   using namespace lf;
@@ -647,9 +759,9 @@ static int pair_entry(const LfGemmArgs* a, const LfTpArgs* t) {
   if (dropmix && !a->b_mn) return -5;
 #define LF_PAIR_DISPATCH(TPV)                                                                                  \
   do {                                                                                                         \
-    if (dropmix) return launch<true, 2, LF_EPI_BF16_DROPMIX, TPV>(p, tA, tB, tA2, tB2, pairs, st, tp);         \
-    if (a->b_mn) return launch<true, 1, LF_EPI_BF16, TPV>(p, tA, tB, tA2, tB2, pairs, st, tp);                 \
-    return launch<false, 1, LF_EPI_BF16, TPV>(p, tA, tB, tA2, tB2, pairs, st, tp);                             \
+    if (dropmix) return launch<true, LF_EPI_BF16_DROPMIX, TPV>(p, tA, tB, tA2, tB2, pairs, st, tp);         \
+    if (a->b_mn) return launch<true, LF_EPI_BF16, TPV>(p, tA, tB, tA2, tB2, pairs, st, tp);                 \
+    return launch<false, LF_EPI_BF16, TPV>(p, tA, tB, tA2, tB2, pairs, st, tp);                             \
   } while (0)
   if (mode == 1) LF_PAIR_DISPATCH(1);
   if (mode == 2) LF_PAIR_DISPATCH(2);

@@ -163,6 +163,43 @@ def test_gradient_kernels_split_long_segments_into_chunks(mixed_p):
         assert_close_two_rounds(da_all[a], _f32mm(ds[r0:r1].t(), xh), rtol=1e-3, atol=2e-2, msg=f"split lora_da[{a}]")
 
 
+@pytest.mark.parametrize("N", [768, 64])
+def test_pair_dx_dropout_walks_many_tiles_per_pair(N):
+    """The CTA-pair dX kernel with dropout puts the LoRA slab of the NEXT tile into the other
+    accumulator in the middle of the current main loop and masks it in place.  With four pairs and
+    twenty tiles every pair runs that hand-over several times; adapters differ inside a pair, one
+    has no dropout, one row tile has no adapter, and the last pair is half empty.  ``N = 64`` is
+    the single-main-block edge (the next slab is issued before the main product)."""
+    from lorafusion_b200.ops import lora_kernels as lk
+    from lorafusion_b200.ops import _native as nv
+    from lorafusion_b200.ops.gemm import launch_gemm
+    from lorafusion_b200.ops.philox import dropout_threshold, keep_mask
+
+    K, n, R = 1024, 4, 64
+    seg_adapters, seg_tiles = [2, 0, -1, 3, 1], [2, 1, 1, 3, 2]
+    M = 128 * sum(seg_tiles)
+    tile_adapter = _tile_adapters(seg_adapters, seg_tiles)
+    ps = [0.1, 0.0, 0.2, 0.3]
+    dy, w = _rand(M, N, seed=50), _rand(N, K, scale=0.03, seed=51)
+    ds = _rand(M, R, scale=0.1, seed=52)
+    a_all, _ = _adapters(n, N, K)
+    drop = lk.DropoutSpec(seed=99, stream_id=5, p=0.0,
+                          adapter_thresh16=torch.tensor([dropout_threshold(q) for q in ps], dtype=torch.int32,
+                                                        device="cuda"),
+                          adapter_inv_keep=torch.tensor([1 / (1 - q) for q in ps], device="cuda"))
+    out = torch.full((M, K), float("nan"), dtype=torch.bfloat16, device="cuda")
+    launch_gemm(pair=True, a=dy, b=w, out=out, M=M, N=K, K=N, b_mn=True, b2_mn=True, bn=256, nacc=2,
+                epi=nv.EPI_BF16_DROPMIX, a2=ds, b2=a_all.reshape(n * R, K), K2=R, b2_adapter_rows=R,
+                tile_adapter=tile_adapter, max_ctas=8, **drop.kwargs())
+    ref = _f32mm(dy, w)
+    row_adapter = tile_adapter.repeat_interleave(128).long()
+    for a in range(n):
+        rows = row_adapter == a
+        keep = keep_mask(M, K, ps[a], 99, 5).cuda()[rows]
+        ref[rows] += torch.where(keep, _f32mm(ds[rows], a_all[a]) / (1 - ps[a]), torch.zeros((), device="cuda"))
+    assert_close_two_rounds(out, ref, msg=f"pair dx dropout, contraction {N}")
+
+
 def test_dropout_keep_fraction():
     from lorafusion_b200.ops.philox import keep_mask
 
