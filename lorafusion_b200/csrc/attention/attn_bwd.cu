@@ -104,11 +104,12 @@ attn_dq_kernel(const AttnBwdParams p, const __grid_constant__ CUtensorMap tmQKV,
       mbar_init(&kv_empty[i], 1);
     }
     mbar_init(sdp_full, 1);
-    mbar_init(sdp_empty, 256);
-    mbar_init(ds_full, 256);
+    // one arrival per softmax warp (lane 0 after __syncwarp): 256 arrivals on one word serialise
+    mbar_init(sdp_empty, 8);
+    mbar_init(ds_full, 8);
     mbar_init(dq_done, 1);
     mbar_init(q_empty, 1);
-    mbar_init(dq_empty, 256);
+    mbar_init(dq_empty, 8);
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -193,13 +194,13 @@ attn_dq_kernel(const AttnBwdParams p, const __grid_constant__ CUtensorMap tmQKV,
       const float dlt = row_valid ? p.delta[(long long)h * p.M_total + grow] : 0.f;
       for (int j = 0; j < n_kv; ++j) {
         const int J = hi * n_kv + j;
-        if (!mbar_wait(sdp_full, J & 1, ctx, ERR_WAIT_TMEM_FULL)) {
+        if (!__all_sync(0xffffffffu, mbar_wait(sdp_full, J & 1, ctx, ERR_WAIT_TMEM_FULL))) {
           ok = false;
           break;
         }
         // sDS is still being read by the previous tile's dQ product (for j == 0 the previous
         // head's final store has already waited for it)
-        if (j > 0 && !mbar_wait(dq_done, (J - 1) & 1, ctx, ERR_WAIT_MISC)) {
+        if (j > 0 && !__all_sync(0xffffffffu, mbar_wait(dq_done, (J - 1) & 1, ctx, ERR_WAIT_MISC))) {
           ok = false;
           break;
         }
@@ -222,12 +223,15 @@ attn_dq_kernel(const AttnBwdParams p, const __grid_constant__ CUtensorMap tmQKV,
           att_store_row_chunk(sDS, r, c0 + cc * 32, ds);
         }
         tc_fence_before_sync();
-        mbar_arrive(sdp_empty);
         fence_proxy_async_smem();
-        mbar_arrive(ds_full);
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(sdp_empty);
+          mbar_arrive(ds_full);
+        }
       }
       if (!ok) break;
-      if (!mbar_wait(dq_done, (hi * n_kv + n_kv - 1) & 1, ctx, ERR_WAIT_MISC)) {
+      if (!__all_sync(0xffffffffu, mbar_wait(dq_done, (hi * n_kv + n_kv - 1) & 1, ctx, ERR_WAIT_MISC))) {
         ok = false;
         break;
       }
@@ -249,7 +253,8 @@ attn_dq_kernel(const AttnBwdParams p, const __grid_constant__ CUtensorMap tmQKV,
         }
       }
       tc_fence_before_sync();
-      mbar_arrive(dq_empty);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(dq_empty);
     }
   }
 
@@ -310,10 +315,10 @@ attn_dkdv_kernel(const AttnBwdParams p, const __grid_constant__ CUtensorMap tmQK
       mbar_init(&qd_empty[i], 1);
     }
     mbar_init(sdp_full, 1);
-    mbar_init(sdp_empty, 256);
-    mbar_init(p_full, 256);
+    mbar_init(sdp_empty, 8);  // one arrival per softmax warp
+    mbar_init(p_full, 8);
     mbar_init(dv_done, 1);
-    mbar_init(ds_full, 256);
+    mbar_init(ds_full, 8);
     mbar_init(dk_done, 1);
     *abort_flag = 0;
     fence_mbar_init();
@@ -394,11 +399,11 @@ attn_dkdv_kernel(const AttnBwdParams p, const __grid_constant__ CUtensorMap tmQK
       const long long grow = (long long)qrow0 + r;
       const float lse2 = row_valid ? p.lse[(long long)h * p.M_total + grow] * 1.4426950408889634f : 0.f;
       const float dlt = row_valid ? p.delta[(long long)h * p.M_total + grow] : 0.f;
-      if (!mbar_wait(sdp_full, it & 1, ctx, ERR_WAIT_TMEM_FULL)) {
+      if (!__all_sync(0xffffffffu, mbar_wait(sdp_full, it & 1, ctx, ERR_WAIT_TMEM_FULL))) {
         ok = false;
         break;
       }
-      if (it > 0 && !mbar_wait(dk_done, (it - 1) & 1, ctx, ERR_WAIT_MISC)) {
+      if (it > 0 && !__all_sync(0xffffffffu, mbar_wait(dk_done, (it - 1) & 1, ctx, ERR_WAIT_MISC))) {
         ok = false;
         break;
       }
@@ -422,8 +427,9 @@ attn_dkdv_kernel(const AttnBwdParams p, const __grid_constant__ CUtensorMap tmQK
         att_store_row_chunk(sPD, r, c0 + cc * 32, pv);
       }
       fence_proxy_async_smem();
-      mbar_arrive(p_full);
-      if (!mbar_wait(dv_done, it & 1, ctx, ERR_WAIT_MISC)) {
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_full);
+      if (!__all_sync(0xffffffffu, mbar_wait(dv_done, it & 1, ctx, ERR_WAIT_MISC))) {
         ok = false;
         break;
       }
@@ -443,11 +449,14 @@ attn_dkdv_kernel(const AttnBwdParams p, const __grid_constant__ CUtensorMap tmQK
         att_store_row_chunk(sPD, r, c0 + cc * 32, ds);
       }
       tc_fence_before_sync();
-      mbar_arrive(sdp_empty);
       fence_proxy_async_smem();
-      mbar_arrive(ds_full);
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(sdp_empty);
+        mbar_arrive(ds_full);
+      }
     }
-    if (ok && n_it > 0 && mbar_wait(dk_done, (n_it - 1) & 1, ctx, ERR_WAIT_MISC)) {
+    if (ok && n_it > 0 && __all_sync(0xffffffffu, mbar_wait(dk_done, (n_it - 1) & 1, ctx, ERR_WAIT_MISC))) {
       tc_fence_after_sync();
       const long long grow = (long long)row0 + r;  // key row owned by this thread
       __nv_bfloat16* krow = p.dqkv + grow * p.ld_qkv + p.k_col0 + g * ATT_D;

@@ -57,7 +57,6 @@ attn_fwd_kernel(const AttnFwdParams p, const __grid_constant__ CUtensorMap tm) {
   uint64_t* s_empty = bars + 7;   // [2]
   uint64_t* p_full = bars + 9;
   uint64_t* pv_done = bars + 10;
-  uint64_t* x_full = bars + 11;
   uint64_t* q_empty = bars + 12;  // every S = Q K^T of the current head has completed: sQ may be refilled
   uint64_t* o_empty = bars + 13;  // the softmax warps have read the finished O: the next head may overwrite it
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
@@ -80,13 +79,12 @@ attn_fwd_kernel(const AttnFwdParams p, const __grid_constant__ CUtensorMap tm) {
       mbar_init(&kv_full[i], 1);
       mbar_init(&kv_empty[i], 1);
       mbar_init(&s_full[i], 1);
-      mbar_init(&s_empty[i], 256);
+      mbar_init(&s_empty[i], 8);  // one arrival per softmax warp
     }
-    mbar_init(p_full, 256);
+    mbar_init(p_full, 8);
     mbar_init(pv_done, 1);
-    mbar_init(x_full, 256);
     mbar_init(q_empty, 1);
-    mbar_init(o_empty, 256);
+    mbar_init(o_empty, 8);
     *abort_flag = 0;
     fence_mbar_init();
     tma_prefetch_desc(&tm);
@@ -184,7 +182,13 @@ attn_fwd_kernel(const AttnFwdParams p, const __grid_constant__ CUtensorMap tm) {
     const int c0 = half * 64;
     const uint32_t lane_addr = uint32_t(q * 32) << 16;
     const float c = p.scale_log2e;
-    bool ok = true;
+    constexpr uint32_t FULL = 0xffffffffu;
+    // Synchronisation is kept cheap because it sits on the critical path of every key tile: the two
+    // warps that share a row quarter meet in a hardware named barrier (id 1 + q, 64 threads) for
+    // the row-max exchange, and every mbarrier gets ONE arrival per warp (256 arrivals on one
+    // barrier word serialise).  `good` is warp-uniform (the tcgen05.ld/st below are .sync.aligned);
+    // a failed wait is carried to the next named barrier, whose vote lets both warps leave together.
+    bool good = true, ok = true;
     for (int hi = 0; ok && hi < group; ++hi) {
       const int h = h0 + hi;
       float m_ref = -INFINITY, l = 0.f;
@@ -192,20 +196,23 @@ attn_fwd_kernel(const AttnFwdParams p, const __grid_constant__ CUtensorMap tm) {
         const int J = hi * n_kv + j;          // position in the flat sequence: S / P / K-V ring parities
         const int X = hi * (n_kv + 1) + j;    // exchanges through shared memory so far (one more per head)
         const int b = J & 1, xb = X & 1;
-        if (!mbar_wait(&s_full[b], (J >> 1) & 1, ctx, ERR_WAIT_TMEM_FULL)) {
-          ok = false;
-          break;
-        }
-        tc_fence_after_sync();
+        good = __all_sync(FULL, good && mbar_wait(&s_full[b], (J >> 1) & 1, ctx, ERR_WAIT_TMEM_FULL));
         float s[64];
+        if (good) {
+          tc_fence_after_sync();
 #pragma unroll
-        for (int cc = 0; cc < 2; ++cc) {
-          uint32_t(&dst)[32] = *reinterpret_cast<uint32_t(*)[32]>(&s[cc * 32]);
-          tmem_ld_32x32b_x32(tS[b] + lane_addr + c0 + cc * 32, dst);
+          for (int cc = 0; cc < 2; ++cc) {
+            uint32_t(&dst)[32] = *reinterpret_cast<uint32_t(*)[32]>(&s[cc * 32]);
+            tmem_ld_32x32b_x32(tS[b] + lane_addr + c0 + cc * 32, dst);
+          }
+          tmem_ld_wait();
+          tc_fence_before_sync();
+        } else {
+#pragma unroll
+          for (int col = 0; col < 64; ++col) s[col] = 0.f;
         }
-        tmem_ld_wait();
-        tc_fence_before_sync();
-        mbar_arrive(&s_empty[b]);
+        __syncwarp();
+        if (lane == 0 && good) mbar_arrive(&s_empty[b]);
         if (j == n_kv - 1) {
 #pragma unroll
           for (int col = 0; col < 64; ++col)
@@ -215,8 +222,8 @@ attn_fwd_kernel(const AttnFwdParams p, const __grid_constant__ CUtensorMap tm) {
 #pragma unroll
         for (int col = 1; col < 64; ++col) mx = fmaxf(mx, s[col]);
         xchg[xb * 256 + half * 128 + r] = mx;
-        mbar_arrive(x_full);
-        if (!mbar_wait(x_full, X & 1, ctx, ERR_WAIT_MISC)) {
+        good = named_bar_and_id(1 + q, 64, good);
+        if (!good) {
           ok = false;
           break;
         }
@@ -233,7 +240,7 @@ attn_fwd_kernel(const AttnFwdParams p, const __grid_constant__ CUtensorMap tm) {
             l *= alpha;
           }
         }
-        const bool warp_need = __any_sync(0xffffffffu, need);
+        const bool warp_need = __any_sync(FULL, need);
         const float mc = m_ref * c;
         float sum = 0.f;
 #pragma unroll
@@ -244,68 +251,67 @@ attn_fwd_kernel(const AttnFwdParams p, const __grid_constant__ CUtensorMap tm) {
         l += sum;
         if (j > 0) {
           // (for j == 0 the previous head's last P V was awaited by that head's final store)
-          if (!mbar_wait(pv_done, (J - 1) & 1, ctx, ERR_WAIT_MISC)) {
-            ok = false;
-            break;
-          }
+          good = __all_sync(FULL, mbar_wait(pv_done, (J - 1) & 1, ctx, ERR_WAIT_MISC));
+        }
+        if (good) {
           tc_fence_after_sync();
-        }
 #pragma unroll
-        for (int cc = 0; cc < 2; ++cc) {
-          float(&src)[32] = *reinterpret_cast<float(*)[32]>(&s[cc * 32]);
-          att_store_row_chunk(sP, r, c0 + cc * 32, src);
-        }
-        if (warp_need) {
-#pragma unroll 1
           for (int cc = 0; cc < 2; ++cc) {
-            uint32_t o[32];
-            tmem_ld_32x32b_x32(tO + lane_addr + c0 + cc * 32, o);
-            tmem_ld_wait();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-            tmem_st_32x32b_x32(tO + lane_addr + c0 + cc * 32, o);
+            float(&src)[32] = *reinterpret_cast<float(*)[32]>(&s[cc * 32]);
+            att_store_row_chunk(sP, r, c0 + cc * 32, src);
           }
-          tmem_st_wait();
+          if (warp_need) {
+#pragma unroll 1
+            for (int cc = 0; cc < 2; ++cc) {
+              uint32_t o[32];
+              tmem_ld_32x32b_x32(tO + lane_addr + c0 + cc * 32, o);
+              tmem_ld_wait();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+              tmem_st_32x32b_x32(tO + lane_addr + c0 + cc * 32, o);
+            }
+            tmem_st_wait();
+          }
+          fence_proxy_async_smem();
+          tc_fence_before_sync();
         }
-        fence_proxy_async_smem();
-        tc_fence_before_sync();
-        mbar_arrive(p_full);
+        __syncwarp();
+        if (lane == 0 && good) mbar_arrive(p_full);
       }
       if (!ok) break;
       // ---- this head is complete: combine the two partial row sums (both relative to the same
       // m_ref), normalise, store, and hand the O accumulator to the next head
-      const int Xs = hi * (n_kv + 1) + n_kv;
       xchg[512 + half * 128 + r] = l;
-      mbar_arrive(x_full);
-      if (!mbar_wait(x_full, Xs & 1, ctx, ERR_WAIT_MISC) ||
-          !mbar_wait(pv_done, (hi * n_kv + n_kv - 1) & 1, ctx, ERR_WAIT_MISC)) {
-        ok = false;
-        break;
-      }
+      good = named_bar_and_id(1 + q, 64, good);
+      if (!good) break;
       l += xchg[512 + (half ^ 1) * 128 + r];
-      tc_fence_after_sync();
-      const float inv_l = 1.f / l;
-      const long long grow = (long long)row0 + r;
-      __nv_bfloat16* orow = p.out + grow * p.ldo + h * ATT_D + c0;
+      good = __all_sync(FULL, mbar_wait(pv_done, (hi * n_kv + n_kv - 1) & 1, ctx, ERR_WAIT_MISC));
+      if (good) {
+        tc_fence_after_sync();
+        const float inv_l = 1.f / l;
+        const long long grow = (long long)row0 + r;
+        __nv_bfloat16* orow = p.out + grow * p.ldo + h * ATT_D + c0;
 #pragma unroll 1
-      for (int cc = 0; cc < 2; ++cc) {
-        uint32_t o[32];
-        tmem_ld_32x32b_x32(tO + lane_addr + c0 + cc * 32, o);
-        tmem_ld_wait();
-        if (r < rows) {
+        for (int cc = 0; cc < 2; ++cc) {
+          uint32_t o[32];
+          tmem_ld_32x32b_x32(tO + lane_addr + c0 + cc * 32, o);
+          tmem_ld_wait();
+          if (r < rows) {
 #pragma unroll
-          for (int gq = 0; gq < 4; ++gq) {
-            st_global_v4(orow + cc * 32 + gq * 8,
-                         pack_bf16x2(__uint_as_float(o[gq * 8 + 0]) * inv_l, __uint_as_float(o[gq * 8 + 1]) * inv_l),
-                         pack_bf16x2(__uint_as_float(o[gq * 8 + 2]) * inv_l, __uint_as_float(o[gq * 8 + 3]) * inv_l),
-                         pack_bf16x2(__uint_as_float(o[gq * 8 + 4]) * inv_l, __uint_as_float(o[gq * 8 + 5]) * inv_l),
-                         pack_bf16x2(__uint_as_float(o[gq * 8 + 6]) * inv_l, __uint_as_float(o[gq * 8 + 7]) * inv_l));
+            for (int gq = 0; gq < 4; ++gq) {
+              st_global_v4(orow + cc * 32 + gq * 8,
+                           pack_bf16x2(__uint_as_float(o[gq * 8 + 0]) * inv_l, __uint_as_float(o[gq * 8 + 1]) * inv_l),
+                           pack_bf16x2(__uint_as_float(o[gq * 8 + 2]) * inv_l, __uint_as_float(o[gq * 8 + 3]) * inv_l),
+                           pack_bf16x2(__uint_as_float(o[gq * 8 + 4]) * inv_l, __uint_as_float(o[gq * 8 + 5]) * inv_l),
+                           pack_bf16x2(__uint_as_float(o[gq * 8 + 6]) * inv_l, __uint_as_float(o[gq * 8 + 7]) * inv_l));
+            }
           }
         }
+        if (half == 0 && r < rows) p.lse[(long long)h * p.M_total + grow] = m_ref * p.scale + __logf(l);
+        tc_fence_before_sync();
       }
-      if (half == 0 && r < rows) p.lse[(long long)h * p.M_total + grow] = m_ref * p.scale + __logf(l);
-      tc_fence_before_sync();
-      mbar_arrive(o_empty);
+      __syncwarp();
+      if (lane == 0 && good) mbar_arrive(o_empty);
     }
   }
 

@@ -137,6 +137,22 @@ __device__ __forceinline__ bool named_bar_and(bool pred) {
   return out != 0;
 }
 
+// Same with the barrier id and the thread count in registers (e.g. one barrier per pair of warps).
+__device__ __forceinline__ bool named_bar_and_id(int id, int nthreads, bool pred) {
+  uint32_t out;
+  asm volatile(
+      "{\n"
+      ".reg .pred pin, pout;\n"
+      "setp.ne.u32 pin, %1, 0;\n"
+      "bar.red.and.pred pout, %2, %3, pin;\n"
+      "selp.u32 %0, 1, 0, pout;\n"
+      "}\n"
+      : "=r"(out)
+      : "r"(uint32_t(pred)), "r"(id), "r"(nthreads)
+      : "memory");
+  return out != 0;
+}
+
 // ----------------------------------------------------------------------------------
 // cross-CTA / cross-GPU flag waits (system scope, acquire)
 // ----------------------------------------------------------------------------------

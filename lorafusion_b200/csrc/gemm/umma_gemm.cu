@@ -32,6 +32,10 @@ namespace lf {
 constexpr int BM = 128;
 constexpr int BK = 64;
 constexpr int kNumMaskWarps = 8;
+// The dropout warps work in groups on DIFFERENT stages at the same time: one stage's rewrite is a
+// chain of latencies (barrier poll, shared-memory load, seven Philox rounds, store, proxy fence),
+// and eight warps on one stage at a time left the kernel bound by that chain, not by issue slots.
+constexpr int kMaskGroups = 4;
 
 struct GemmKParams {
   int M, N;
@@ -172,7 +176,8 @@ __global__ void __launch_bounds__(192 + ((MASK_A || NF4B) ? 32 * kNumMaskWarps :
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
-      mbar_init(&ready[s], kNumMaskWarps);  // lane 0 of every rewriting warp reports for its warp
+      // lane 0 of every warp that rewrites the stage reports for its warp
+      mbar_init(&ready[s], MASK_A ? kNumMaskWarps / kMaskGroups : kNumMaskWarps);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tfull[b], 1);
@@ -686,8 +691,9 @@ __global__ void __launch_bounds__(192 + ((MASK_A || NF4B) ? 32 * kNumMaskWarps :
     }
   } else if (MASK_A) {
     // ------------------- dropout mask applied to the A stage in place -------------------
-    const int mt = threadIdx.x - 192;  // 0 .. 32*kNumMaskWarps-1
-    constexpr int NMT = 32 * kNumMaskWarps;
+    constexpr int NMT = 32 * kNumMaskWarps / kMaskGroups;  // threads that share one stage
+    const int grp = (threadIdx.x - 192) / NMT;             // this thread's group takes stages grp, grp + kMaskGroups, ...
+    const int mt = (threadIdx.x - 192) % NMT;
     int it = 0;
     bool ok = true;
     for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
@@ -702,6 +708,7 @@ __global__ void __launch_bounds__(192 + ((MASK_A || NF4B) ? 32 * kNumMaskWarps :
         inv_keep = p.adapter_inv_keep[t.adapter];
       }
       for (int kb = 0; kb < total; ++kb, ++it) {
+        if (it % kMaskGroups != grp) continue;
         const int s = it % STAGES;
         const uint32_t ph = (it / STAGES) & 1;
         // one answer per warp: its lanes meet again in __syncwarp below

@@ -21,7 +21,7 @@
 // issuer (leader CTA only), warps 2..9 = epilogue (both).  Barriers: "stage full" lives in
 // the leader and is credited by both CTAs' loads; "stage empty" and "accumulator full" exist
 // in both CTAs and are signalled by two tcgen05.commit (own + peer address); "accumulator
-// empty" lives in the leader and collects 256 arrivals.  All waits are bounded.
+// empty" lives in the leader and collects one arrival per epilogue warp of both CTAs.  All waits are bounded.
 #include <stdio.h>
 
 #include "../common/launch.h"
@@ -158,9 +158,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS + (TP !
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tfull[b], 1);
-      mbar_init(&tempty[b], 2 * 32 * PAIR_EPI_WARPS);  // every epilogue thread of both CTAs
+      mbar_init(&tempty[b], 2 * PAIR_EPI_WARPS);  // lane 0 of every epilogue warp of both CTAs
       mbar_init(&sfull[b], 1);
-      mbar_init(&masked[b], 2 * 32 * PAIR_EPI_WARPS);
+      mbar_init(&masked[b], 2 * PAIR_EPI_WARPS);
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -375,7 +375,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS + (TP !
     // only reports in.
     auto mask_slab = [&](const Tile& t, int iter) -> bool {
       const int buf = iter % NBUF;
-      bool got = mbar_wait(&sfull[buf], uint32_t(iter / NBUF) & 1, ctx, ERR_WAIT_TMEM_FULL);
+      // warp-uniform: the tcgen05.ld/st below are .sync.aligned, and the warp reports in as one
+      bool got = __all_sync(0xffffffffu, mbar_wait(&sfull[buf], uint32_t(iter / NBUF) & 1, ctx, ERR_WAIT_TMEM_FULL));
       // the reduce-scatter epilogue meets in named barriers: one answer for all 256 threads
       if (TP == 2) got = named_bar_and<1, 32 * PAIR_EPI_WARPS>(got);
       if (!got) return false;
@@ -414,7 +415,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS + (TP !
         tmem_st_wait();
       }
       tc_fence_before_sync();
-      mbar_arrive_cluster(mapa_shared(&masked[buf], 0));
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(mapa_shared(&masked[buf], 0));
       return true;
     };
 
@@ -431,7 +433,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS + (TP !
       }
       const int buf = tile_iter % NBUF;
       const uint32_t bph = (tile_iter / NBUF) & 1;
-      bool got = mbar_wait(&tfull[buf], bph, ctx, ERR_WAIT_TMEM_FULL);
+      bool got = __all_sync(0xffffffffu, mbar_wait(&tfull[buf], bph, ctx, ERR_WAIT_TMEM_FULL));
       // the reduce-scatter epilogue ends in a named barrier of its 256 threads: one answer for all
       if (TP == 2) got = named_bar_and<1, 32 * PAIR_EPI_WARPS>(got);
       if (!got) {
@@ -476,7 +478,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS + (TP !
         }
       }
       tc_fence_before_sync();
-      mbar_arrive_cluster(mapa_shared(&tempty[buf], 0));
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(mapa_shared(&tempty[buf], 0));
       if (TP == 2) {
         // all 256 epilogue threads of this CTA have stored their part of the 128 x 256 partial
         __threadfence_system();
