@@ -337,7 +337,8 @@ def main():
     clocks = sampler.stop()
     launches = _native.launch_count() - launches0
     ms_e2e = ev_begin.elapsed_time(ev_end)
-    ms = sum(a.elapsed_time(b) for a, b in ev)
+    step_ms = [a.elapsed_time(b) for a, b in ev]
+    ms = sum(step_ms)
     toks = float(sum(tokens_per_step[args.warmup:])) if tp_rank == 0 else 0.0   # a tp pair's tokens count once
     stats = torch.tensor([ms, ms_e2e, toks], dtype=torch.float64, device=device)
     if world > 1:
@@ -346,6 +347,9 @@ def main():
         sm = stats.clone()
         dist.all_reduce(sm, op=dist.ReduceOp.SUM)
         ms, ms_e2e, toks = float(mx[0]), float(mx[1]), float(sm[2])
+        per_step = torch.tensor(step_ms, dtype=torch.float64, device=device)
+        dist.all_reduce(per_step, op=dist.ReduceOp.MAX)
+        step_ms = per_step.tolist()
     _native.check_device_errors()
     loss_val = last_loss
     value = toks / (ms / 1e3)
@@ -385,6 +389,7 @@ def main():
                        "(train.data.pack_balanced_dp_step)",
             "balance": balance,
             "same_policy_at_every_n": like_for_like,
+            "step_ms_max_over_ranks": [round(v, 3) for v in step_ms],
             "final_loss": loss_val,
             "peak_memory_gib": {"allocated": round(torch.cuda.max_memory_allocated() / 2**30, 1),
                                 "reserved": round(torch.cuda.max_memory_reserved() / 2**30, 1)},

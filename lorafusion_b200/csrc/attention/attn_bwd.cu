@@ -216,7 +216,7 @@ attn_dq_kernel(const AttnBwdParams p, const __grid_constant__ CUtensorMap tmQKV,
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
             const int col = c0 + cc * 32 + i;
-            float pv = exp2f(__uint_as_float(sv[i]) * p.scale_log2e - lse2);
+            float pv = fast_exp2(__uint_as_float(sv[i]) * p.scale_log2e - lse2);
             if (!row_valid || (diag && col > r)) pv = 0.f;
             ds[i] = pv * (__uint_as_float(dv[i]) - dlt) * p.scale;
           }
@@ -418,7 +418,7 @@ attn_dkdv_kernel(const AttnBwdParams p, const __grid_constant__ CUtensorMap tmQK
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
           const int col = c0 + cc * 32 + i;
-          float x = exp2f(__uint_as_float(sv[i]) * p.scale_log2e - lse2);
+          float x = fast_exp2(__uint_as_float(sv[i]) * p.scale_log2e - lse2);
           if (!row_valid || (diag && col > r)) x = 0.f;
           pv[i] = x;
         }

@@ -67,6 +67,15 @@ __device__ __forceinline__ void att_mma_mnmn(uint32_t tmem_d, uint32_t sA, uint3
   }
 }
 
+// 2^x on the special-function unit, one instruction (relative error about 2^-22, results below
+// 2^-126 flush to zero): exp2f() wraps the same instruction in range handling that the softmax
+// does not need (its arguments are bounded above by the lazy-rescaling threshold).
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 // Writes 32 consecutive values of row `r` (columns [c0, c0+32), c0 a multiple of 32) of a
 // [128 x 128] bf16 tile into its swizzled two-panel shared-memory layout.
 __device__ __forceinline__ void att_store_row_chunk(uint8_t* smem_tile, int r, int c0,
