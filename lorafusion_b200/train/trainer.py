@@ -164,6 +164,14 @@ class MultiLoRATrainer:
         n_layers = len(self.stage.layers)
         if self._fused_sync is None or not self.overlap_grad_sync or n_layers < 2 * self.sync_layer_groups:
             return None
+        if self.tp_size > 1:
+            # Under tensor parallelism the compute stream's own kernels wait on a peer (the fused
+            # all-gather -> GEMM / GEMM -> reduce-scatter kernels).  A sync kernel spinning on a side
+            # stream can then hold the SMs a GEMM of this GPU needs while the rank it waits for is
+            # itself behind a GEMM that waits for this GPU: a cycle over the four ranks of two
+            # replicas that only the bounded waits break (seen once as "timeout waiting for a TMA
+            # stage" on 4 GPUs).  Kernels that wait on other GPUs are kept in ONE stream order.
+            return None
         if self._sync_stream is None:
             self._sync_stream = torch.cuda.Stream(self.device)
         active = list(range(len(self.adapters)) if active_adapters is None else active_adapters)
