@@ -18,7 +18,7 @@ import torch
 from ..models.config import AdapterSpec, get_model_config
 from ..models.decoder import DecoderStage
 from ..ops import _native
-from ..parallel.pipeline import even_layer_partition
+from ..parallel.pipeline import PipeModel
 from ..train.data import MicroBatchSpec, build_packed_batch
 
 
@@ -27,8 +27,7 @@ def run(model: str = "small", stages: int = 4, device: str = "cuda:0", seed: int
     adapters = [AdapterSpec("lora_0", r=16, dropout=0.1), AdapterSpec("lora_1", r=8, dropout=0.0)]
     kw = dict(init_b_std=0.01, seed=seed, recompute=True, with_optimizer_state=False)
     whole = DecoderStage(cfg, adapters, device, **kw)
-    parts = [DecoderStage(cfg, adapters, device, layer_start=a, layer_end=b, **kw).adopt_weights(whole)
-             for a, b in even_layer_partition(cfg.num_layers, stages)]
+    parts = [PipeModel.from_model(whole, stage_idx=s, num_stages=stages, **kw) for s in range(stages)]
     batch = build_packed_batch(MicroBatchSpec([(0, [300, 84]), (1, [128, 200])]), adapters, cfg.vocab_size,
                                device, seed=seed)
     loss_whole = float(whole.forward_backward(batch))

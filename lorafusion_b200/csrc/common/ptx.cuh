@@ -36,6 +36,10 @@ constexpr unsigned long long kPeerWaitNs = 10000000000ull;   // 10 s for cross-G
 struct AbortCtx {
   int* err_word;            // global, may be nullptr
   volatile int* abort_smem; // CTA-wide flag in shared memory
+  // Limit of the intra-kernel waits.  A kernel whose TMA producer waits for another GPU (the
+  // tensor-parallel fusions) sets it above the peer limit: its consumers must not give up on a
+  // stage while the producer is still legitimately waiting for a late peer.
+  unsigned long long local_wait_ns = kLocalWaitNs;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -109,7 +113,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
     if (mbar_try_wait(bar, parity)) return true;
     if ((it & 0xff) == 0) {
       if (aborted(ctx)) return false;
-      if (globaltimer_ns() - t0 > kLocalWaitNs) {
+      if (globaltimer_ns() - t0 > ctx.local_wait_ns) {
         raise_abort(ctx, code);
         return false;
       }

@@ -170,7 +170,7 @@ __global__ void __launch_bounds__(192 + ((MASK_A || NF4B) ? 32 * kNumMaskWarps :
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  AbortCtx ctx{p.err, abort_flag};
+  AbortCtx ctx{p.err, abort_flag, TP != 0 ? kPeerWaitNs + kLocalWaitNs : kLocalWaitNs};
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {

@@ -147,7 +147,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS + (TP !
   const uint32_t cta = cluster_ctarank();  // 0 = leader
   const int pair_id = blockIdx.x >> 1;
   const int num_pairs = gridDim.x >> 1;
-  AbortCtx ctx{p.err, abort_flag};
+  AbortCtx ctx{p.err, abort_flag, TP != 0 ? kPeerWaitNs + kLocalWaitNs : kLocalWaitNs};
   // main-loop block before which the next tile's slab is slipped in (slab-first variant)
   const int ks = SLAB_FIRST ? p.nkb_main / 2 : p.nkb_main;
 

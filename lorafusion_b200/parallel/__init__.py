@@ -8,12 +8,12 @@ Names follow the reference where it has a counterpart
 
 from .health import HealthMonitor, PeerFailure
 from .layout import ParallelLayout, ParallelState, initialize_parallel_state
-from .pipeline import (EMPTY_BATCH_MAGIC_TOKEN, PipelineMicrobatch, PipelineRuntime, PipelineStats,
+from .pipeline import (EMPTY_BATCH_MAGIC_TOKEN, PipeModel, PipelineMicrobatch, PipelineRuntime, PipelineStats,
                        even_layer_partition, get_pipeline_stage_layer_indices,
                        multi_lora_get_forward_backward_func)
 
 __all__ = [
     "HealthMonitor", "PeerFailure", "ParallelLayout", "ParallelState", "initialize_parallel_state",
-    "EMPTY_BATCH_MAGIC_TOKEN", "PipelineMicrobatch", "PipelineRuntime", "PipelineStats",
+    "EMPTY_BATCH_MAGIC_TOKEN", "PipeModel", "PipelineMicrobatch", "PipelineRuntime", "PipelineStats",
     "even_layer_partition", "get_pipeline_stage_layer_indices", "multi_lora_get_forward_backward_func",
 ]

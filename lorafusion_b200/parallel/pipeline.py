@@ -57,6 +57,40 @@ def get_pipeline_stage_layer_indices(num_layers: int, num_stages: int, stage_idx
     return list(range(s, e))
 
 
+class PipeModel:
+    """Factory of pipeline stages: ``PipeModel.from_model(model, stage_idx=s, num_stages=n)``
+    returns the :class:`~lorafusion_b200.models.decoder.DecoderStage` that owns stage ``s``'s
+    layers (embedding on the first stage, final norm + lm_head + loss on the last).
+
+    ``model`` is either a whole-model ``DecoderStage`` -- the new stage then SHARES its frozen
+    weights and copies its adapter weights, which is how a partitioned run is compared with the
+    unpartitioned one -- or a ``ModelConfig``, in which case the stage is built on its own
+    (random-init or NF4 weights of that architecture; every rank of a multi-GPU job does this for
+    its own stage only, so no rank ever holds the whole model).  Counterpart of
+    ``PipeModel.from_model`` (``lorafusion/pipeline_parallel/pipe_module.py:156-196``), which
+    slices the layer list of a loaded HF model."""
+
+    @staticmethod
+    def from_model(model, *, stage_idx: int, num_stages: int, adapters=None, device=None, **stage_kwargs):
+        from ..models.decoder import DecoderStage
+
+        if isinstance(model, DecoderStage):
+            cfg = model.cfg
+            adapters = model.adapters if adapters is None else adapters
+            device = model.device if device is None else device
+        else:
+            cfg = model
+            if adapters is None or device is None:
+                raise ValueError("building a stage from a ModelConfig needs adapters= and device=")
+        if not 0 <= stage_idx < num_stages:
+            raise ValueError(f"stage_idx {stage_idx} outside [0, {num_stages})")
+        start, end = even_layer_partition(cfg.num_layers, num_stages)[stage_idx]
+        stage = DecoderStage(cfg, adapters, device, layer_start=start, layer_end=end, **stage_kwargs)
+        if isinstance(model, DecoderStage):
+            stage.adopt_weights(model)
+        return stage
+
+
 # The reference marks a no-op microbatch by sending input ids filled with this value
 # (``lorafusion/pipeline_parallel/multi_lora_schedule.py``); here the schedule is known to every
 # stage, so ``PipelineMicrobatch.is_empty`` carries the information and nothing is sent.  The

@@ -40,6 +40,19 @@ def mismatch_report(actual: torch.Tensor, expected: torch.Tensor, rtol: float, a
     return False, "\n".join(lines), ratio
 
 
+def verbose_allclose(actual: torch.Tensor, expected: torch.Tensor, rtol: float | None = None,
+                     atol: float | None = None, msg: str = "", print_fn=print) -> bool:
+    """``allclose`` that says what differs: prints the count, the share and the first few
+    positions of the mismatches and returns whether the tensors are close (it never raises).
+    Counterpart of ``verbose_allclose`` in ``lorafusion/utils/testing.py:18-95``."""
+    tol = DEFAULT_TOL.get(actual.dtype, DEFAULT_TOL[torch.float32])
+    ok, text, _ = mismatch_report(actual, expected, tol["rtol"] if rtol is None else rtol,
+                                  tol["atol"] if atol is None else atol)
+    if not ok:
+        print_fn(f"{msg}: {text}" if msg else text)
+    return ok
+
+
 def assert_close(actual: torch.Tensor, expected: torch.Tensor, rtol: float | None = None,
                  atol: float | None = None, msg: str = "") -> None:
     tol = DEFAULT_TOL.get(actual.dtype, DEFAULT_TOL[torch.float32])

@@ -116,3 +116,23 @@ def test_figure_drivers_draw_published_and_measured_data(tmp_path):
     (tmp_path / "l.jsonl").write_text("\n".join(json.dumps(r) for r in layer))
     p, = figures.main(["layer-perf", "--results", str(tmp_path / "l.jsonl"), "--out", str(tmp_path)])
     assert "llama-3.1-8b" in p.read_text()
+
+
+def test_packed_dummy_inputs_and_verbose_allclose():
+    """Helpers with the reference's names: packed varlen inputs (positions restart per sequence,
+    padding forms one more sequence) and an allclose that reports instead of raising."""
+    import torch
+
+    from lorafusion_b200.utils import create_packed_dummy_inputs, verbose_allclose
+
+    d = create_packed_dummy_inputs(32, [5, 3], multiple_of=16, device="cpu", return_labels=True,
+                                   return_inputs_embeds=True, seed=1)
+    assert d["cu_seq_lens_q"].tolist() == [0, 5, 8, 16] and d["cu_seq_lens_q"].dtype == torch.int32
+    assert d["position_ids"][0].tolist() == [0, 1, 2, 3, 4, 0, 1, 2] + list(range(8))
+    assert d["input_ids"].shape == (1, 16) and int(d["input_ids"].max()) < 10000
+    assert d["inputs_embeds"].shape == (1, 16, 32) and d["labels"].shape == (1, 16)
+    assert d["max_length_q"] == 8
+    said = []
+    assert verbose_allclose(torch.ones(4), torch.ones(4), print_fn=said.append) and not said
+    assert not verbose_allclose(torch.ones(4), torch.tensor([1.0, 1.0, 2.0, 1.0]), msg="x", print_fn=said.append)
+    assert "1/4 mismatched" in said[0]

@@ -274,6 +274,35 @@ def test_loopback_runs_the_copy_and_reduce_warps_on_one_gpu(world, pair):
         ref = mine[:ms] + sum(o.float()[:ms] for o in others) + res.float()
         assert_close_two_rounds(out, ref, atol=2e-2, msg=f"loop-back gemm_rs it{it}")
 
+        if it < 2:
+            # ---- the backward forms with dropout: the weight is consumed MN-major and the LoRA slab is
+            # multiplied by the regenerated mask (CTA-pair kernels: in place in TMEM before the main
+            # product lands on top; single-CTA template: second accumulator mixed in the epilogue)
+            from lorafusion_b200.ops import lora_kernels as lk
+            from lorafusion_b200.ops.philox import keep_mask
+
+            p_drop = 0.25
+            drop = lk.DropoutSpec(seed=4321 + it, stream_id=11, p=p_drop).kwargs()
+            keep = keep_mask(T, N, p_drop, 4321 + it, 11).to(dev)
+            dy_full, ds_full = rnd(T, K, seed=100 + it), rnd(T, R, scale=0.1, seed=110 + it)
+            wt, a2 = rnd(K, N, scale=0.05, seed=120 + it), rnd(1, R, N, scale=0.05, seed=130 + it)
+            ctx.gather_view(T, K).copy_(dy_full)
+            ctx.gather2_view(T, R).copy_(ds_full)
+            ctx.loopback_arm_gather(T)
+            dx = ag_gemm(ctx, T, K, wt, w_mn=True, slab_cols=R, b2=a2, b2_adapter_rows=R, dropout_kwargs=drop)
+            torch.cuda.synchronize()
+            _native.check_device_errors()
+            slab = torch.where(keep, ds_full.float() @ a2[0].float() / (1 - p_drop), torch.zeros((), device=dev))
+            assert_close_two_rounds(dx, dy_full.float() @ wt.float() + slab, msg=f"loop-back ag_gemm dropout it{it}")
+            ctx.loopback_arm_reduce(T, N, others)
+            outd = gemm_rs(ctx, dy_full, wt, w_mn=True, s=ds_full, b2=a2, b2_adapter_rows=R, dropout_kwargs=drop,
+                           residual=res)
+            torch.cuda.synchronize()
+            _native.check_device_errors()
+            mine = (dy_full.float() @ wt.float() + slab).to(torch.bfloat16).float()
+            assert_close_two_rounds(outd, mine[:ms] + sum(o.float()[:ms] for o in others) + res.float(), atol=2e-2,
+                                    msg=f"loop-back gemm_rs dropout it{it}")
+
         if it == 0:
             # ---- the same two fused kernels reading their weight shard as NF4, expanded in the main loop
             from lorafusion_b200.ops.nf4 import dequantize_nf4_reference, quantize_nf4
