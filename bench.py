@@ -76,6 +76,8 @@ def parse_args():
 
 
 def reference_arm(args) -> None:
+    if int(os.environ.get("RANK", "0")) != 0:   # one line per job, from rank 0
+        return
     print(json.dumps({
         "impl": "reference",
         "unavailable": "pip install of the reference yields only lorafusion/__init__.py (its pyproject lists "

@@ -70,19 +70,32 @@ attn_dq_kernel(const AttnBwdParams p, const __grid_constant__ CUtensorMap tmQKV,
                                              ~uintptr_t(1023));
   uint8_t* sQ = smem;
   uint8_t* sDO = smem + ATT_TILE_BYTES;
-  uint8_t* sKV = smem + 2 * ATT_TILE_BYTES;  // stage s: K, V
+  // Three K stages and one V stage: K of a tile is read twice (S early, dQ last), V once (dP), so
+  // a V slot is free early and one suffices, while the K of tile J + 2 must already be on its way
+  // during tile J (with two K stages its load could only start after dQ of tile J, and the load
+  // latency sat between two tiles).
+  uint8_t* sK3 = smem + 2 * ATT_TILE_BYTES;  // K stage s at s * 32 KB
+  uint8_t* sV = smem + 5 * ATT_TILE_BYTES;
   uint8_t* sDS = smem + 6 * ATT_TILE_BYTES;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 7 * ATT_TILE_BYTES);
   uint64_t* q_full = bars;
-  uint64_t* kv_full = bars + 1;
-  uint64_t* kv_empty = bars + 3;
-  uint64_t* sdp_full = bars + 5;
-  uint64_t* sdp_empty = bars + 6;
+  uint64_t* k_full = bars + 1;    // [3]
+  uint64_t* v_full = bars + 4;
+  uint64_t* v_empty = bars + 15;
+  uint64_t* k_empty = bars + 16;  // [3]
+  // S has two TMEM buffers and barriers of its own, dP one: S of tile J + 1 is issued while the
+  // element-wise warps still work on tile J, and they turn it into P (the exponentials) while the
+  // tensor pipe produces dP of the same tile.  With S and dP behind one barrier the tensor pipe and
+  // the element-wise warps strictly took turns.
+  uint64_t* s_full = bars + 5;     // [2]
   uint64_t* ds_full = bars + 7;
   uint64_t* dq_done = bars + 8;
   uint64_t* q_empty = bars + 9;    // every S / dP product of the current head has completed: sQ, sDO may be refilled
   uint64_t* dq_empty = bars + 10;  // the finished dQ has been read: the next head may overwrite the accumulator
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
+  uint64_t* s_empty = bars + 11;   // [2]
+  uint64_t* dp_full = bars + 13;
+  uint64_t* dp_empty = bars + 14;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 19);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -99,13 +112,19 @@ attn_dq_kernel(const AttnBwdParams p, const __grid_constant__ CUtensorMap tmQKV,
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&kv_full[i], 1);
-      mbar_init(&kv_empty[i], 1);
+    for (int i = 0; i < 3; ++i) {
+      mbar_init(&k_full[i], 1);
+      mbar_init(&k_empty[i], 1);
     }
-    mbar_init(sdp_full, 1);
-    // one arrival per softmax warp (lane 0 after __syncwarp): 256 arrivals on one word serialise
-    mbar_init(sdp_empty, 8);
+    mbar_init(v_full, 1);
+    mbar_init(v_empty, 1);
+    // one arrival per element-wise warp (lane 0 after __syncwarp): 256 arrivals on one word serialise
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&s_full[i], 1);
+      mbar_init(&s_empty[i], 8);
+    }
+    mbar_init(dp_full, 1);
+    mbar_init(dp_empty, 8);
     mbar_init(ds_full, 8);
     mbar_init(dq_done, 1);
     mbar_init(q_empty, 1);
@@ -121,7 +140,8 @@ attn_dq_kernel(const AttnBwdParams p, const __grid_constant__ CUtensorMap tmQKV,
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tS = tmem_base, tDP = tmem_base + 128, tDQ = tmem_base + 256;
+  const uint32_t tS[2] = {tmem_base, tmem_base + 128};
+  const uint32_t tDP = tmem_base + 256, tDQ = tmem_base + 384;
 
   if (warp == 0) {
     if (lane == 0) {
@@ -129,16 +149,13 @@ attn_dq_kernel(const AttnBwdParams p, const __grid_constant__ CUtensorMap tmQKV,
       for (int hi = 0; ok && hi < group; ++hi) {
         for (int j = 0; j < n_kv; ++j) {
           const int J = hi * n_kv + j;
-          const int s = J & 1;
-          if (!mbar_wait(&kv_empty[s], ((J >> 1) & 1) ^ 1, ctx, ERR_WAIT_EMPTY)) {
+          const int s = J % 3;
+          if (!mbar_wait(&k_empty[s], ((J / 3) & 1) ^ 1, ctx, ERR_WAIT_EMPTY)) {
             ok = false;
             break;
           }
-          mbar_expect_tx(&kv_full[s], 2 * ATT_TILE_BYTES);
-          uint8_t* sK = sKV + s * 2 * ATT_TILE_BYTES;
-          att_load_tile(sK, &tmQKV, &kv_full[s], p.k_col0 + g * ATT_D, seq_row0 + j * ATT_TILE);
-          att_load_tile(sK + ATT_TILE_BYTES, &tmQKV, &kv_full[s], p.v_col0 + g * ATT_D,
-                        seq_row0 + j * ATT_TILE);
+          mbar_expect_tx(&k_full[s], ATT_TILE_BYTES);
+          att_load_tile(sK3 + s * ATT_TILE_BYTES, &tmQKV, &k_full[s], p.k_col0 + g * ATT_D, seq_row0 + j * ATT_TILE);
           if (j == 0) {
             if (hi > 0 && !mbar_wait(q_empty, (hi - 1) & 1, ctx, ERR_WAIT_EMPTY)) {
               ok = false;
@@ -148,35 +165,64 @@ attn_dq_kernel(const AttnBwdParams p, const __grid_constant__ CUtensorMap tmQKV,
             att_load_tile(sQ, &tmQKV, q_full, p.q_col0 + (h0 + hi) * ATT_D, row0);
             att_load_tile(sDO, &tmDO, q_full, (h0 + hi) * ATT_D, row0);
           }
+          if (!mbar_wait(v_empty, (J & 1) ^ 1, ctx, ERR_WAIT_EMPTY)) {
+            ok = false;
+            break;
+          }
+          mbar_expect_tx(v_full, ATT_TILE_BYTES);
+          att_load_tile(sV, &tmQKV, v_full, p.v_col0 + g * ATT_D, seq_row0 + j * ATT_TILE);
         }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      bool ok = true;
+      // Issue order: S(0), dP(0), then per tile J: S(J + 1) early, [dS(J) ready] dP(J + 1), dQ(J).
+      auto issue_s = [&](int J1) -> bool {   // S of tile J1 into its buffer; K (and for a new head Q) must have landed
+        const int hi1 = J1 / n_kv, j1 = J1 - hi1 * n_kv;
+        const int b1 = J1 & 1;
+        const uint32_t ph = (J1 >> 1) & 1;
+        if ((j1 == 0 && !mbar_wait(q_full, hi1 & 1, ctx, ERR_WAIT_FULL)) ||
+            !mbar_wait(&k_full[J1 % 3], (J1 / 3) & 1, ctx, ERR_WAIT_FULL) ||
+            !mbar_wait(&s_empty[b1], ph ^ 1, ctx, ERR_WAIT_TMEM_EMPTY))
+          return false;
+        tc_fence_after_sync();
+        att_mma_kk(tS[b1], smem_u32(sQ), smem_u32(sK3 + (J1 % 3) * ATT_TILE_BYTES), false);
+        tc_commit(&s_full[b1]);
+        return true;
+      };
+      auto issue_dp = [&](int J1) -> bool {  // dP of tile J1 (dO of its head was awaited by issue_s(J1))
+        const int hi1 = J1 / n_kv, j1 = J1 - hi1 * n_kv;
+        if (!mbar_wait(v_full, J1 & 1, ctx, ERR_WAIT_FULL) ||
+            !mbar_wait(dp_empty, (J1 & 1) ^ 1, ctx, ERR_WAIT_TMEM_EMPTY))
+          return false;
+        tc_fence_after_sync();
+        att_mma_kk(tDP, smem_u32(sDO), smem_u32(sV), false);
+        tc_commit(dp_full);
+        tc_commit(v_empty);
+        if (j1 == n_kv - 1) tc_commit(q_empty);  // last use of this head's Q and dO
+        return true;
+      };
+      bool ok = total > 0 && issue_s(0) && issue_dp(0);
       for (int J = 0; ok && J < total; ++J) {
         const int hi = J / n_kv, j = J - hi * n_kv;
-        const int s = J & 1;
-        const uint32_t sK = smem_u32(sKV + s * 2 * ATT_TILE_BYTES);
-        if ((j == 0 && !mbar_wait(q_full, hi & 1, ctx, ERR_WAIT_FULL)) ||
-            !mbar_wait(&kv_full[s], (J >> 1) & 1, ctx, ERR_WAIT_FULL) ||
-            !mbar_wait(sdp_empty, (J & 1) ^ 1, ctx, ERR_WAIT_TMEM_EMPTY)) {
+        const int s = J % 3;
+        const uint32_t sK = smem_u32(sK3 + s * ATT_TILE_BYTES);
+        if (J + 1 < total && !issue_s(J + 1)) {
           ok = false;
           break;
         }
-        tc_fence_after_sync();
-        att_mma_kk(tS, smem_u32(sQ), sK, false);
-        att_mma_kk(tDP, smem_u32(sDO), sK + ATT_TILE_BYTES, false);
-        tc_commit(sdp_full);
-        if (j == n_kv - 1) tc_commit(q_empty);  // last use of this head's Q and dO
         if (!mbar_wait(ds_full, J & 1, ctx, ERR_WAIT_READY) ||
             (j == 0 && hi > 0 && !mbar_wait(dq_empty, (hi - 1) & 1, ctx, ERR_WAIT_TMEM_EMPTY))) {
           ok = false;
           break;
         }
+        if (J + 1 < total && !issue_dp(J + 1)) {
+          ok = false;
+          break;
+        }
         tc_fence_after_sync();
         att_mma_kmn(tDQ, smem_u32(sDS), sK, j > 0);
-        tc_commit(&kv_empty[s]);
+        tc_commit(&k_empty[s]);
         tc_commit(dq_done);
       }
     }
@@ -194,39 +240,52 @@ attn_dq_kernel(const AttnBwdParams p, const __grid_constant__ CUtensorMap tmQKV,
       const float dlt = row_valid ? p.delta[(long long)h * p.M_total + grow] : 0.f;
       for (int j = 0; j < n_kv; ++j) {
         const int J = hi * n_kv + j;
-        if (!__all_sync(0xffffffffu, mbar_wait(sdp_full, J & 1, ctx, ERR_WAIT_TMEM_FULL))) {
-          ok = false;
-          break;
-        }
-        // sDS is still being read by the previous tile's dQ product (for j == 0 the previous
-        // head's final store has already waited for it)
-        if (j > 0 && !__all_sync(0xffffffffu, mbar_wait(dq_done, (J - 1) & 1, ctx, ERR_WAIT_MISC))) {
+        const int sb = J & 1;
+        if (!__all_sync(0xffffffffu, mbar_wait(&s_full[sb], (J >> 1) & 1, ctx, ERR_WAIT_TMEM_FULL))) {
           ok = false;
           break;
         }
         tc_fence_after_sync();
         const bool diag = (j == n_kv - 1);
-#pragma unroll 1
+        // P of this thread's 64 columns from S alone, while the tensor pipe still produces dP
+        float pv[64];
+#pragma unroll
         for (int cc = 0; cc < 2; ++cc) {
-          uint32_t sv[32], dv[32];
-          tmem_ld_32x32b_x32(tS + lane_addr + c0 + cc * 32, sv);
+          uint32_t(&dst)[32] = *reinterpret_cast<uint32_t(*)[32]>(&pv[cc * 32]);
+          tmem_ld_32x32b_x32(tS[sb] + lane_addr + c0 + cc * 32, dst);
+        }
+        tmem_ld_wait();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&s_empty[sb]);
+#pragma unroll
+        for (int i = 0; i < 64; ++i) {
+          const float e = fast_exp2(pv[i] * p.scale_log2e - lse2);
+          pv[i] = (!row_valid || (diag && c0 + i > r)) ? 0.f : e * p.scale;
+        }
+        // sDS is still being read by the previous tile's dQ product (for j == 0 the previous
+        // head's final store has already waited for it)
+        if (!__all_sync(0xffffffffu, mbar_wait(dp_full, J & 1, ctx, ERR_WAIT_TMEM_FULL)) ||
+            (j > 0 && !__all_sync(0xffffffffu, mbar_wait(dq_done, (J - 1) & 1, ctx, ERR_WAIT_MISC)))) {
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+#pragma unroll
+        for (int cc = 0; cc < 2; ++cc) {
+          uint32_t dv[32];
           tmem_ld_32x32b_x32(tDP + lane_addr + c0 + cc * 32, dv);
           tmem_ld_wait();
           float ds[32];
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int col = c0 + cc * 32 + i;
-            float pv = fast_exp2(__uint_as_float(sv[i]) * p.scale_log2e - lse2);
-            if (!row_valid || (diag && col > r)) pv = 0.f;
-            ds[i] = pv * (__uint_as_float(dv[i]) - dlt) * p.scale;
-          }
+          for (int i = 0; i < 32; ++i) ds[i] = pv[cc * 32 + i] * (__uint_as_float(dv[i]) - dlt);
           att_store_row_chunk(sDS, r, c0 + cc * 32, ds);
         }
         tc_fence_before_sync();
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) {
-          mbar_arrive(sdp_empty);
+          mbar_arrive(dp_empty);
           mbar_arrive(ds_full);
         }
       }
