@@ -60,4 +60,86 @@ inline TpParams make_tp_params(const LfTpArgs* t) {
   return tp;
 }
 
+#ifdef __CUDACC__
+// GEMM -> reduce-scatter, consumer side: sum of all ranks' bf16 partials (+ residual) of one
+// ROWS x COLS item of the rows this rank owns, by the 128 threads of the reduce warps (`et` =
+// thread index among them).  The loads cross NVLink (2-3 us), so the bytes in flight per SM, not
+// the adds, set the pace: every thread keeps U output vectors of 16 bytes from W sources in flight
+// at once, and walks the sources W at a time (rank order, so the sum does not depend on U or W).
+template <int U, int W, int ROWS, int COLS>
+__device__ __forceinline__ void tp_reduce_item(const TpParams& tp, int et, int lt, int nt, int n_cols) {
+  constexpr int VEC_PER_ROW = COLS / 8;
+  constexpr int NV = ROWS * VEC_PER_ROW;
+  const long long grow0 = (long long)tp.rank * tp.tiles_per_shard * ROWS;  // first own row in every source's stage [M, N]
+  for (int v0 = et; v0 < NV; v0 += 128 * U) {
+    float acc[U][8];
+    int row[U], col[U];
+    bool live[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int v = v0 + u * 128;
+      row[u] = lt * ROWS + v / VEC_PER_ROW;
+      col[u] = nt * COLS + (v % VEC_PER_ROW) * 8;
+      live[u] = v < NV && col[u] < n_cols;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[u][j] = 0.f;
+    }
+    uint4 res[U];   // the residual travels with the first round of source loads
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+      if (live[u] && tp.rs_residual != nullptr)
+        res[u] = ld_global_v4(tp.rs_residual + (long long)row[u] * tp.rs_ldo + col[u]);
+    for (int s0 = 0; s0 < tp.world; s0 += W) {
+      uint4 raw[U][W];
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+#pragma unroll
+        for (int i = 0; i < W; ++i)
+          if (live[u] && s0 + i < tp.world)
+            raw[u][i] = ld_global_v4(tp.rs_peer_stage[s0 + i] + (grow0 + row[u]) * n_cols + col[u]);
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+#pragma unroll
+        for (int i = 0; i < W; ++i)
+          if (live[u] && s0 + i < tp.world) {
+            const uint32_t w[4] = {raw[u][i].x, raw[u][i].y, raw[u][i].z, raw[u][i].w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float2 f = unpack_bf16x2(w[j]);
+              acc[u][2 * j] += f.x;
+              acc[u][2 * j + 1] += f.y;
+            }
+          }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (!live[u]) continue;
+      const long long off = (long long)row[u] * tp.rs_ldo + col[u];
+      if (tp.rs_residual != nullptr) {
+        const uint32_t w[4] = {res[u].x, res[u].y, res[u].z, res[u].w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = unpack_bf16x2(w[j]);
+          acc[u][2 * j] += f.x;
+          acc[u][2 * j + 1] += f.y;
+        }
+      }
+      st_global_v4(tp.rs_out + off, pack_bf16x2(acc[u][0], acc[u][1]), pack_bf16x2(acc[u][2], acc[u][3]),
+                   pack_bf16x2(acc[u][4], acc[u][5]), pack_bf16x2(acc[u][6], acc[u][7]));
+    }
+  }
+}
+
+// Depth by world size: two ranks -> four vectors from both sources at once; more ranks -> two
+// vectors from four sources per round.
+// DEEP = false for kernels with a tight register budget (the NF4-expanding variants).
+template <int ROWS, int COLS, bool DEEP = true>
+__device__ __forceinline__ void tp_reduce_item_any(const TpParams& tp, int et, int lt, int nt, int n_cols) {
+  if (DEEP && tp.world <= 2)
+    tp_reduce_item<4, 2, ROWS, COLS>(tp, et, lt, nt, n_cols);
+  else
+    tp_reduce_item<2, 4, ROWS, COLS>(tp, et, lt, nt, n_cols);
+}
+#endif  // __CUDACC__
+
 }  // namespace lf

@@ -498,12 +498,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS + (TP !
     // ---- reduce the partials of the rows this rank owns, as they arrive ----
     // Four dedicated warps, concurrent with the GEMM of the other warps: they poll the
     // per-(source, row tile, column tile) flags and sum the bf16 partials in fp32 (+ residual).
-    // Every thread keeps the loads of two output vectors from all sources in flight.
+    // Every thread keeps the loads of several output vectors from all sources in flight (tp_reduce_item).
     const int et = threadIdx.x - PAIR_THREADS;  // 0..127
-    const int ms = tp.tiles_per_shard * BM;
     const int items = tp.tiles_per_shard * p.num_n_tiles;
-    constexpr int VEC_PER_ROW = BN / 8;
-    constexpr int NV = BM * VEC_PER_ROW;
     bool ok = true;
     for (int item = blockIdx.x; ok && item < items; item += gridDim.x) {
       const int lt = item / p.num_n_tiles, nt = item - lt * p.num_n_tiles;
@@ -514,57 +511,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS + (TP !
       // one agreed answer for the 128 reduce threads (see named_bar_and)
       ok = named_bar_and<2, 128>(ok && !aborted(ctx));
       if (!ok) break;
-      // row of this item inside every source's stage [M, N]
-      const long long grow0 = (long long)tp.rank * ms;
-      for (int v0 = et; v0 < NV; v0 += 256) {
-        uint4 raw[2][8];
-        uint4 res[2];
-        long long out_off[2];
-        bool live[2];
-#pragma unroll
-        for (int u = 0; u < 2; ++u) {
-          const int v = v0 + u * 128;
-          const int lr = lt * BM + v / VEC_PER_ROW;
-          const int col = nt * BN + (v % VEC_PER_ROW) * 8;
-          live[u] = v < NV && col < p.N;
-          out_off[u] = (long long)lr * tp.rs_ldo + col;
-#pragma unroll
-          for (int src = 0; src < 8; ++src)
-            if (live[u] && src < tp.world)
-              raw[u][src] = ld_global_v4(tp.rs_peer_stage[src] + (grow0 + lr) * p.N + col);
-          if (live[u] && tp.rs_residual != nullptr) res[u] = ld_global_v4(tp.rs_residual + out_off[u]);
-        }
-#pragma unroll
-        for (int u = 0; u < 2; ++u) {
-          if (!live[u]) continue;
-          float acc[8];
-#pragma unroll
-          for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-#pragma unroll
-          for (int src = 0; src < 8; ++src) {
-            if (src < tp.world) {
-              const uint32_t w[4] = {raw[u][src].x, raw[u][src].y, raw[u][src].z, raw[u][src].w};
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                const float2 f = unpack_bf16x2(w[j]);
-                acc[2 * j] += f.x;
-                acc[2 * j + 1] += f.y;
-              }
-            }
-          }
-          if (tp.rs_residual != nullptr) {
-            const uint32_t w[4] = {res[u].x, res[u].y, res[u].z, res[u].w};
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const float2 f = unpack_bf16x2(w[j]);
-              acc[2 * j] += f.x;
-              acc[2 * j + 1] += f.y;
-            }
-          }
-          st_global_v4(tp.rs_out + out_off[u], pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]),
-                       pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7]));
-        }
-      }
+      tp_reduce_item_any<BM, BN>(tp, et, lt, nt, p.N);
     }
   } else if (TP == 1) {
     // ------------- push this rank's token shard to every peer's gathered buffer -------------
