@@ -98,11 +98,6 @@ class LayerSaved:
     full: Optional[dict] = None
 
 
-def _pinned_bytes(nbytes: int) -> int:
-    """The pinned-memory allocator hands out power-of-two blocks."""
-    return 1 << max(0, int(nbytes - 1).bit_length())
-
-
 class DecoderStage:
     """Layers ``[layer_start, layer_end)`` of a decoder, on one GPU."""
 
@@ -348,12 +343,12 @@ class DecoderStage:
             n_full = int(min(n_part, (budget - n_part * per_part) // per_gu))
             modes = [False] * (n - n_part) + ["nogu"] * (n_part - n_full) + ["cheap"] * n_full
             if offload:
-                from .offload import default_host_budget_bytes
+                from .offload import default_host_budget_bytes, host_slot_bytes
 
                 if self.offload_host_budget is None:  # fixed at the first plan: pinning shrinks MemAvailable
                     self.offload_host_budget = default_host_budget_bytes()
                 cand = [li for li in range(n) if modes[li] == "nogu"]
-                slots = int(self.offload_host_budget // _pinned_bytes(per_gu))
+                slots = int(self.offload_host_budget // host_slot_bytes(per_gu))
                 # without a measured link rate: two layers out of three (a forward pass
                 # produces gate|up about 1.5x faster than one PCIe 5 link drains it)
                 cap = self.offload_max_layers if self.offload_max_layers is not None else (2 * n + 2) // 3
@@ -404,6 +399,8 @@ class DecoderStage:
     def disable_offload(self) -> None:
         """Drop the offloader and give its pinned host buffers back to the operating system
         (the pinned-memory allocator would otherwise keep them cached)."""
+        if self._offloader is not None:
+            self._offloader.close()
         self._offloader = None
         self.set_offload(False)
         release = getattr(torch._C, "_host_emptyCache", None)
