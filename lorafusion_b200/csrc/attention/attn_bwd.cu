@@ -347,13 +347,18 @@ attn_dkdv_kernel(const AttnBwdParams p, const __grid_constant__ CUtensorMap tmQK
   uint64_t* kv_full = bars;
   uint64_t* qd_full = bars + 1;
   uint64_t* qd_empty = bars + 3;
-  uint64_t* sdp_full = bars + 5;
-  uint64_t* sdp_empty = bars + 6;
+  // S and dP have barriers of their own (one TMEM buffer each): S of the next iteration is issued
+  // as soon as P of this one has been formed, so the element-wise warps turn it into P while the
+  // tensor pipe runs dK of this iteration and dP of the next.
+  uint64_t* s_full = bars + 5;
+  uint64_t* s_empty = bars + 6;
   uint64_t* p_full = bars + 7;
   uint64_t* dv_done = bars + 8;
   uint64_t* ds_full = bars + 9;
   uint64_t* dk_done = bars + 10;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
+  uint64_t* dp_full = bars + 11;
+  uint64_t* dp_empty = bars + 12;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -373,8 +378,10 @@ attn_dkdv_kernel(const AttnBwdParams p, const __grid_constant__ CUtensorMap tmQK
       mbar_init(&qd_full[i], 1);
       mbar_init(&qd_empty[i], 1);
     }
-    mbar_init(sdp_full, 1);
-    mbar_init(sdp_empty, 8);  // one arrival per softmax warp
+    mbar_init(s_full, 1);
+    mbar_init(s_empty, 8);  // one arrival per element-wise warp
+    mbar_init(dp_full, 1);
+    mbar_init(dp_empty, 8);
     mbar_init(p_full, 8);
     mbar_init(dv_done, 1);
     mbar_init(ds_full, 8);
@@ -410,20 +417,30 @@ attn_dkdv_kernel(const AttnBwdParams p, const __grid_constant__ CUtensorMap tmQK
     }
   } else if (warp == 1) {
     if (lane == 0) {
+      // Issue order per iteration: [P ready] dV(it), S(it + 1), [dS ready] dK(it), dP(it + 1).
+      auto issue_s = [&](int i1) -> bool {   // S = Q K^T of iteration i1 (its Q / dO stage must have landed)
+        const int s1 = i1 & 1;
+        if (!mbar_wait(&qd_full[s1], (i1 >> 1) & 1, ctx, ERR_WAIT_FULL) ||
+            !mbar_wait(s_empty, (i1 & 1) ^ 1, ctx, ERR_WAIT_TMEM_EMPTY))
+          return false;
+        tc_fence_after_sync();
+        att_mma_kk(tS, smem_u32(sQD + s1 * 2 * ATT_TILE_BYTES), smem_u32(sK), false);
+        tc_commit(s_full);
+        return true;
+      };
+      auto issue_dp = [&](int i1) -> bool {  // dP = dO V^T of iteration i1 (stage awaited by issue_s(i1))
+        if (!mbar_wait(dp_empty, (i1 & 1) ^ 1, ctx, ERR_WAIT_TMEM_EMPTY)) return false;
+        tc_fence_after_sync();
+        att_mma_kk(tDP, smem_u32(sQD + (i1 & 1) * 2 * ATT_TILE_BYTES + ATT_TILE_BYTES), smem_u32(sV), false);
+        tc_commit(dp_full);
+        return true;
+      };
       bool ok = mbar_wait(kv_full, 0, ctx, ERR_WAIT_FULL);
+      ok = ok && n_it > 0 && issue_s(0) && issue_dp(0);
       for (int it = 0; ok && it < n_it; ++it) {
         const int s = it & 1;
         const uint32_t sQ = smem_u32(sQD + s * 2 * ATT_TILE_BYTES);
         const uint32_t sDO = sQ + ATT_TILE_BYTES;
-        if (!mbar_wait(&qd_full[s], (it >> 1) & 1, ctx, ERR_WAIT_FULL) ||
-            !mbar_wait(sdp_empty, (it & 1) ^ 1, ctx, ERR_WAIT_TMEM_EMPTY)) {
-          ok = false;
-          break;
-        }
-        tc_fence_after_sync();
-        att_mma_kk(tS, sQ, smem_u32(sK), false);
-        att_mma_kk(tDP, sDO, smem_u32(sV), false);
-        tc_commit(sdp_full);
         if (!mbar_wait(p_full, it & 1, ctx, ERR_WAIT_READY)) {
           ok = false;
           break;
@@ -431,6 +448,10 @@ attn_dkdv_kernel(const AttnBwdParams p, const __grid_constant__ CUtensorMap tmQK
         tc_fence_after_sync();
         att_mma_mnmn(tDV, smem_u32(sPD), sDO, it > 0);
         tc_commit(dv_done);
+        if (it + 1 < n_it && !issue_s(it + 1)) {
+          ok = false;
+          break;
+        }
         if (!mbar_wait(ds_full, it & 1, ctx, ERR_WAIT_READY)) {
           ok = false;
           break;
@@ -439,6 +460,10 @@ attn_dkdv_kernel(const AttnBwdParams p, const __grid_constant__ CUtensorMap tmQK
         att_mma_mnmn(tDK, smem_u32(sPD), sQ, it > 0);
         tc_commit(&qd_empty[s]);
         tc_commit(dk_done);
+        if (it + 1 < n_it && !issue_dp(it + 1)) {
+          ok = false;
+          break;
+        }
       }
     }
   } else {
@@ -458,10 +483,11 @@ attn_dkdv_kernel(const AttnBwdParams p, const __grid_constant__ CUtensorMap tmQK
       const long long grow = (long long)qrow0 + r;
       const float lse2 = row_valid ? p.lse[(long long)h * p.M_total + grow] * 1.4426950408889634f : 0.f;
       const float dlt = row_valid ? p.delta[(long long)h * p.M_total + grow] : 0.f;
-      if (!__all_sync(0xffffffffu, mbar_wait(sdp_full, it & 1, ctx, ERR_WAIT_TMEM_FULL))) {
+      if (!__all_sync(0xffffffffu, mbar_wait(s_full, it & 1, ctx, ERR_WAIT_TMEM_FULL))) {
         ok = false;
         break;
       }
+      // sPD still holds dS of the previous iteration until its dK product has read it
       if (it > 0 && !__all_sync(0xffffffffu, mbar_wait(dk_done, (it - 1) & 1, ctx, ERR_WAIT_MISC))) {
         ok = false;
         break;
@@ -485,35 +511,47 @@ attn_dkdv_kernel(const AttnBwdParams p, const __grid_constant__ CUtensorMap tmQK
         for (int i = 0; i < 16; ++i) pk[cc * 16 + i] = pack_bf16x2(pv[2 * i], pv[2 * i + 1]);
         att_store_row_chunk(sPD, r, c0 + cc * 32, pv);
       }
+      tc_fence_before_sync();
       fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0) mbar_arrive(p_full);
-      if (!__all_sync(0xffffffffu, mbar_wait(dv_done, it & 1, ctx, ERR_WAIT_MISC))) {
+      if (lane == 0) {
+        mbar_arrive(s_empty);   // S has been read: the next iteration's S may be issued
+        mbar_arrive(p_full);
+      }
+      // dS of this thread's 64 columns in registers while the dV product still reads P from sPD
+      if (!__all_sync(0xffffffffu, mbar_wait(dp_full, it & 1, ctx, ERR_WAIT_TMEM_FULL))) {
         ok = false;
         break;
       }
       tc_fence_after_sync();
+      float ds[64];
 #pragma unroll
       for (int cc = 0; cc < 2; ++cc) {
         uint32_t dv[32];
         tmem_ld_32x32b_x32(tDP + lane_addr + c0 + cc * 32, dv);
         tmem_ld_wait();
-        float ds[32];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
           const float2 pp = unpack_bf16x2(pk[cc * 16 + i]);
-          ds[2 * i] = pp.x * (__uint_as_float(dv[2 * i]) - dlt) * p.scale;
-          ds[2 * i + 1] = pp.y * (__uint_as_float(dv[2 * i + 1]) - dlt) * p.scale;
+          ds[cc * 32 + 2 * i] = pp.x * (__uint_as_float(dv[2 * i]) - dlt) * p.scale;
+          ds[cc * 32 + 2 * i + 1] = pp.y * (__uint_as_float(dv[2 * i + 1]) - dlt) * p.scale;
         }
-        att_store_row_chunk(sPD, r, c0 + cc * 32, ds);
       }
       tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(dp_empty);
+      if (!__all_sync(0xffffffffu, mbar_wait(dv_done, it & 1, ctx, ERR_WAIT_MISC))) {
+        ok = false;
+        break;
+      }
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc) {
+        float(&src)[32] = *reinterpret_cast<float(*)[32]>(&ds[cc * 32]);
+        att_store_row_chunk(sPD, r, c0 + cc * 32, src);
+      }
       fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(sdp_empty);
-        mbar_arrive(ds_full);
-      }
+      if (lane == 0) mbar_arrive(ds_full);
     }
     if (ok && n_it > 0 && __all_sync(0xffffffffu, mbar_wait(dk_done, (n_it - 1) & 1, ctx, ERR_WAIT_MISC))) {
       tc_fence_after_sync();
