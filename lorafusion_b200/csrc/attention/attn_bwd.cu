@@ -176,7 +176,8 @@ attn_dq_kernel(const AttnBwdParams p, const __grid_constant__ CUtensorMap tmQKV,
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      // Issue order: S(0), dP(0), then per tile J: S(J + 1) early, [dS(J) ready] dP(J + 1), dQ(J).
+      // Issue order: S(0), dP(0), then per tile J: S(J + 1), dP(J + 1) (both as soon as their TMEM
+      // buffers have been read), [dS(J) ready] dQ(J).
       auto issue_s = [&](int J1) -> bool {   // S of tile J1 into its buffer; K (and for a new head Q) must have landed
         const int hi1 = J1 / n_kv, j1 = J1 - hi1 * n_kv;
         const int b1 = J1 & 1;
@@ -207,16 +208,12 @@ attn_dq_kernel(const AttnBwdParams p, const __grid_constant__ CUtensorMap tmQKV,
         const int hi = J / n_kv, j = J - hi * n_kv;
         const int s = J % 3;
         const uint32_t sK = smem_u32(sK3 + s * ATT_TILE_BYTES);
-        if (J + 1 < total && !issue_s(J + 1)) {
+        if (J + 1 < total && !(issue_s(J + 1) && issue_dp(J + 1))) {
           ok = false;
           break;
         }
         if (!mbar_wait(ds_full, J & 1, ctx, ERR_WAIT_READY) ||
             (j == 0 && hi > 0 && !mbar_wait(dq_empty, (hi - 1) & 1, ctx, ERR_WAIT_TMEM_EMPTY))) {
-          ok = false;
-          break;
-        }
-        if (J + 1 < total && !issue_dp(J + 1)) {
           ok = false;
           break;
         }
@@ -263,31 +260,36 @@ attn_dq_kernel(const AttnBwdParams p, const __grid_constant__ CUtensorMap tmQKV,
           const float e = fast_exp2(pv[i] * p.scale_log2e - lse2);
           pv[i] = (!row_valid || (diag && c0 + i > r)) ? 0.f : e * p.scale;
         }
-        // sDS is still being read by the previous tile's dQ product (for j == 0 the previous
-        // head's final store has already waited for it)
-        if (!__all_sync(0xffffffffu, mbar_wait(dp_full, J & 1, ctx, ERR_WAIT_TMEM_FULL)) ||
-            (j > 0 && !__all_sync(0xffffffffu, mbar_wait(dq_done, (J - 1) & 1, ctx, ERR_WAIT_MISC)))) {
+        if (!__all_sync(0xffffffffu, mbar_wait(dp_full, J & 1, ctx, ERR_WAIT_TMEM_FULL))) {
           ok = false;
           break;
         }
         tc_fence_after_sync();
 #pragma unroll
-        for (int cc = 0; cc < 2; ++cc) {
+        for (int cc = 0; cc < 2; ++cc) {   // dS in registers (over P); dP's buffer is free right after
           uint32_t dv[32];
           tmem_ld_32x32b_x32(tDP + lane_addr + c0 + cc * 32, dv);
           tmem_ld_wait();
-          float ds[32];
 #pragma unroll
-          for (int i = 0; i < 32; ++i) ds[i] = pv[cc * 32 + i] * (__uint_as_float(dv[i]) - dlt);
-          att_store_row_chunk(sDS, r, c0 + cc * 32, ds);
+          for (int i = 0; i < 32; ++i) pv[cc * 32 + i] *= __uint_as_float(dv[i]) - dlt;
         }
         tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(dp_empty);
+        // sDS is still being read by the previous tile's dQ product (for j == 0 the previous
+        // head's final store has already waited for it)
+        if (j > 0 && !__all_sync(0xffffffffu, mbar_wait(dq_done, (J - 1) & 1, ctx, ERR_WAIT_MISC))) {
+          ok = false;
+          break;
+        }
+#pragma unroll
+        for (int cc = 0; cc < 2; ++cc) {
+          float(&src)[32] = *reinterpret_cast<float(*)[32]>(&pv[cc * 32]);
+          att_store_row_chunk(sDS, r, c0 + cc * 32, src);
+        }
         fence_proxy_async_smem();
         __syncwarp();
-        if (lane == 0) {
-          mbar_arrive(dp_empty);
-          mbar_arrive(ds_full);
-        }
+        if (lane == 0) mbar_arrive(ds_full);
       }
       if (!ok) break;
       if (!__all_sync(0xffffffffu, mbar_wait(dq_done, (hi * n_kv + n_kv - 1) & 1, ctx, ERR_WAIT_MISC))) {
@@ -417,7 +419,7 @@ attn_dkdv_kernel(const AttnBwdParams p, const __grid_constant__ CUtensorMap tmQK
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      // Issue order per iteration: [P ready] dV(it), S(it + 1), [dS ready] dK(it), dP(it + 1).
+      // Issue order per iteration: [P ready] dV(it), S(it + 1), dP(it + 1), [dS ready] dK(it).
       auto issue_s = [&](int i1) -> bool {   // S = Q K^T of iteration i1 (its Q / dO stage must have landed)
         const int s1 = i1 & 1;
         if (!mbar_wait(&qd_full[s1], (i1 >> 1) & 1, ctx, ERR_WAIT_FULL) ||
@@ -448,7 +450,7 @@ attn_dkdv_kernel(const AttnBwdParams p, const __grid_constant__ CUtensorMap tmQK
         tc_fence_after_sync();
         att_mma_mnmn(tDV, smem_u32(sPD), sDO, it > 0);
         tc_commit(dv_done);
-        if (it + 1 < n_it && !issue_s(it + 1)) {
+        if (it + 1 < n_it && !(issue_s(it + 1) && issue_dp(it + 1))) {
           ok = false;
           break;
         }
@@ -460,10 +462,6 @@ attn_dkdv_kernel(const AttnBwdParams p, const __grid_constant__ CUtensorMap tmQK
         att_mma_mnmn(tDK, smem_u32(sPD), sQ, it > 0);
         tc_commit(&qd_empty[s]);
         tc_commit(dk_done);
-        if (it + 1 < n_it && !issue_dp(it + 1)) {
-          ok = false;
-          break;
-        }
       }
     }
   } else {
@@ -487,37 +485,39 @@ attn_dkdv_kernel(const AttnBwdParams p, const __grid_constant__ CUtensorMap tmQK
         ok = false;
         break;
       }
+      tc_fence_after_sync();
+      // P of this thread's 64 columns in registers first; its store waits for the shared P / dS buffer
+      float pv[64];
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc) {
+        uint32_t(&dst)[32] = *reinterpret_cast<uint32_t(*)[32]>(&pv[cc * 32]);
+        tmem_ld_32x32b_x32(tS + lane_addr + c0 + cc * 32, dst);
+      }
+      tmem_ld_wait();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(s_empty);   // S has been read: the next iteration's S may be issued
+#pragma unroll
+      for (int i = 0; i < 64; ++i) {
+        const float x = fast_exp2(pv[i] * p.scale_log2e - lse2);
+        pv[i] = (!row_valid || (diag && c0 + i > r)) ? 0.f : x;
+      }
+      uint32_t pk[32];  // the same P as packed bf16 pairs (what the dV product sees), kept for dS
+#pragma unroll
+      for (int i = 0; i < 32; ++i) pk[i] = pack_bf16x2(pv[2 * i], pv[2 * i + 1]);
       // sPD still holds dS of the previous iteration until its dK product has read it
       if (it > 0 && !__all_sync(0xffffffffu, mbar_wait(dk_done, (it - 1) & 1, ctx, ERR_WAIT_MISC))) {
         ok = false;
         break;
       }
-      tc_fence_after_sync();
-      uint32_t pk[32];  // P of this thread's 64 columns as packed bf16 pairs
 #pragma unroll
       for (int cc = 0; cc < 2; ++cc) {
-        uint32_t sv[32];
-        tmem_ld_32x32b_x32(tS + lane_addr + c0 + cc * 32, sv);
-        tmem_ld_wait();
-        float pv[32];
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int col = c0 + cc * 32 + i;
-          float x = fast_exp2(__uint_as_float(sv[i]) * p.scale_log2e - lse2);
-          if (!row_valid || (diag && col > r)) x = 0.f;
-          pv[i] = x;
-        }
-#pragma unroll
-        for (int i = 0; i < 16; ++i) pk[cc * 16 + i] = pack_bf16x2(pv[2 * i], pv[2 * i + 1]);
-        att_store_row_chunk(sPD, r, c0 + cc * 32, pv);
+        float(&src)[32] = *reinterpret_cast<float(*)[32]>(&pv[cc * 32]);
+        att_store_row_chunk(sPD, r, c0 + cc * 32, src);
       }
-      tc_fence_before_sync();
       fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(s_empty);   // S has been read: the next iteration's S may be issued
-        mbar_arrive(p_full);
-      }
+      if (lane == 0) mbar_arrive(p_full);
       // dS of this thread's 64 columns in registers while the dV product still reads P from sPD
       if (!__all_sync(0xffffffffu, mbar_wait(dp_full, it & 1, ctx, ERR_WAIT_TMEM_FULL))) {
         ok = false;
