@@ -136,3 +136,16 @@ def test_packed_dummy_inputs_and_verbose_allclose():
     assert verbose_allclose(torch.ones(4), torch.ones(4), print_fn=said.append) and not said
     assert not verbose_allclose(torch.ones(4), torch.tensor([1.0, 1.0, 2.0, 1.0]), msg="x", print_fn=said.append)
     assert "1/4 mismatched" in said[0]
+
+
+def test_offload_slots_are_sized_exactly():
+    """A host slot takes its size rounded to pages, not to a power of two: the 1.75 GiB gate|up
+    output of a 16K-token 70B microbatch fits 49 times into 92 GB, not 43 times."""
+    from lorafusion_b200.models.offload import host_slot_bytes
+
+    per_gu = 16384 * 2 * 28672 * 2
+    assert host_slot_bytes(per_gu) == per_gu            # already a multiple of 4096
+    assert host_slot_bytes(per_gu + 1) == per_gu + 4096
+    budget = int(0.45 * 205.8e9)
+    assert budget // host_slot_bytes(per_gu) == 49
+    assert budget // (1 << (per_gu - 1).bit_length()) == 43
