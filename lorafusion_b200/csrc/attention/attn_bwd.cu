@@ -234,7 +234,7 @@ attn_dq_kernel(const AttnBwdParams p, const __grid_constant__ CUtensorMap tmQKV,
     for (int hi = 0; ok && hi < group; ++hi) {
       const int h = h0 + hi;
       const float lse2 = row_valid ? p.lse[(long long)h * p.M_total + grow] * 1.4426950408889634f : 0.f;
-      const float dlt = row_valid ? p.delta[(long long)h * p.M_total + grow] : 0.f;
+      const float dlts = row_valid ? p.delta[(long long)h * p.M_total + grow] * p.scale : 0.f;  // delta * softmax scale
       for (int j = 0; j < n_kv; ++j) {
         const int J = hi * n_kv + j;
         const int sb = J & 1;
@@ -256,9 +256,11 @@ attn_dq_kernel(const AttnBwdParams p, const __grid_constant__ CUtensorMap tmQKV,
         __syncwarp();
         if (lane == 0) mbar_arrive(&s_empty[sb]);
 #pragma unroll
-        for (int i = 0; i < 64; ++i) {
-          const float e = fast_exp2(pv[i] * p.scale_log2e - lse2);
-          pv[i] = (!row_valid || (diag && c0 + i > r)) ? 0.f : e * p.scale;
+        for (int i = 0; i < 64; ++i) pv[i] = fast_exp2(pv[i] * p.scale_log2e - lse2);
+        if (diag || rows < ATT_TILE) {   // uniform: only the diagonal tile and a ragged query tile mask anything
+#pragma unroll
+          for (int i = 0; i < 64; ++i)
+            if (!row_valid || (diag && c0 + i > r)) pv[i] = 0.f;
         }
         if (!__all_sync(0xffffffffu, mbar_wait(dp_full, J & 1, ctx, ERR_WAIT_TMEM_FULL))) {
           ok = false;
@@ -271,7 +273,7 @@ attn_dq_kernel(const AttnBwdParams p, const __grid_constant__ CUtensorMap tmQKV,
           tmem_ld_32x32b_x32(tDP + lane_addr + c0 + cc * 32, dv);
           tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) pv[cc * 32 + i] *= __uint_as_float(dv[i]) - dlt;
+          for (int i = 0; i < 32; ++i) pv[cc * 32 + i] *= fmaf(__uint_as_float(dv[i]), p.scale, -dlts);
         }
         tc_fence_before_sync();
         __syncwarp();
@@ -471,16 +473,26 @@ attn_dkdv_kernel(const AttnBwdParams p, const __grid_constant__ CUtensorMap tmQK
     const int r = q * 32 + lane;  // query row inside the current query tile
     const uint32_t lane_addr = uint32_t(q * 32) << 16;
     bool ok = true;
+    // log-sum-exp and delta of this thread's query row: loaded one iteration ahead, so that the
+    // two global loads are not on the critical path of every iteration
+    auto row_stats = [&](int i1, float& lse2_out, float& dlt_out) {
+      const int h1 = g * group + i1 / per_head;
+      const int jq1 = i_kv + i1 % per_head;
+      const bool valid1 = r < min(ATT_TILE, seq_rows - jq1 * ATT_TILE);
+      const long long grow1 = (long long)seq_row0 + jq1 * ATT_TILE + r;
+      lse2_out = valid1 ? p.lse[(long long)h1 * p.M_total + grow1] * 1.4426950408889634f : 0.f;
+      dlt_out = valid1 ? p.delta[(long long)h1 * p.M_total + grow1] * p.scale : 0.f;
+    };
+    float lse2_next = 0.f, dlts_next = 0.f;
+    if (n_it > 0) row_stats(0, lse2_next, dlts_next);
     for (int it = 0; it < n_it; ++it) {
-      const int h = g * group + it / per_head;
       const int jq = i_kv + it % per_head;
-      const int qrow0 = seq_row0 + jq * ATT_TILE;
       const int q_valid = min(ATT_TILE, seq_rows - jq * ATT_TILE);
       const bool row_valid = r < q_valid;
       const bool diag = (jq == i_kv);
-      const long long grow = (long long)qrow0 + r;
-      const float lse2 = row_valid ? p.lse[(long long)h * p.M_total + grow] * 1.4426950408889634f : 0.f;
-      const float dlt = row_valid ? p.delta[(long long)h * p.M_total + grow] : 0.f;
+      const bool need_mask = diag || q_valid < ATT_TILE;   // uniform over the CTA
+      const float lse2 = lse2_next, dlts = dlts_next;       // dlts = delta * softmax scale
+      if (it + 1 < n_it) row_stats(it + 1, lse2_next, dlts_next);
       if (!__all_sync(0xffffffffu, mbar_wait(s_full, it & 1, ctx, ERR_WAIT_TMEM_FULL))) {
         ok = false;
         break;
@@ -498,13 +510,12 @@ attn_dkdv_kernel(const AttnBwdParams p, const __grid_constant__ CUtensorMap tmQK
       __syncwarp();
       if (lane == 0) mbar_arrive(s_empty);   // S has been read: the next iteration's S may be issued
 #pragma unroll
-      for (int i = 0; i < 64; ++i) {
-        const float x = fast_exp2(pv[i] * p.scale_log2e - lse2);
-        pv[i] = (!row_valid || (diag && c0 + i > r)) ? 0.f : x;
-      }
-      uint32_t pk[32];  // the same P as packed bf16 pairs (what the dV product sees), kept for dS
+      for (int i = 0; i < 64; ++i) pv[i] = fast_exp2(pv[i] * p.scale_log2e - lse2);
+      if (need_mask) {   // only the diagonal tile and a ragged last query tile have anything to mask
 #pragma unroll
-      for (int i = 0; i < 32; ++i) pk[i] = pack_bf16x2(pv[2 * i], pv[2 * i + 1]);
+        for (int i = 0; i < 64; ++i)
+          if (!row_valid || (diag && c0 + i > r)) pv[i] = 0.f;
+      }
       // sPD still holds dS of the previous iteration until its dK product has read it
       if (it > 0 && !__all_sync(0xffffffffu, mbar_wait(dk_done, (it - 1) & 1, ctx, ERR_WAIT_MISC))) {
         ok = false;
@@ -524,18 +535,14 @@ attn_dkdv_kernel(const AttnBwdParams p, const __grid_constant__ CUtensorMap tmQK
         break;
       }
       tc_fence_after_sync();
-      float ds[64];
+      // dS = P (.) (dP - delta) * scale, in place over P (fp32; the dV product saw the same P rounded to bf16)
 #pragma unroll
       for (int cc = 0; cc < 2; ++cc) {
         uint32_t dv[32];
         tmem_ld_32x32b_x32(tDP + lane_addr + c0 + cc * 32, dv);
         tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const float2 pp = unpack_bf16x2(pk[cc * 16 + i]);
-          ds[cc * 32 + 2 * i] = pp.x * (__uint_as_float(dv[2 * i]) - dlt) * p.scale;
-          ds[cc * 32 + 2 * i + 1] = pp.y * (__uint_as_float(dv[2 * i + 1]) - dlt) * p.scale;
-        }
+        for (int i = 0; i < 32; ++i) pv[cc * 32 + i] *= fmaf(__uint_as_float(dv[i]), p.scale, -dlts);
       }
       tc_fence_before_sync();
       __syncwarp();
@@ -546,7 +553,7 @@ attn_dkdv_kernel(const AttnBwdParams p, const __grid_constant__ CUtensorMap tmQK
       }
 #pragma unroll
       for (int cc = 0; cc < 2; ++cc) {
-        float(&src)[32] = *reinterpret_cast<float(*)[32]>(&ds[cc * 32]);
+        float(&src)[32] = *reinterpret_cast<float(*)[32]>(&pv[cc * 32]);
         att_store_row_chunk(sPD, r, c0 + cc * 32, src);
       }
       fence_proxy_async_smem();
