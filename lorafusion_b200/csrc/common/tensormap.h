@@ -31,6 +31,22 @@ inline EncodeTiledFn get_encode_tiled() {
   return fn;
 }
 
+// The encoder is a driver call and wants a context current in the calling thread.  A thread that
+// has made no runtime call yet has none: PyTorch's autograd worker threads are the case that
+// matters (a custom Function's backward whose first CUDA call is this encoder; seen as
+// CUDA_ERROR_INVALID_CONTEXT when an attention backward was the first backward of a process).
+// Binds the primary context of the device that owns `base`.
+inline void bind_context_of(const void* base) {
+  cudaPointerAttributes attr;
+  int dev = -1;
+  if (cudaPointerGetAttributes(&attr, base) == cudaSuccess && attr.type == cudaMemoryTypeDevice)
+    dev = attr.device;
+  else
+    cudaGetLastError();
+  if (dev >= 0) cudaSetDevice(dev);
+  cudaFree(nullptr);
+}
+
 // 2-D row-major tensor [rows, cols] (cols contiguous, row pitch ld elements) of 2-byte
 // elements, box [box_rows, box_cols], 128-byte swizzle (box_cols * 2 must be 128) or none.
 // Out-of-range elements read as zero.  Returns 0 on success.
@@ -44,10 +60,19 @@ inline int make_tmap_2d_b16(CUtensorMap* out, const void* base, uint64_t rows, u
   cuuint64_t strides[1] = {ld_elems * 2};
   cuuint32_t box[2] = {box_cols, box_rows};
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims,
-                   strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                   swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
-                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  CUresult r = CUDA_SUCCESS;
+  for (int attempt = 0; attempt < 2; ++attempt) {
+    r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_ERROR_INVALID_CONTEXT && r != CUDA_ERROR_NOT_INITIALIZED) break;
+    bind_context_of(base);   // no context in this thread yet: bind one and encode again
+  }
+  if (r != CUDA_SUCCESS)
+    fprintf(stderr,
+            "lorafusion_b200: cuTensorMapEncodeTiled failed (%d): base %p, [%llu x %llu], pitch %llu B, box [%u x %u]\n",
+            int(r), base, (unsigned long long)rows, (unsigned long long)cols, (unsigned long long)(ld_elems * 2),
+            box_rows, box_cols);
   return r == CUDA_SUCCESS ? 0 : -3;
 }
 
@@ -61,9 +86,14 @@ inline int make_tmap_2d_u8(CUtensorMap* out, const void* base, uint64_t rows, ui
   cuuint64_t strides[1] = {ld_bytes};
   cuuint32_t box[2] = {box_cols, box_rows};
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides,
-                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
-                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  CUresult r = CUDA_SUCCESS;
+  for (int attempt = 0; attempt < 2; ++attempt) {
+    r = enc(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_ERROR_INVALID_CONTEXT && r != CUDA_ERROR_NOT_INITIALIZED) break;
+    bind_context_of(base);
+  }
   return r == CUDA_SUCCESS ? 0 : -3;
 }
 

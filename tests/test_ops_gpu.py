@@ -176,7 +176,12 @@ def _attn_case(lens, Hq, Hkv, seed):
 
 
 @pytest.mark.parametrize("lens,Hq,Hkv", [([128], 1, 1), ([256, 128], 2, 1), ([100, 37, 300, 129], 4, 2),
-                                         ([1000, 24], 8, 1)])
+                                         ([1000, 24], 8, 1),
+                                         # one query head per KV head and five key tiles: the three-stage K
+                                         # ring and the two S buffers of dQ wrap around inside ONE head
+                                         ([640], 2, 2),
+                                         # five query heads per KV head (the 32B grouping), ragged lengths
+                                         ([700, 513, 65], 10, 2)])
 def test_attention_fwd_bwd(lens, Hq, Hkv):
     out, ref, dqkv, dref = _attn_case(lens, Hq, Hkv, seed=20)
     assert_close_two_rounds(out, ref, atol=2e-2, msg="attention fwd")
@@ -186,3 +191,34 @@ def test_attention_fwd_bwd(lens, Hq, Hkv):
                             rtol=3e-2, msg="dK")
     assert_close_two_rounds(dqkv[:, (Hq + Hkv) * D:], dref[:, (Hq + Hkv) * D:], atol=8e-2, rtol=3e-2,
                             msg="dV")
+
+
+def test_first_backward_of_a_process_may_be_a_custom_function():
+    """A fresh process whose very first backward node is one of this package's autograd
+    Functions: the autograd worker thread has made no CUDA runtime call yet, so no context is
+    current in it when the backward builds its TMA tensor maps (a driver call).  The tensor-map
+    helper binds the context of the device that owns the data and encodes again."""
+    import subprocess
+    import sys
+
+    code = (
+        "import torch\n"
+        "from lorafusion_b200.ops import attention as att, _native\n"
+        "from lorafusion_b200.ops import fused_linear_lora\n"
+        "g = torch.Generator(device='cuda').manual_seed(0)\n"
+        "qkv = torch.randn(128, 384, generator=g, device='cuda').to(torch.bfloat16).requires_grad_(True)\n"
+        "tiles = att.build_attn_tiles([0, 128], 'cuda')\n"
+        "out = att.packed_attention(qkv, tiles, 1, 1)\n"
+        "out.backward(torch.ones_like(out))\n"
+        "x = torch.randn(256, 512, generator=g, device='cuda').to(torch.bfloat16).requires_grad_(True)\n"
+        "w = (torch.randn(512, 512, generator=g, device='cuda') * 0.03).to(torch.bfloat16)\n"
+        "a = (torch.randn(16, 512, generator=g, device='cuda') * 0.03).to(torch.bfloat16).requires_grad_(True)\n"
+        "b = (torch.randn(512, 16, generator=g, device='cuda') * 0.03).to(torch.bfloat16).requires_grad_(True)\n"
+        "y = fused_linear_lora(x, w, a, b, alpha=2.0, dropout_p=0.1, seed=1)\n"
+        "y.backward(torch.ones_like(y))\n"
+        "torch.cuda.synchronize(); _native.check_device_errors()\n"
+        "assert torch.isfinite(qkv.grad.float()).all() and torch.isfinite(x.grad.float()).all()\n"
+        "print('first-backward ok')\n"
+    )
+    res = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0 and "first-backward ok" in res.stdout, res.stdout[-2000:] + res.stderr[-2000:]
