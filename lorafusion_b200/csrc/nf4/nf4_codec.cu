@@ -82,9 +82,14 @@ __global__ void nf4_quantize_kernel(const __nv_bfloat16* __restrict__ w, uint8_t
   if ((t & 7) == 0) absmax[e0 / 64] = am;
 }
 
-// Each thread expands 16 packed bytes into 32 bf16 values.
+// Each thread expands four 4-byte words (8 codes each) that lie one block-width apart, so that
+// every load instruction of a warp reads 128 contiguous bytes and every store instruction writes
+// 512 contiguous bytes (one thread expanding 16 adjacent bytes made each store hit 32 separate
+// 64-byte pieces).
 //   absmax_q == nullptr : `absmax` holds fp32 block scales
 //   absmax_q != nullptr : scale = code256[absmax_q[b]] * nested[b / 256] + offset
+constexpr int kDequantWordsPerThread = 4;
+
 __global__ void nf4_dequantize_kernel(const uint8_t* __restrict__ packed,
                                       const float* __restrict__ absmax,
                                       const uint8_t* __restrict__ absmax_q,
@@ -94,35 +99,33 @@ __global__ void nf4_dequantize_kernel(const uint8_t* __restrict__ packed,
   __shared__ float lut[16];
   if (threadIdx.x < 16) lut[threadIdx.x] = kNf4Code[threadIdx.x];
   __syncthreads();
-  const long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x;
-  const long long e0 = t * 32;
-  if (e0 >= n_elems) return;
-  const long long blk = e0 / 64;
-  float scale;
-  if (absmax_q != nullptr) {
-    scale = code256[absmax_q[blk]] * nested[blk / 256] + offset;
-  } else {
-    scale = absmax[blk];
-  }
-  const uint4 raw = *reinterpret_cast<const uint4*>(packed + e0 / 2);
-  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-  uint32_t o[16];
+  const long long n_words = n_elems / 8;
+  const long long w0 = (long long)blockIdx.x * blockDim.x * kDequantWordsPerThread + threadIdx.x;
+  uint32_t word[kDequantWordsPerThread];
+  float scale[kDequantWordsPerThread];
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const uint32_t byte = (w[i] >> (8 * j)) & 0xffu;
-      const float a = lut[byte >> 4] * scale;
-      const float b = lut[byte & 15u] * scale;
-      __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
-      o[i * 4 + j] = *reinterpret_cast<uint32_t*>(&v);
+  for (int k = 0; k < kDequantWordsPerThread; ++k) {   // all loads first
+    const long long wi = w0 + (long long)k * blockDim.x;
+    if (wi < n_words) {
+      word[k] = reinterpret_cast<const uint32_t*>(packed)[wi];
+      const long long blk = wi / 8;   // 64 codes per scale block
+      scale[k] = (absmax_q != nullptr) ? code256[absmax_q[blk]] * nested[blk / 256] + offset : absmax[blk];
     }
   }
-  uint4* dst = reinterpret_cast<uint4*>(out + e0);
-  dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
-  dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
-  dst[2] = make_uint4(o[8], o[9], o[10], o[11]);
-  dst[3] = make_uint4(o[12], o[13], o[14], o[15]);
+#pragma unroll
+  for (int k = 0; k < kDequantWordsPerThread; ++k) {
+    const long long wi = w0 + (long long)k * blockDim.x;
+    if (wi >= n_words) continue;
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint32_t byte = (word[k] >> (8 * j)) & 0xffu;
+      // even element in the high nibble
+      __nv_bfloat162 v = __floats2bfloat162_rn(lut[byte >> 4] * scale[k], lut[byte & 15u] * scale[k]);
+      o[j] = *reinterpret_cast<uint32_t*>(&v);
+    }
+    reinterpret_cast<uint4*>(out)[wi] = make_uint4(o[0], o[1], o[2], o[3]);
+  }
 }
 
 }  // namespace lf
@@ -147,9 +150,9 @@ int lf_nf4_dequantize(const void* packed, const float* absmax, const void* absma
                       long long n_elems, void* stream) {
   if (n_elems % 64 != 0) return -1;
   if (n_elems == 0) return 0;
-  const long long threads = n_elems / 32;
   const int block = 256;
-  const long long grid = (threads + block - 1) / block;
+  const long long per_block = (long long)block * kDequantWordsPerThread * 8;   // codes per block
+  const long long grid = (n_elems + per_block - 1) / per_block;
   nf4_dequantize_kernel<<<(unsigned)grid, block, 0, (cudaStream_t)stream>>>(
       (const uint8_t*)packed, absmax, (const uint8_t*)absmax_q, code256, nested, offset,
       (__nv_bfloat16*)out, n_elems);
