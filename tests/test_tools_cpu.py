@@ -149,3 +149,25 @@ def test_offload_slots_are_sized_exactly():
     budget = int(0.45 * 205.8e9)
     assert budget // host_slot_bytes(per_gu) == 49
     assert budget // (1 << (per_gu - 1).bit_length()) == 43
+
+
+def test_bench_reference_arm_prints_one_unavailable_line():
+    """``bench.py --impl reference`` cannot run the reference on this image: it says so in one
+    JSON line and exits 0, also when every rank of a multi-process launch calls it."""
+    import json
+    import os
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    bench = Path(__file__).resolve().parents[1] / "bench.py"
+    for rank, expect_lines in ((0, 1), (1, 0)):
+        env = dict(os.environ, RANK=str(rank), WORLD_SIZE="2", LOCAL_RANK=str(rank))
+        res = subprocess.run([sys.executable, str(bench), "--impl", "reference", "--gpus", "2", "--steps", "2",
+                              "--warmup", "1"], capture_output=True, text=True, timeout=300, env=env)
+        assert res.returncode == 0, res.stderr[-2000:]
+        lines = [ln for ln in res.stdout.splitlines() if ln.startswith("{")]
+        assert len(lines) == expect_lines
+        if lines:
+            rec = json.loads(lines[0])
+            assert rec["impl"] == "reference" and "unavailable" in rec and "\n" not in rec["unavailable"]
