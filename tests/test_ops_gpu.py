@@ -220,5 +220,8 @@ def test_first_backward_of_a_process_may_be_a_custom_function():
         "assert torch.isfinite(qkv.grad.float()).all() and torch.isfinite(x.grad.float()).all()\n"
         "print('first-backward ok')\n"
     )
-    res = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=300)
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parents[1]   # the package is imported from the source tree
+    res = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=300, cwd=root)
     assert res.returncode == 0 and "first-backward ok" in res.stdout, res.stdout[-2000:] + res.stderr[-2000:]
